@@ -1,0 +1,45 @@
+// Where a pointer lives and whether this process has a CUDA context, both asked of the driver
+// API, which (unlike the runtime API) never creates a context as a side effect. A program that
+// only passes host buffers therefore stays context-free, as the reference guarantees
+// (src/memspace_cuda.cc:13-53, tests/gpu_host_no_context.cc).
+#include "core/devpath.h"
+#include "device/cudrv.h"
+
+namespace hx {
+
+MemKind classify(const void* p) {
+  if (!p) return MemKind::Null;
+  const CuDriver& d = cu();
+  if (!d.ok) return MemKind::Host;
+  unsigned type = 0;
+  if (d.PointerGetAttribute(&type, CU_POINTER_ATTRIBUTE_MEMORY_TYPE,
+                            reinterpret_cast<CUdeviceptr>(p)) != CUDA_SUCCESS)
+    return MemKind::Host;  // unknown to CUDA: ordinary host memory
+  if (type == CU_MEMORYTYPE_DEVICE) return MemKind::Device;
+  if (type == CU_MEMORYTYPE_UNIFIED) return MemKind::Device;  // managed memory
+  unsigned managed = 0;
+  if (d.PointerGetAttribute(&managed, CU_POINTER_ATTRIBUTE_IS_MANAGED,
+                            reinterpret_cast<CUdeviceptr>(p)) == CUDA_SUCCESS && managed)
+    return MemKind::Device;
+  return MemKind::Host;  // pinned / registered host memory
+}
+
+bool cuda_context_exists() {
+  const CuDriver& d = cu();
+  if (!d.ok) return false;
+  CUcontext cur = nullptr;
+  if (d.CtxGetCurrent(&cur) == CUDA_SUCCESS && cur) return true;
+  int n = 0;
+  if (d.DeviceGetCount(&n) != CUDA_SUCCESS) return false;
+  for (int i = 0; i < n; ++i) {
+    CUdevice dev;
+    unsigned flags = 0;
+    int active = 0;
+    if (d.DeviceGet(&dev, i) == CUDA_SUCCESS &&
+        d.DevicePrimaryCtxGetState(dev, &flags, &active) == CUDA_SUCCESS && active)
+      return true;
+  }
+  return false;
+}
+
+}  // namespace hx

@@ -1,0 +1,225 @@
+#include "device/planner.h"
+
+#include <algorithm>
+#include <cstring>
+
+#include "device/nvls_modes.h"
+#include "math/dtypes.h"
+
+namespace hx {
+namespace {
+size_t round_up(size_t v, size_t m) { return (v + m - 1) / m * m; }
+size_t round_down(size_t v, size_t m) { return v / m * m; }
+size_t ceil_div(size_t a, size_t b) { return (a + b - 1) / b; }
+
+int threads_for(size_t bytes_per_cta) { return bytes_per_cta >= 32 * 1024 ? 512 : 256; }
+
+void clear(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g) {
+  std::memset(a, 0, sizeof *a);
+  a->w = w;
+  a->epoch0 = epoch;
+  a->steps = g.steps;
+  a->sub_bytes = g.sub_bytes;
+  a->slot_stride = round_down(w.half_bytes / w.n, 256);
+}
+}  // namespace
+
+Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t) {
+  Geometry g;
+  const size_t stride = round_down(half_bytes / n, 256);
+  const int cap = std::max(1, std::min(t.max_ctas, kMaxCtas));
+  g.ctas = int(std::min<size_t>(cap, std::max<size_t>(1, ceil_div(max_pair, 16 * 1024))));
+  const size_t fit = round_down(stride / g.ctas, 16);  // what a CTA's share of a slot can hold
+  g.sub_bytes = std::min(std::max<size_t>(16, round_up(ceil_div(max_pair, g.ctas), 16)), fit);
+  g.steps = int(std::max<size_t>(1, ceil_div(max_pair, g.sub_bytes * g.ctas)));
+  g.threads = threads_for(g.sub_bytes * n);
+  return g;
+}
+
+Geometry plan_sliced(size_t bytes, int n, size_t half_bytes, const Tuning& t) {
+  Geometry g;
+  const int cap = std::max(1, std::min(t.max_ctas, kMaxCtas));
+  g.ctas = int(std::min<size_t>(cap, std::max<size_t>(1, ceil_div(bytes, size_t(n) * 16 * 1024))));
+  const size_t fit = round_down(half_bytes / 2 / n / g.ctas, 16);  // staging per (slice, CTA)
+  g.sub_bytes =
+      std::min(std::max<size_t>(16, round_up(ceil_div(bytes, size_t(n) * g.ctas), 16)), fit);
+  g.steps = int(std::max<size_t>(1, ceil_div(bytes, g.sub_bytes * g.ctas * n)));
+  g.threads = threads_for(g.sub_bytes * n);
+  return g;
+}
+
+FoldSpec make_fold(const OpPlan& plan, int kind) {
+  FoldSpec f{};
+  f.kind = kind;
+  f.op = plan.base;
+  f.dir = 1;
+  f.premul = plan.premul ? 1 : 0;
+  f.postdiv = plan.postdiv ? plan.divisor : 0;
+  std::memcpy(&f.scalar_bits, plan.scalar, 8);
+  f.scalar_ptr = plan.scalar_dev;
+  return f;
+}
+
+int choose_variant(size_t bytes, int dt, const OpPlan& plan, int n, const Tuning& t, int forced) {
+  (void)n;
+  const bool nvls_ok = t.nvls && bytes % 16 == 0 && bytes > 0 &&
+                       nvls_mode(dt, plan.base) != kNvNone && (is_integer(dt) || !t.exact);
+  if (forced == kVarNvls && nvls_ok) return kVarNvls;
+  if (forced == kVarOneShot || forced == kVarTwoShot) return forced;
+  if (nvls_ok && bytes >= t.nvls_min) return kVarNvls;
+  return bytes <= t.oneshot_max ? kVarOneShot : kVarTwoShot;
+}
+
+void build_allreduce_oneshot(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                             const void* send, void* recv, size_t count, int dt,
+                             const OpPlan& plan, int order) {
+  clear(a, w, epoch, g);
+  const size_t bytes = count * dtype_size(dt);
+  for (int j = 0; j < w.n; ++j) {
+    a->send_ptr[j] = static_cast<const char*>(send);
+    a->send_bytes[j] = j == w.rank ? 0 : bytes;
+  }
+  a->fold_dst = static_cast<char*>(recv);
+  a->own_ptr = static_cast<const char*>(send);
+  a->fold_bytes = bytes;
+  a->fold_elem0 = 0;
+  a->fold = make_fold(plan, order == kOrderRing ? kFoldLinear : kFoldDoubling);
+  a->fold.ring = order == kOrderRing;
+  a->fold.ring_count = count;
+  a->push_scaled = plan.premul;
+}
+
+void build_allreduce_twoshot(TwoShotArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                             const void* send, void* recv, size_t count, int dt,
+                             const OpPlan& plan, int order, bool use_mc) {
+  std::memset(a, 0, sizeof *a);
+  a->w = w;
+  a->epoch0 = epoch;
+  a->steps = g.steps;
+  a->sub_bytes = g.sub_bytes;
+  a->send = static_cast<const char*>(send);
+  a->recv = static_cast<char*>(recv);
+  a->bytes = count * dtype_size(dt);
+  a->fold = make_fold(plan, order == kOrderRing ? kFoldLinear : kFoldDoubling);
+  a->fold.ring = order == kOrderRing;
+  a->fold.ring_count = count;
+  a->use_mc = use_mc && w.mc != nullptr;
+}
+
+void build_allreduce_nvls(NvlsArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                          const void* send, void* recv, size_t count, int dt, const OpPlan& plan) {
+  std::memset(a, 0, sizeof *a);
+  a->w = w;
+  a->epoch0 = epoch;
+  a->steps = g.steps;
+  a->sub_bytes = g.sub_bytes;
+  a->send = static_cast<const char*>(send);
+  a->recv = static_cast<char*>(recv);
+  a->bytes = count * dtype_size(dt);
+  a->op = plan.base;
+  a->dt = dt;
+  a->premul = plan.premul;
+  a->postdiv = plan.postdiv ? plan.divisor : 0;
+  std::memcpy(&a->scalar_bits, plan.scalar, 8);
+  a->scalar_ptr = plan.scalar_dev;
+}
+
+void build_reducescatter(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                         const void* send, void* recv, size_t per, int dt, const OpPlan& plan) {
+  clear(a, w, epoch, g);
+  const size_t block = per * dtype_size(dt);
+  for (int j = 0; j < w.n; ++j) {
+    a->send_ptr[j] = static_cast<const char*>(send) + size_t(j) * block;
+    a->send_bytes[j] = j == w.rank ? 0 : block;
+  }
+  a->fold_dst = static_cast<char*>(recv);
+  a->own_ptr = static_cast<const char*>(send) + size_t(w.rank) * block;
+  a->fold_bytes = block;
+  a->fold = make_fold(plan, kFoldLinear);  // block b: start with rank b+1, end with rank b
+  a->fold.start = (w.rank + 1) % w.n;
+  a->push_scaled = plan.premul;
+}
+
+void build_reduce(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                  const void* send, void* recv, size_t count, int dt, const OpPlan& plan,
+                  int root) {
+  clear(a, w, epoch, g);
+  const size_t bytes = count * dtype_size(dt);
+  for (int j = 0; j < w.n; ++j) {
+    a->send_ptr[j] = static_cast<const char*>(send);
+    a->send_bytes[j] = (w.rank != root && j == root) ? bytes : 0;
+  }
+  a->push_scaled = plan.premul;
+  if (w.rank != root) return;  // only the root folds
+  a->fold_dst = static_cast<char*>(recv);
+  a->own_ptr = static_cast<const char*>(send);
+  a->fold_bytes = bytes;
+  if (bytes < kTreeMaxBytes) {
+    a->fold = make_fold(plan, kFoldTree);
+    a->fold.root = root;
+  } else {  // chain toward the root: farthest position first
+    a->fold = make_fold(plan, kFoldLinear);
+    a->fold.start = (root + w.n - 1) % w.n;
+    a->fold.dir = -1;
+  }
+}
+
+void build_allgather(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                     const void* send, void* recv, size_t block) {
+  clear(a, w, epoch, g);
+  for (int j = 0; j < w.n; ++j) {
+    a->send_ptr[j] = static_cast<const char*>(send);
+    a->send_bytes[j] = j == w.rank ? 0 : block;
+    a->recv_ptr[j] = static_cast<char*>(recv) + size_t(j) * block;
+    a->recv_bytes[j] = block;
+  }
+}
+
+void build_broadcast(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                     const void* send, void* recv, size_t bytes, int root) {
+  clear(a, w, epoch, g);
+  for (int j = 0; j < w.n; ++j) {
+    a->send_ptr[j] = static_cast<const char*>(send);
+    a->send_bytes[j] = (w.rank == root && j != root) ? bytes : 0;
+    a->recv_ptr[j] = static_cast<char*>(recv);
+    a->recv_bytes[j] = j == root ? bytes : 0;  // on the root this is the send -> recv copy
+  }
+}
+
+void build_gather(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                  const void* send, void* recv, size_t block, int root) {
+  clear(a, w, epoch, g);
+  for (int j = 0; j < w.n; ++j) {
+    a->send_ptr[j] = static_cast<const char*>(send);
+    a->send_bytes[j] = (w.rank != root && j == root) ? block : 0;
+    if (w.rank == root) {
+      a->recv_ptr[j] = static_cast<char*>(recv) + size_t(j) * block;
+      a->recv_bytes[j] = block;
+    }
+  }
+}
+
+void build_scatter(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                   const void* send, void* recv, size_t block, int root) {
+  clear(a, w, epoch, g);
+  for (int j = 0; j < w.n; ++j) {
+    a->send_ptr[j] = static_cast<const char*>(send) + size_t(j) * block;
+    a->send_bytes[j] = (w.rank == root && j != root) ? block : 0;
+    a->recv_ptr[j] = static_cast<char*>(recv);
+    a->recv_bytes[j] = j == root ? block : 0;
+  }
+}
+
+void build_alltoallv(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                     const char* send, const size_t* sbytes, const size_t* soff, char* recv,
+                     const size_t* rbytes, const size_t* roff) {
+  clear(a, w, epoch, g);
+  for (int j = 0; j < w.n; ++j) {
+    a->send_ptr[j] = send + soff[j];
+    a->send_bytes[j] = j == w.rank ? 0 : sbytes[j];
+    a->recv_ptr[j] = recv + roff[j];
+    a->recv_bytes[j] = rbytes[j];
+  }
+}
+
+}  // namespace hx

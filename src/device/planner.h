@@ -1,0 +1,69 @@
+// Turns one rank's collective call into kernel arguments and a launch shape. Pure host code:
+// every rank computes the same geometry from the same (agreed) sizes, which the kernels rely
+// on (same CTA count and step count everywhere). Used by the production path and by the
+// single-GPU world used in tests, so both run exactly the same plans.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+#include "core/devpath.h"
+#include "core/schedule.h"
+#include "device/proto.h"
+
+namespace hx {
+
+struct Geometry {
+  int ctas = 1;
+  int threads = 256;
+  int steps = 1;
+  size_t sub_bytes = 16;
+};
+
+// AllReduce transport variants
+enum : int { kVarAuto = 0, kVarOneShot = 1, kVarTwoShot = 2, kVarNvls = 3 };
+
+struct Tuning {
+  int max_ctas = 64;          // upper bound of any collective grid
+  size_t oneshot_max = 256 * 1024;  // AllReduce: up to here every rank pushes everything
+  bool exact = true;          // floats must match the host path bit for bit
+  bool nvls = false;          // multicast alias available
+  bool nvls_gather = true;    // two-shot publishes results through the multicast alias
+  size_t nvls_min = 512 * 1024;    // AllReduce: from here NVLS, when allowed for (dtype, op)
+};
+
+// generic exchange where the largest block of any pair is `max_pair` bytes
+Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t);
+// two-shot / NVLS AllReduce of `bytes`
+Geometry plan_sliced(size_t bytes, int n, size_t half_bytes, const Tuning& t);
+
+FoldSpec make_fold(const OpPlan& plan, int kind);
+
+// which variant an AllReduce takes
+int choose_variant(size_t bytes, int dt, const OpPlan& plan, int n, const Tuning& t, int forced);
+
+void build_allreduce_oneshot(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                             const void* send, void* recv, size_t count, int dt,
+                             const OpPlan& plan, int order);
+void build_allreduce_twoshot(TwoShotArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                             const void* send, void* recv, size_t count, int dt,
+                             const OpPlan& plan, int order, bool use_mc);
+void build_allreduce_nvls(NvlsArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                          const void* send, void* recv, size_t count, int dt, const OpPlan& plan);
+void build_reducescatter(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                         const void* send, void* recv, size_t per, int dt, const OpPlan& plan);
+void build_reduce(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                  const void* send, void* recv, size_t count, int dt, const OpPlan& plan,
+                  int root);
+void build_allgather(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                     const void* send, void* recv, size_t block);
+void build_broadcast(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                     const void* send, void* recv, size_t bytes, int root);
+void build_gather(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                  const void* send, void* recv, size_t block, int root);
+void build_scatter(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                   const void* send, void* recv, size_t block, int root);
+void build_alltoallv(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                     const char* send, const size_t* sbytes, const size_t* soff, char* recv,
+                     const size_t* rbytes, const size_t* roff);
+
+}  // namespace hx

@@ -1,0 +1,161 @@
+// Layout of a rank's communication window and the argument blocks of the kernels. Shared by
+// the host launchers and the device code.
+//
+// Every rank of a communicator owns one window in its GPU's memory, mapped into every peer's
+// address space (and, where the node has NVSwitch multicast, bound to one multicast object).
+// Kernels move data with plain stores into a peer's window followed by a flag; nothing on the
+// data path goes through the host. This replaces the reference's per-pair cudaIpc staging
+// buffers with host READY/DONE handshakes (src/transport_ipc.cc:13-32, :358-432).
+//
+//   [control]  abort word, Send/Recv counters and flags
+//   [flags A]  one 64-bit epoch per (CTA, source rank): "my step-e data is in your window"
+//   [flags B]  same, for the second phase of two-phase kernels
+//   [p2p]      double-buffered Send/Recv slots, one set per (sender, worker)
+//   [half 0] [half 1]  collective staging, alternating per step
+//
+// Steps. A collective launch runs K >= 1 steps; the communicator numbers all steps of all its
+// launches with one increasing epoch, the same on every rank. Step e stages in half e & 1.
+// In every step each rank signals each rank, so a writer that reached step e+2 has seen the
+// step e+1 signal of the window's owner, which that owner sent only after it finished reading
+// step e: the half is free again without any extra handshake. Flags only ever grow.
+//
+// All waits are bounded: a wait that runs out of time records a status in pinned host memory,
+// raises the abort word in every peer's window (so they stop too) and the kernel returns.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+namespace hx {
+
+constexpr int kMaxRanks = 16;       // ranks of one device communicator
+constexpr int kFastRanks = 8;       // the unrolled fold covers this many
+constexpr int kMaxCtas = 512;       // flag rows
+constexpr int kP2pWorkers = 8;      // independent sub-channels per directed pair
+constexpr size_t kP2pSlotBytes = 128 * 1024;  // per (sender, worker, parity)
+
+// byte offsets inside a window
+constexpr size_t kOffAbort = 0;
+constexpr size_t kOffP2pTx = 4096;    // u64 [kMaxRanks][kP2pWorkers]  chunk-slots sent (local)
+constexpr size_t kOffP2pRx = 8192;    // u64 [kMaxRanks][kP2pWorkers]  chunk-slots taken (local)
+constexpr size_t kOffP2pReady = 12288;  // u64 [sender][worker], written by the sender
+constexpr size_t kOffP2pDone = 16384;   // u64 [receiver][worker], written by the receiver
+constexpr size_t kOffP2pHdr = 20480;    // u64 [sender][worker][2]: message bytes per slot
+constexpr size_t kOffFlagsA = 64 * 1024;
+constexpr size_t kOffFlagsB = kOffFlagsA + size_t(kMaxCtas) * kMaxRanks * 8;
+constexpr size_t kHeaderBytes = 1u << 20;
+constexpr size_t kOffP2pSlots = kHeaderBytes;
+
+inline constexpr size_t p2p_region_bytes(int n) {
+  return size_t(n) * kP2pWorkers * 2 * kP2pSlotBytes;
+}
+
+// status word (pinned host memory, one per communicator): 0 fine, else
+// (code << 56) | detail. Codes below.
+enum : unsigned { kStatTimeout = 1, kStatRemote = 2, kStatTruncated = 3 };
+
+struct WinView {
+  char* win[kMaxRanks];   // every rank's window in this rank's address space (win[rank] local)
+  char* mc;               // multicast alias of the windows, or null
+  unsigned long long* status;  // pinned host status word (sticky failures)
+  unsigned long long* soft;    // pinned host word for truncation reports (not sticky)
+  size_t half_off[2];     // offsets of the two staging halves
+  size_t half_bytes;
+  unsigned long long wait_ns;  // limit of every device-side wait
+  int rank, n;
+};
+
+// How a fold combines the ranks' values for one element (see core/schedule.h):
+//   Linear   acc = x[s0]; then x[s0+dir], x[s0+2dir], ... each as the LEFT operand. With
+//            ring = 1 the start is the index of the ring block the element belongs to plus
+//            `start` (AllReduce ring order start 0; element blocks given by `count`), else
+//            `start` itself (ReduceScatter block b: start b+1; Reduce chain: start root+n-1,
+//            dir -1).
+//   Doubling recursive doubling as rank `rank` sees it.
+//   Tree     binomial tree toward `root` (only the root's value is meaningful).
+enum : int { kFoldLinear = 0, kFoldDoubling = 1, kFoldTree = 2 };
+struct FoldSpec {
+  int kind;
+  int op;          // kSum..kMin
+  int start, dir;  // Linear
+  int ring;        // Linear: add the element's ring-block index to start
+  int root;        // Tree
+  int premul;      // scale own input by the scalar before anything else
+  int postdiv;     // integer Avg divisor, 0 = none
+  unsigned long long scalar_bits;  // scalar when known at launch
+  const void* scalar_ptr;          // else read from here (device memory)
+  size_t ring_count;               // Linear+ring: element count that defines the blocks
+};
+
+// ---- generic exchange: every rank pushes a block to some peers, then copies or folds what
+// ---- landed in its own window. One step moves up to `step_bytes` of every pair's block.
+struct XchgArgs {
+  WinView w;
+  unsigned long long epoch0;
+  int steps;
+  size_t sub_bytes;      // bytes of a pair's block one CTA moves per step (multiple of 16)
+  size_t slot_stride;    // distance between two source ranks' slots in a half
+  // push: bytes [0, send_bytes[j]) at send_ptr[j] go to rank j (0 = nothing)
+  const char* send_ptr[kMaxRanks];
+  size_t send_bytes[kMaxRanks];
+  // copy mode: bytes from rank i land at recv_ptr[i]
+  char* recv_ptr[kMaxRanks];
+  size_t recv_bytes[kMaxRanks];
+  // fold mode (fold_bytes > 0): all n sources (own input at own_ptr, not staged) combine into dst
+  char* fold_dst;
+  const char* own_ptr;
+  size_t fold_bytes;
+  size_t fold_elem0;     // index of dst[0] in the full vector (ring-block lookup)
+  FoldSpec fold;
+  int push_scaled;       // pushes carry input * scalar (fold.premul) instead of raw bytes
+};
+
+// ---- two-shot AllReduce: reduce-scatter into owners, owners fold, all-gather the results
+struct TwoShotArgs {
+  WinView w;
+  unsigned long long epoch0;
+  int steps;
+  size_t sub_bytes;    // per CTA, per slice, per step (multiple of 16)
+  const char* send;
+  char* recv;
+  size_t bytes;        // whole message
+  FoldSpec fold;
+  int use_mc;          // all-gather phase through the multicast alias
+};
+
+// ---- NVLS AllReduce: copy in, multimem.ld_reduce own slice, multimem.st, copy out
+struct NvlsArgs {
+  WinView w;
+  unsigned long long epoch0;
+  int steps;
+  size_t sub_bytes;
+  const char* send;
+  char* recv;
+  size_t bytes;
+  int op;        // kSum / kMax / kMin
+  int dt;        // hxcclDataType_t
+  int premul;    // scale while copying in
+  int postdiv;
+  unsigned long long scalar_bits;
+  const void* scalar_ptr;
+};
+
+// ---- Send/Recv lanes
+struct P2pLaneOp {
+  char* buf;
+  size_t bytes;
+};
+constexpr int kMaxLaneOps = 8;   // operations of one (peer, direction) in one launch
+constexpr int kMaxLanes = 2 * kMaxRanks;
+struct P2pLane {
+  int peer;
+  int is_send;
+  int nops;
+  P2pLaneOp ops[kMaxLaneOps];
+};
+struct P2pArgs {
+  WinView w;
+  int nlanes;
+  P2pLane lanes[kMaxLanes];  // CTA (lane, worker) = blockIdx.x / kP2pWorkers, % kP2pWorkers
+};
+
+}  // namespace hx

@@ -1,0 +1,204 @@
+#include "algos.h"
+
+#include <algorithm>
+#include <cstring>
+#include <vector>
+
+#include "math/reduce_host.h"
+
+namespace hx {
+namespace {
+char* at(void* p, size_t off) { return static_cast<char*>(p) + off; }
+const char* at(const void* p, size_t off) { return static_cast<const char*>(p) + off; }
+#define HX_TRY(expr)                                  \
+  do {                                                \
+    const hxcclResult_t hx_rc_ = (expr);              \
+    if (hx_rc_ != hxcclSuccess) return hx_rc_;        \
+  } while (0)
+}  // namespace
+
+// Reduce-scatter around the ring, then all-gather around the ring: 2(n-1) messages of about
+// count/n elements per rank. Block c starts at rank c and gathers one rank per hop; the
+// receiver's own value is the left operand of each combine.
+hxcclResult_t host_allreduce_ring(HostCtx c, const void* send, void* recv, size_t count, int dt,
+                                  int op) {
+  const size_t es = dtype_size(dt);
+  if (send != recv) std::memmove(recv, send, count * es);
+  if (c.n == 1 || count == 0) return hxcclSuccess;
+  const int next = wrap(c.rank + 1, c.n), prev = wrap(c.rank - 1, c.n);
+  std::vector<char> inbox(ring_block(count, c.n, 0).len * es);
+  auto blk = [&](int i) { return ring_block(count, c.n, wrap(i, c.n)); };
+  for (int hop = 0; hop < c.n - 1; ++hop) {
+    const Span out = blk(c.rank - hop), in = blk(c.rank - hop - 1);
+    HX_TRY(c.wire.exchange(next, at(recv, out.off * es), out.len * es, prev, inbox.data(),
+                           in.len * es));
+    reduce_into(at(recv, in.off * es), inbox.data(), in.len, dt, op);
+  }
+  for (int hop = 0; hop < c.n - 1; ++hop) {
+    const Span out = blk(c.rank + 1 - hop), in = blk(c.rank - hop);
+    HX_TRY(c.wire.exchange(next, at(recv, out.off * es), out.len * es, prev,
+                           at(recv, in.off * es), in.len * es));
+  }
+  return hxcclSuccess;
+}
+
+// Recursive doubling over the largest power of two p <= n. The first 2(n-p) ranks pair up:
+// the even one lends its data to its odd neighbour and later gets the finished result back.
+hxcclResult_t host_allreduce_doubling(HostCtx c, const void* send, void* recv, size_t count,
+                                      int dt, int op) {
+  const size_t bytes = count * dtype_size(dt);
+  if (send != recv) std::memmove(recv, send, bytes);
+  if (c.n == 1 || count == 0) return hxcclSuccess;
+  int p = 1;
+  while (2 * p <= c.n) p *= 2;
+  const int spare = c.n - p;
+  std::vector<char> inbox(bytes);
+  const bool paired = c.rank < 2 * spare;
+  if (paired && c.rank % 2 == 0) {
+    HX_TRY(c.wire.send(c.rank + 1, recv, bytes));
+    return c.wire.recv(c.rank + 1, recv, bytes);
+  }
+  if (paired) {
+    HX_TRY(c.wire.recv(c.rank - 1, inbox.data(), bytes));
+    reduce_into(recv, inbox.data(), count, dt, op);
+  }
+  const int me = paired ? c.rank / 2 : c.rank - spare;  // index among the p active ranks
+  for (int bit = 1; bit < p; bit <<= 1) {
+    const int q = me ^ bit;
+    const int peer = q < spare ? 2 * q + 1 : q + spare;
+    HX_TRY(c.wire.exchange(peer, recv, bytes, peer, inbox.data(), bytes));
+    reduce_into(recv, inbox.data(), count, dt, op);
+  }
+  if (paired) return c.wire.send(c.rank - 1, recv, bytes);
+  return hxcclSuccess;
+}
+
+hxcclResult_t host_allgather(HostCtx c, const void* send, void* recv, size_t block) {
+  if (send != at(recv, c.rank * block)) std::memmove(at(recv, c.rank * block), send, block);
+  if (c.n == 1 || block == 0) return hxcclSuccess;
+  const int next = wrap(c.rank + 1, c.n), prev = wrap(c.rank - 1, c.n);
+  for (int hop = 0; hop < c.n - 1; ++hop) {
+    const int out = wrap(c.rank - hop, c.n), in = wrap(c.rank - hop - 1, c.n);
+    HX_TRY(c.wire.exchange(next, at(recv, out * block), block, prev, at(recv, in * block), block));
+  }
+  return hxcclSuccess;
+}
+
+// Ring reduce-scatter on a private copy of the input (recv may point into send). The hops
+// are one block ahead of the AllReduce schedule so that rank r finishes with block r.
+hxcclResult_t host_reducescatter(HostCtx c, const void* send, void* recv, size_t per, int dt,
+                                 int op) {
+  const size_t block = per * dtype_size(dt);
+  if (per == 0) return hxcclSuccess;
+  std::vector<char> work(block * c.n), inbox(block);
+  std::memcpy(work.data(), send, work.size());
+  const int next = wrap(c.rank + 1, c.n), prev = wrap(c.rank - 1, c.n);
+  for (int hop = 0; hop < c.n - 1; ++hop) {
+    const int out = wrap(c.rank - hop - 1, c.n), in = wrap(c.rank - hop - 2, c.n);
+    HX_TRY(c.wire.exchange(next, work.data() + out * block, block, prev, inbox.data(), block));
+    reduce_into(work.data() + in * block, inbox.data(), per, dt, op);
+  }
+  std::memcpy(recv, work.data() + c.rank * block, block);
+  return hxcclSuccess;
+}
+
+// Small: binomial tree rooted at `root`. Large: a chain root -> root+1 -> ... in pieces.
+hxcclResult_t host_broadcast(HostCtx c, const void* send, void* recv, size_t bytes, int root) {
+  if (c.rank == root && send != recv) std::memmove(recv, send, bytes);
+  if (c.n == 1 || bytes == 0) return hxcclSuccess;
+  const int pos = wrap(c.rank - root, c.n);
+  auto rank_at = [&](int v) { return (v + root) % c.n; };
+  if (bytes < kTreeMaxBytes) {
+    int bit = 1;
+    for (; bit < c.n; bit <<= 1)
+      if (pos & bit) {
+        HX_TRY(c.wire.recv(rank_at(pos - bit), recv, bytes));
+        break;
+      }
+    for (bit >>= 1; bit > 0; bit >>= 1)
+      if (pos + bit < c.n) HX_TRY(c.wire.send(rank_at(pos + bit), recv, bytes));
+    return hxcclSuccess;
+  }
+  for (size_t off = 0; off < bytes; off += kChainPiece) {
+    const size_t len = std::min(kChainPiece, bytes - off);
+    if (pos > 0) HX_TRY(c.wire.recv(rank_at(pos - 1), at(recv, off), len));
+    if (pos < c.n - 1) HX_TRY(c.wire.send(rank_at(pos + 1), at(recv, off), len));
+  }
+  return hxcclSuccess;
+}
+
+// Mirror image of the broadcast: partial results flow toward the root. Non-root ranks may
+// have no recv buffer, so they work in a private copy.
+hxcclResult_t host_reduce(HostCtx c, const void* send, void* recv, size_t count, int dt, int op,
+                          int root) {
+  const size_t es = dtype_size(dt), bytes = count * es;
+  std::vector<char> own;
+  char* acc;
+  if (c.rank == root) {
+    acc = static_cast<char*>(recv);
+    if (send != recv) std::memmove(acc, send, bytes);
+  } else {
+    own.assign(at(send, 0), at(send, bytes));
+    acc = own.data();
+  }
+  if (c.n == 1 || count == 0) return hxcclSuccess;
+  const int pos = wrap(c.rank - root, c.n);
+  auto rank_at = [&](int v) { return (v + root) % c.n; };
+  if (bytes < kTreeMaxBytes) {
+    std::vector<char> inbox(bytes);
+    for (int bit = 1; bit < c.n; bit <<= 1) {
+      if (pos & bit) return c.wire.send(rank_at(pos - bit), acc, bytes);
+      if (pos + bit < c.n) {
+        HX_TRY(c.wire.recv(rank_at(pos + bit), inbox.data(), bytes));
+        reduce_into(acc, inbox.data(), count, dt, op);
+      }
+    }
+    return hxcclSuccess;
+  }
+  std::vector<char> inbox(kChainPiece);  // a multiple of every element size
+  for (size_t off = 0; off < bytes; off += kChainPiece) {
+    const size_t len = std::min(kChainPiece, bytes - off);
+    if (pos < c.n - 1) {
+      HX_TRY(c.wire.recv(rank_at(pos + 1), inbox.data(), len));
+      reduce_into(acc + off, inbox.data(), len / es, dt, op);
+    }
+    if (pos > 0) HX_TRY(c.wire.send(rank_at(pos - 1), acc + off, len));
+  }
+  return hxcclSuccess;
+}
+
+hxcclResult_t host_gather(HostCtx c, const void* send, void* recv, size_t block, int root) {
+  if (block == 0) return hxcclSuccess;
+  if (c.rank != root) return c.wire.send(root, send, block);
+  if (send != at(recv, root * block)) std::memmove(at(recv, root * block), send, block);
+  for (int i = 0; i < c.n; ++i)
+    if (i != root) c.wire.post_recv(i, at(recv, i * block), block, kTagColl);
+  return c.wire.finish_all();
+}
+
+hxcclResult_t host_scatter(HostCtx c, const void* send, void* recv, size_t block, int root) {
+  if (block == 0) return hxcclSuccess;
+  if (c.rank != root) return c.wire.recv(root, recv, block);
+  for (int i = 0; i < c.n; ++i)
+    if (i != root)
+      if (hxcclResult_t r = c.wire.post_send(i, at(send, i * block), block, kTagColl)) {
+        c.wire.cancel_all();
+        return r;
+      }
+  if (recv != at(send, root * block)) std::memmove(recv, at(send, root * block), block);
+  return c.wire.finish_all();
+}
+
+// Pairwise exchange: in round k a rank sends to rank+k and receives from rank-k.
+hxcclResult_t host_alltoallv(HostCtx c, const char* send, const size_t* sbytes,
+                             const size_t* soff, char* recv, const size_t* rbytes,
+                             const size_t* roff) {
+  if (rbytes[c.rank]) std::memmove(recv + roff[c.rank], send + soff[c.rank], rbytes[c.rank]);
+  for (int k = 1; k < c.n; ++k) {
+    const int to = (c.rank + k) % c.n, from = wrap(c.rank - k, c.n);
+    HX_TRY(c.wire.exchange(to, send + soff[to], sbytes[to], from, recv + roff[from], rbytes[from]));
+  }
+  return hxcclSuccess;
+}
+
+}  // namespace hx

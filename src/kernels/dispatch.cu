@@ -1,0 +1,144 @@
+// Type-independent kernels (byte exchange, Send/Recv lanes, NVLS) and the run-time dispatch
+// from hxcclDataType_t to the per-type launchers.
+#include "kernels/inst.cuh"
+#include "kernels/nvls_body.cuh"
+#include "kernels/p2p_body.cuh"
+#include "math/dtypes.h"
+
+namespace hx {
+
+__global__ void __launch_bounds__(512) k_xchg_copy(const __grid_constant__ XchgArgs a) {
+  __shared__ FoldShared sh;
+  xchg_body<uint8_t, false>(a, blockIdx.x, gridDim.x, sh);
+}
+__global__ void __launch_bounds__(512) k_xchg_copy_world(const XchgArgs* a) {
+  __shared__ FoldShared sh;
+  xchg_body<uint8_t, false>(a[blockIdx.y], blockIdx.x, gridDim.x, sh);
+}
+__global__ void __launch_bounds__(512) k_p2p(const __grid_constant__ P2pArgs a) {
+  __shared__ int fail;
+  __shared__ unsigned long long word;
+  p2p_body(a, blockIdx.x / kP2pWorkers, blockIdx.x % kP2pWorkers, &fail, &word);
+}
+__global__ void __launch_bounds__(512) k_p2p_world(const P2pArgs* a) {
+  __shared__ int fail;
+  __shared__ unsigned long long word;
+  const P2pArgs& mine = a[blockIdx.y];
+  if (int(blockIdx.x) / kP2pWorkers < mine.nlanes)
+    p2p_body(mine, blockIdx.x / kP2pWorkers, blockIdx.x % kP2pWorkers, &fail, &word);
+}
+template <typename T, int kMode>
+__global__ void __launch_bounds__(512) k_nvls(const __grid_constant__ NvlsArgs a) {
+  __shared__ FoldShared sh;
+  nvls_body<T, kMode>(a, blockIdx.x, gridDim.x, sh);
+}
+
+cudaError_t launch_xchg_copy(const XchgArgs* args, LaunchShape s, cudaStream_t st) {
+  if (s.world) return launch_world(reinterpret_cast<const void*>(&k_xchg_copy_world), args, s, st);
+  k_xchg_copy<<<s.ctas, s.threads, 0, st>>>(*args);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_p2p(const P2pArgs* args, LaunchShape s, cudaStream_t st) {
+  if (s.world) return launch_world(reinterpret_cast<const void*>(&k_p2p_world), args, s, st);
+  k_p2p<<<s.ctas, s.threads, 0, st>>>(*args);
+  return cudaGetLastError();
+}
+
+#define HX_EXTERN_TYPE(T)                                                                       \
+  extern template cudaError_t launch_xchg_fold_t<T>(const XchgArgs*, LaunchShape, cudaStream_t); \
+  extern template cudaError_t launch_twoshot_t<T>(const TwoShotArgs*, LaunchShape, cudaStream_t); \
+  extern template cudaError_t launch_reduce_t<T>(void*, const void*, size_t, int, cudaStream_t); \
+  extern template cudaError_t launch_scale_t<T>(void*, const void*, size_t, unsigned long long, \
+                                                cudaStream_t);                                  \
+  extern template cudaError_t launch_divide_t<T>(void*, size_t, int, cudaStream_t);
+HX_EXTERN_TYPE(int8_t)
+HX_EXTERN_TYPE(uint8_t)
+HX_EXTERN_TYPE(int32_t)
+HX_EXTERN_TYPE(uint32_t)
+HX_EXTERN_TYPE(int64_t)
+HX_EXTERN_TYPE(uint64_t)
+HX_EXTERN_TYPE(float)
+HX_EXTERN_TYPE(double)
+HX_EXTERN_TYPE(f16)
+HX_EXTERN_TYPE(bf16)
+HX_EXTERN_TYPE(e4m3)
+HX_EXTERN_TYPE(e5m2)
+
+cudaError_t launch_xchg_fold(int dt, const XchgArgs* args, LaunchShape s, cudaStream_t st) {
+  cudaError_t rc = cudaErrorInvalidValue;
+  HX_DISPATCH_DTYPE(dt, rc = launch_xchg_fold_t<T>(args, s, st))
+  return rc;
+}
+cudaError_t launch_twoshot(int dt, const TwoShotArgs* args, LaunchShape s, cudaStream_t st) {
+  cudaError_t rc = cudaErrorInvalidValue;
+  HX_DISPATCH_DTYPE(dt, rc = launch_twoshot_t<T>(args, s, st))
+  return rc;
+}
+cudaError_t launch_reduce(void* dst, const void* src, size_t count, int dt, int op, cudaStream_t st) {
+  cudaError_t rc = cudaErrorInvalidValue;
+  HX_DISPATCH_DTYPE(dt, rc = launch_reduce_t<T>(dst, src, count, op, st))
+  return rc;
+}
+cudaError_t launch_scale(void* dst, const void* src, size_t count, int dt, const void* scalar_host,
+                         cudaStream_t st) {
+  unsigned long long bits = 0;
+  memcpy(&bits, scalar_host, dtype_size(dt));
+  cudaError_t rc = cudaErrorInvalidValue;
+  HX_DISPATCH_DTYPE(dt, rc = launch_scale_t<T>(dst, src, count, bits, st))
+  return rc;
+}
+cudaError_t launch_divide(void* buf, size_t count, int dt, int divisor, cudaStream_t st) {
+  cudaError_t rc = cudaErrorInvalidValue;
+  HX_DISPATCH_DTYPE(dt, rc = launch_divide_t<T>(buf, count, divisor, st))
+  return rc;
+}
+
+#define HX_NVLS_CASE(MODE, T)                             \
+  case MODE:                                              \
+    k_nvls<T, MODE><<<s.ctas, s.threads, 0, st>>>(*args); \
+    break;
+cudaError_t launch_nvls(const NvlsArgs* args, LaunchShape s, cudaStream_t st) {
+  switch (nvls_mode(args->dt, args->op)) {
+    HX_NVLS_CASE(kNvF32Add, float)
+    HX_NVLS_CASE(kNvF64Add, double)
+    HX_NVLS_CASE(kNvF16Add, f16)
+    HX_NVLS_CASE(kNvF16Min, f16)
+    HX_NVLS_CASE(kNvF16Max, f16)
+    HX_NVLS_CASE(kNvBf16Add, bf16)
+    HX_NVLS_CASE(kNvBf16Min, bf16)
+    HX_NVLS_CASE(kNvBf16Max, bf16)
+    HX_NVLS_CASE(kNvS32Add, int32_t)  // wrapping add: the same bits for signed and unsigned
+    HX_NVLS_CASE(kNvS32Min, int32_t)
+    HX_NVLS_CASE(kNvS32Max, int32_t)
+    HX_NVLS_CASE(kNvU32Min, uint32_t)
+    HX_NVLS_CASE(kNvU32Max, uint32_t)
+    HX_NVLS_CASE(kNvU64Add, uint64_t)
+    HX_NVLS_CASE(kNvS64Min, int64_t)
+    HX_NVLS_CASE(kNvS64Max, int64_t)
+    HX_NVLS_CASE(kNvU64Min, uint64_t)
+    HX_NVLS_CASE(kNvU64Max, uint64_t)
+    HX_NVLS_CASE(kNvE4m3Add, e4m3)
+    HX_NVLS_CASE(kNvE4m3Min, e4m3)
+    HX_NVLS_CASE(kNvE4m3Max, e4m3)
+    HX_NVLS_CASE(kNvE5m2Add, e5m2)
+    HX_NVLS_CASE(kNvE5m2Min, e5m2)
+    HX_NVLS_CASE(kNvE5m2Max, e5m2)
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+int max_resident_ctas(int threads) {
+  int dev = 0, sms = 0, per_sm = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 1;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // the double-precision two-shot kernel is the heaviest in registers
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_twoshot<double>, threads, 0) !=
+          cudaSuccess ||
+      per_sm < 1)
+    per_sm = 1;
+  return sms * per_sm;
+}
+
+}  // namespace hx

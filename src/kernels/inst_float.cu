@@ -1,0 +1,4 @@
+#include "kernels/inst.cuh"
+namespace hx {
+HX_INSTANTIATE_TYPE(float)
+}

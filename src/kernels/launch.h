@@ -1,0 +1,34 @@
+// Host-callable launchers of the sm_100a kernels. `world` > 1 launches the single-GPU
+// "whole world in one grid" form: args then points to `world` argument blocks in device
+// memory and blockIdx.y selects the rank (cooperative launch, so all ranks' CTAs are
+// co-resident and can wait on one another). world == 0 launches the production form with
+// the one argument block passed by value.
+#pragma once
+#include <cuda_runtime.h>
+
+#include "device/proto.h"
+
+namespace hx {
+
+struct LaunchShape {
+  int ctas;
+  int threads;
+  int world;  // 0 = production (one rank per GPU)
+};
+
+cudaError_t launch_xchg_copy(const XchgArgs* args, LaunchShape s, cudaStream_t st);
+cudaError_t launch_xchg_fold(int dt, const XchgArgs* args, LaunchShape s, cudaStream_t st);
+cudaError_t launch_twoshot(int dt, const TwoShotArgs* args, LaunchShape s, cudaStream_t st);
+cudaError_t launch_nvls(const NvlsArgs* args, LaunchShape s, cudaStream_t st);  // production only
+cudaError_t launch_p2p(const P2pArgs* args, LaunchShape s, cudaStream_t st);
+
+// standalone elementwise kernels (dst op= src, dst = src*scalar, buf /= divisor)
+cudaError_t launch_reduce(void* dst, const void* src, size_t count, int dt, int op, cudaStream_t st);
+cudaError_t launch_scale(void* dst, const void* src, size_t count, int dt, const void* scalar_host,
+                         cudaStream_t st);
+cudaError_t launch_divide(void* buf, size_t count, int dt, int divisor, cudaStream_t st);
+
+// largest grid of `threads`-wide CTAs of the widest collective kernel that is co-resident
+int max_resident_ctas(int threads);
+
+}  // namespace hx

@@ -1,0 +1,131 @@
+// AllReduce through NVSwitch multicast (NVLS). Each rank copies its input into its window,
+// then reduces the slice it owns with multimem.ld_reduce (the switch fetches the slice from
+// every GPU and combines it on the way) and publishes the result to every GPU with one
+// multimem.st. The switch's combining order and precision are not specified, so for floating
+// types this variant is offered only when bit-exactness is switched off (HXCCL_EXACT=0);
+// integer sum/min/max are exact under any order and may use it always.
+#pragma once
+#include "hxccl.h"
+#include "kernels/fold.cuh"
+#include "device/nvls_modes.h"
+#include "math/dtypes.h"
+
+namespace hx {
+
+#define HX_MM_V4(INSTR, p, v)                                                   \
+  asm volatile("multimem.ld_reduce.relaxed.sys.global." INSTR " {%0,%1,%2,%3}, [%4];" \
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)                     \
+               : "l"(p)                                                          \
+               : "memory")
+#define HX_MM_S32(INSTR, p, v)                                                              \
+  do {                                                                                       \
+    asm volatile("multimem.ld_reduce.relaxed.sys.global." INSTR " %0, [%1];" : "=r"(v.x) : "l"(p) : "memory");       \
+    asm volatile("multimem.ld_reduce.relaxed.sys.global." INSTR " %0, [%1];" : "=r"(v.y) : "l"(p + 4) : "memory");   \
+    asm volatile("multimem.ld_reduce.relaxed.sys.global." INSTR " %0, [%1];" : "=r"(v.z) : "l"(p + 8) : "memory");   \
+    asm volatile("multimem.ld_reduce.relaxed.sys.global." INSTR " %0, [%1];" : "=r"(v.w) : "l"(p + 12) : "memory");  \
+  } while (0)
+#define HX_MM_S64(INSTR, p, v)                                                              \
+  do {                                                                                       \
+    unsigned long long lo_, hi_;                                                             \
+    asm volatile("multimem.ld_reduce.relaxed.sys.global." INSTR " %0, [%1];" : "=l"(lo_) : "l"(p) : "memory");       \
+    asm volatile("multimem.ld_reduce.relaxed.sys.global." INSTR " %0, [%1];" : "=l"(hi_) : "l"(p + 8) : "memory");   \
+    v.x = unsigned(lo_); v.y = unsigned(lo_ >> 32); v.z = unsigned(hi_); v.w = unsigned(hi_ >> 32);                  \
+  } while (0)
+
+template <int kMode>
+__device__ __forceinline__ uint4 mm_reduce16(const char* p) {
+  uint4 v;
+  if (kMode == kNvF32Add) HX_MM_V4("add.v4.f32", p, v);
+  else if (kMode == kNvF64Add) HX_MM_S64("add.f64", p, v);
+  else if (kMode == kNvF16Add) HX_MM_V4("add.acc::f32.v4.f16x2", p, v);
+  else if (kMode == kNvF16Min) HX_MM_V4("min.v4.f16x2", p, v);
+  else if (kMode == kNvF16Max) HX_MM_V4("max.v4.f16x2", p, v);
+  else if (kMode == kNvBf16Add) HX_MM_V4("add.acc::f32.v4.bf16x2", p, v);
+  else if (kMode == kNvBf16Min) HX_MM_V4("min.v4.bf16x2", p, v);
+  else if (kMode == kNvBf16Max) HX_MM_V4("max.v4.bf16x2", p, v);
+  else if (kMode == kNvS32Add) HX_MM_S32("add.u32", p, v);
+  else if (kMode == kNvS32Min) HX_MM_S32("min.s32", p, v);
+  else if (kMode == kNvS32Max) HX_MM_S32("max.s32", p, v);
+  else if (kMode == kNvU32Min) HX_MM_S32("min.u32", p, v);
+  else if (kMode == kNvU32Max) HX_MM_S32("max.u32", p, v);
+  else if (kMode == kNvU64Add) HX_MM_S64("add.u64", p, v);
+  else if (kMode == kNvS64Min) HX_MM_S64("min.s64", p, v);
+  else if (kMode == kNvS64Max) HX_MM_S64("max.s64", p, v);
+  else if (kMode == kNvU64Min) HX_MM_S64("min.u64", p, v);
+  else if (kMode == kNvU64Max) HX_MM_S64("max.u64", p, v);
+  else if (kMode == kNvE4m3Add) HX_MM_V4("add.acc::f16.v4.e4m3x4", p, v);
+  else if (kMode == kNvE4m3Min) HX_MM_V4("min.v4.e4m3x4", p, v);
+  else if (kMode == kNvE4m3Max) HX_MM_V4("max.v4.e4m3x4", p, v);
+  else if (kMode == kNvE5m2Add) HX_MM_V4("add.acc::f16.v4.e5m2x4", p, v);
+  else if (kMode == kNvE5m2Min) HX_MM_V4("min.v4.e5m2x4", p, v);
+  else HX_MM_V4("max.v4.e5m2x4", p, v);
+  return v;
+}
+
+template <typename T, int kMode>
+__device__ void nvls_body(const NvlsArgs& a, int cta, int ncta, FoldShared& sh) {
+  const WinView& w = a.w;
+  const int me = w.rank, n = w.n;
+  constexpr int V = 16 / sizeof(T);
+  T scalar{};
+  if (a.premul) {
+    FoldSpec f{};
+    f.scalar_bits = a.scalar_bits;
+    f.scalar_ptr = a.scalar_ptr;
+    scalar = load_scalar<T>(f);
+  }
+  if (threadIdx.x == 0) sh.fail = 0;
+  char* mine = w.win[me];
+  const size_t slice = size_t(ncta) * a.sub_bytes;
+  const size_t out_base = w.half_bytes / 2;
+  const size_t in_slice = size_t(cta) * a.sub_bytes;
+  for (int step = 0; step < a.steps; ++step) {
+    const unsigned long long epoch = a.epoch0 + step;
+    const size_t half = w.half_off[epoch & 1];
+    const size_t step0 = size_t(step) * n * slice;
+    // my input, every slice's part of this CTA, into my own window
+    for (int j = 0; j < n; ++j) {
+      const size_t lo = step0 + size_t(j) * slice + in_slice;
+      if (lo >= a.bytes) continue;
+      const size_t len = min_sz(a.sub_bytes, a.bytes - lo);
+      char* to = mine + half + size_t(j) * slice + in_slice;
+      if (a.premul)
+        cta_scale_copy<T>(to, a.send + lo, len, scalar);
+      else
+        cta_copy(to, a.send + lo, len);
+    }
+    if (!signal_and_wait(w, kOffFlagsA, cta, epoch, &sh.fail)) return;
+    {
+      const size_t lo = step0 + size_t(me) * slice + in_slice;
+      if (lo < a.bytes) {
+        const size_t len = min_sz(a.sub_bytes, a.bytes - lo);  // a multiple of 16 (host checks)
+        const char* in = w.mc + half + size_t(me) * slice + in_slice;
+        char* out = w.mc + half + out_base + size_t(me) * slice + in_slice;
+        const bool direct = (reinterpret_cast<uintptr_t>(a.recv + lo) & 15u) == 0;
+        for (size_t v = threadIdx.x; v < (len >> 4); v += blockDim.x) {
+          Vec16<T> r;
+          r.raw = mm_reduce16<kMode>(in + (v << 4));
+          if (a.postdiv) {
+#pragma unroll
+            for (int l = 0; l < V; ++l) r.e[l] = div_trunc(r.e[l], a.postdiv);
+          }
+          asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(out + (v << 4)),
+                       "r"(r.raw.x), "r"(r.raw.y), "r"(r.raw.z), "r"(r.raw.w)
+                       : "memory");
+          if (direct) st16(a.recv + lo + (v << 4), r.raw);
+        }
+      }
+    }
+    if (!signal_and_wait(w, kOffFlagsB, cta, epoch, &sh.fail)) return;
+    for (int ii = 0; ii < n; ++ii) {
+      const int i = (me + ii) % n;
+      const size_t lo = step0 + size_t(i) * slice + in_slice;
+      if (lo >= a.bytes) continue;
+      if (i == me && (reinterpret_cast<uintptr_t>(a.recv + lo) & 15u) == 0) continue;  // stored directly
+      cta_copy(a.recv + lo, mine + half + out_base + size_t(i) * slice + in_slice,
+               min_sz(a.sub_bytes, a.bytes - lo));
+    }
+  }
+}
+
+}  // namespace hx

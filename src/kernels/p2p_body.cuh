@@ -1,0 +1,108 @@
+// Send/Recv as peer-copy lanes. Every Send and Recv of a group on one communicator runs in a
+// single launch: the operations toward one peer in one direction form a lane, a lane is split
+// over kP2pWorkers CTAs, and each (lane, worker) streams its share of every message through a
+// double-buffered slot in the receiver's window:
+//   sender    wait until the slot's previous occupant was taken (done flag in MY window),
+//             store the bytes and the message length, then raise the receiver's ready flag;
+//   receiver  wait for ready, read the length, copy min(sent, wanted) bytes out, raise the
+//             sender's done flag.
+// Counters only grow; both sides keep theirs in their own window between launches. A message
+// longer than the receive buffer delivers the leading bytes and reports truncation on the
+// receiver only (reference behaviour: src/transport_ipc.cc:424-429); the sender succeeds and
+// later transfers are unaffected. This replaces the reference's host-driven READY/DONE chunk
+// protocol (src/transport_ipc.cc:358-432).
+#pragma once
+#include "kernels/prims.cuh"
+
+namespace hx {
+
+__device__ __forceinline__ unsigned long long* p2p_word(char* win, size_t base, int peer, int worker) {
+  return reinterpret_cast<unsigned long long*>(win + base) + size_t(peer) * kP2pWorkers + worker;
+}
+__device__ __forceinline__ char* p2p_slot(char* win, int sender, int worker, unsigned parity) {
+  return win + kOffP2pSlots + ((size_t(sender) * kP2pWorkers + worker) * 2 + parity) * kP2pSlotBytes;
+}
+__device__ __forceinline__ unsigned long long* p2p_hdr(char* win, int sender, int worker, unsigned parity) {
+  return reinterpret_cast<unsigned long long*>(win + kOffP2pHdr) +
+         (size_t(sender) * kP2pWorkers + worker) * 2 + parity;
+}
+
+// bytes of `total` that worker `wk` moves in round q (rounds advance by kP2pWorkers slots)
+__device__ __forceinline__ void p2p_share(size_t total, unsigned long long q, int wk, size_t* off,
+                                          size_t* len) {
+  const size_t o = (q * kP2pWorkers + wk) * kP2pSlotBytes;
+  *off = o;
+  *len = o >= total ? 0 : (total - o < kP2pSlotBytes ? total - o : kP2pSlotBytes);
+}
+__device__ __forceinline__ unsigned long long p2p_rounds(size_t total) {
+  const size_t per = size_t(kP2pWorkers) * kP2pSlotBytes;
+  const unsigned long long r = (total + per - 1) / per;
+  return r ? r : 1;  // an empty message still takes one hand-shake
+}
+
+__device__ inline void p2p_body(const P2pArgs& a, int lane_idx, int wk, int* sh_fail, unsigned long long* sh_word) {
+  const WinView& w = a.w;
+  const P2pLane& lane = a.lanes[lane_idx];
+  const int me = w.rank, peer = lane.peer;
+  char* mine = w.win[me];
+  char* theirs = w.win[peer];
+  if (threadIdx.x == 0) *sh_fail = 0;
+  __syncthreads();
+  if (lane.is_send) {
+    unsigned long long* tx_state = p2p_word(mine, kOffP2pTx, peer, wk);
+    unsigned long long tx = *tx_state;
+    const unsigned long long* done = p2p_word(mine, kOffP2pDone, peer, wk);
+    unsigned long long* ready = p2p_word(theirs, kOffP2pReady, me, wk);
+    for (int k = 0; k < lane.nops; ++k) {
+      const size_t total = lane.ops[k].bytes;
+      const unsigned long long rounds = p2p_rounds(total);
+      for (unsigned long long q = 0; q < rounds; ++q, ++tx) {
+        if (threadIdx.x == 0 && tx >= 2 && !wait_flag(w, done, tx - 1, peer)) *sh_fail = 1;
+        __syncthreads();
+        if (*sh_fail) return;
+        size_t off, len;
+        p2p_share(total, q, wk, &off, &len);
+        if (len) cta_copy(p2p_slot(theirs, me, wk, tx & 1), lane.ops[k].buf + off, len);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          st_relaxed_sys(p2p_hdr(theirs, me, wk, tx & 1), total);
+          __threadfence_system();
+          st_release_sys(ready, tx + 1);
+        }
+      }
+    }
+    if (threadIdx.x == 0) *tx_state = tx;
+  } else {
+    unsigned long long* rx_state = p2p_word(mine, kOffP2pRx, peer, wk);
+    unsigned long long rx = *rx_state;
+    const unsigned long long* ready = p2p_word(mine, kOffP2pReady, peer, wk);
+    unsigned long long* done = p2p_word(theirs, kOffP2pDone, me, wk);
+    for (int k = 0; k < lane.nops; ++k) {
+      const size_t room = lane.ops[k].bytes;
+      unsigned long long rounds = 1;
+      for (unsigned long long q = 0; q < rounds; ++q, ++rx) {
+        if (threadIdx.x == 0) {
+          if (!wait_flag(w, ready, rx + 1, peer)) *sh_fail = 1;
+          *sh_word = ld_relaxed_sys(p2p_hdr(mine, peer, wk, rx & 1));
+        }
+        __syncthreads();
+        if (*sh_fail) return;
+        const size_t total = *sh_word;
+        if (q == 0) rounds = p2p_rounds(total);
+        size_t off, len;
+        p2p_share(total, q, wk, &off, &len);
+        if (off < room && len) {
+          const size_t take = room - off < len ? room - off : len;
+          cta_copy(lane.ops[k].buf + off, p2p_slot(mine, peer, wk, rx & 1), take);
+        }
+        if (q == 0 && wk == 0 && threadIdx.x == 0 && total > room)
+          st_relaxed_sys(w.soft, (static_cast<unsigned long long>(kStatTruncated) << 56) | unsigned(peer));
+        __syncthreads();
+        if (threadIdx.x == 0) st_release_sys(done, rx + 1);
+      }
+    }
+    if (threadIdx.x == 0) *rx_state = rx;
+  }
+}
+
+}  // namespace hx
