@@ -1,0 +1,120 @@
+"""Builds the native parts in-tree: libhxccl.so (C API, host path, sm_100a kernels) and, on
+request, the torch.distributed backend extension.
+
+    python -m hxccl_b200.build            # library
+    python -m hxccl_b200.build --torch    # library + torch backend
+
+The CUDA sources are compiled for sm_100a only (-gencode arch=compute_100a,code=sm_100a);
+nvcc cross-compiles, so no GPU is needed to build. Objects land in build/ (ignored by git),
+the shared objects next to this file so that they travel with the source tree.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+SRC = ROOT / "src"
+OBJ = ROOT / "build" / "obj"
+LIB_DIR = Path(__file__).resolve().parent / "lib"
+LIB = LIB_DIR / "libhxccl.so"
+CUDA_HOME = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+NVCC = str(CUDA_HOME / "bin" / "nvcc")
+
+INCLUDES = [f"-I{ROOT / 'include'}", f"-I{SRC}", f"-I{CUDA_HOME / 'include'}"]
+CXXFLAGS = ["-std=c++17", "-O2", "-fPIC", "-ffp-contract=off", "-Wall", "-Wextra", "-pthread"]
+NVCCFLAGS = [
+    "-std=c++17", "-O3", "-lineinfo",
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-Xcompiler", "-fPIC", "-fmad=false",
+]
+
+
+def _newest_header() -> float:
+    hdrs = list(SRC.rglob("*.h")) + list(SRC.rglob("*.cuh")) + list((ROOT / "include").glob("*.h"))
+    return max(p.stat().st_mtime for p in hdrs)
+
+
+def _compile(src: Path, hdr_time: float, verbose: bool) -> Path:
+    obj = OBJ / (str(src.relative_to(SRC)).replace("/", "_") + ".o")
+    if obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, hdr_time):
+        return obj
+    if src.suffix == ".cu":
+        cmd = [NVCC, *NVCCFLAGS, *INCLUDES, "-c", str(src), "-o", str(obj)]
+    else:
+        cmd = [os.environ.get("CXX", "g++"), *CXXFLAGS, *INCLUDES, "-c", str(src), "-o", str(obj)]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"compiling {src} failed:\n{res.stdout}\n{res.stderr}")
+    return obj
+
+
+def build_lib(verbose: bool = False, jobs: int | None = None) -> Path:
+    """Compiles every source under src/ and links hxccl_b200/lib/libhxccl.so."""
+    OBJ.mkdir(parents=True, exist_ok=True)
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    sources = sorted(SRC.rglob("*.cc")) + sorted(SRC.rglob("*.cu"))
+    hdr_time = _newest_header()
+    jobs = jobs or max(1, (os.cpu_count() or 2))
+    with ThreadPoolExecutor(max_workers=jobs) as pool:
+        objs = list(pool.map(lambda s: _compile(s, hdr_time, verbose), sources))
+    if LIB.exists() and all(LIB.stat().st_mtime > o.stat().st_mtime for o in objs):
+        return LIB
+    cmd = [NVCC, "-shared", "-cudart", "static", "-o", str(LIB), *map(str, objs),
+           "-Xcompiler", "-pthread", "-ldl", "-lrt"]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"linking libhxccl.so failed:\n{res.stdout}\n{res.stderr}")
+    return LIB
+
+
+def build_torch_ext(verbose: bool = False) -> Path:
+    """Builds hxccl_b200/_hxccl_c10d.so, the torch.distributed backend, against libhxccl.so."""
+    build_lib(verbose)
+    from torch.utils import cpp_extension  # noqa: PLC0415  (import torch only when asked)
+
+    pkg = Path(__file__).resolve().parent
+    src = pkg / "csrc" / "backend.cpp"
+    out = pkg / "_hxccl_c10d.so"
+    if out.exists() and out.stat().st_mtime > max(src.stat().st_mtime, LIB.stat().st_mtime):
+        return out
+    build_dir = ROOT / "build" / "torch_ext"
+    build_dir.mkdir(parents=True, exist_ok=True)
+    cpp_extension.load(
+        name="_hxccl_c10d",
+        sources=[str(src)],
+        extra_include_paths=[str(ROOT / "include"), str(CUDA_HOME / "include")],
+        extra_cflags=["-O2", "-std=c++17"],
+        extra_ldflags=[f"-L{LIB_DIR}", "-lhxccl", f"-Wl,-rpath,{LIB_DIR}", "-Wl,-rpath,$ORIGIN/lib",
+                       f"-L{CUDA_HOME / 'lib64'}", "-lcudart"],
+        build_directory=str(build_dir),
+        with_cuda=True,
+        is_python_module=False,
+        verbose=verbose,
+    )
+    shutil.copy2(build_dir / "_hxccl_c10d.so", out)
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--torch", action="store_true", help="also build the torch.distributed backend")
+    ap.add_argument("-v", "--verbose", action="store_true")
+    ap.add_argument("-j", "--jobs", type=int, default=None)
+    args = ap.parse_args()
+    print(build_lib(args.verbose, args.jobs))
+    if args.torch:
+        print(build_torch_ext(args.verbose))
+
+
+if __name__ == "__main__":
+    sys.exit(main())

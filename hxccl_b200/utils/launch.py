@@ -1,0 +1,85 @@
+"""Runs a function as N ranks in N fresh processes on this machine (no MPI, no torchrun).
+
+Rank 0 creates the unique id and hands it to the others through a pipe; each rank builds its
+communicator and calls `fn(comm, rank, nranks, *args)`. The parent collects the return values
+(anything picklable) and re-raises the first failure. With `gpus=True` rank r uses CUDA device
+r % device_count and creates its context before the communicator, so the device path starts.
+This is the stand-in for `mpirun -np N` that the reference's tests use (CMakeLists.txt:47-142).
+"""
+from __future__ import annotations
+
+import multiprocessing as mp
+import os
+import traceback
+from typing import Any, Callable, Dict, List, Optional
+
+
+def _child(rank: int, n: int, fn: Callable, args: tuple, uid_recv, uid_send: List, out, env: Dict[str, str],
+           gpus: bool, make_comm: bool) -> None:
+    try:
+        os.environ.update(env)
+        os.environ["HXCCL_RANK"] = str(rank)
+        from hxccl_b200 import comm as hc  # noqa: PLC0415
+
+        if gpus:
+            import torch  # noqa: PLC0415
+
+            torch.cuda.set_device(rank % torch.cuda.device_count())
+            torch.cuda.init()
+            torch.zeros(1, device="cuda")
+        if rank == 0:
+            uid = hc.get_unique_id()
+            for c in uid_send:
+                c.send(uid)
+        else:
+            uid = uid_recv.recv()
+        if make_comm:
+            comm = hc.Communicator.init_rank(uid, n, rank)
+            try:
+                res = fn(comm, rank, n, *args)
+            finally:
+                if comm.handle:
+                    comm.destroy()
+        else:
+            res = fn(uid, rank, n, *args)
+        out.send(("ok", res))
+    except BaseException as e:  # noqa: BLE001
+        out.send(("err", f"rank {rank}: {e!r}\n{traceback.format_exc()}"))
+
+
+def run_ranks(n: int, fn: Callable, *args: Any, env: Optional[Dict[str, str]] = None, gpus: bool = False,
+              timeout: float = 120.0, make_comm: bool = True,
+              rank_env: Optional[Dict[int, Dict[str, str]]] = None) -> List[Any]:
+    """Returns [fn's result on rank 0, ..., on rank n-1]. `fn` must be importable (module level).
+    `rank_env[r]` adds environment variables for rank r only."""
+    ctx = mp.get_context("spawn")
+    uid_pipes = [ctx.Pipe(duplex=False) for _ in range(n - 1)]
+    outs = [ctx.Pipe(duplex=False) for _ in range(n)]
+    procs = []
+    for r in range(n):
+        e = dict(env or {})
+        e.update((rank_env or {}).get(r, {}))
+        p = ctx.Process(target=_child, args=(r, n, fn, args, uid_pipes[r - 1][0] if r else None,
+                                             [w for _, w in uid_pipes] if r == 0 else [], outs[r][1], e,
+                                             gpus, make_comm))
+        p.start()
+        procs.append(p)
+    results: List[Any] = [None] * n
+    errors = []
+    for r in range(n):
+        if outs[r][0].poll(timeout):
+            kind, val = outs[r][0].recv()
+            if kind == "ok":
+                results[r] = val
+            else:
+                errors.append(val)
+        else:
+            errors.append(f"rank {r}: no result within {timeout} s")
+    for p in procs:
+        p.join(5)
+        if p.is_alive():
+            p.kill()  # this exact child, by handle
+            p.join()
+    if errors:
+        raise RuntimeError("\n".join(errors))
+    return results

@@ -1,0 +1,103 @@
+/*
+ * Additions of this library that the hxccl 0.2 header does not have: diagnostics of the device
+ * path, the standalone elementwise kernels, host versions of the element rules (the oracle the
+ * device results are compared with), fault-injection hooks for tests, and a "world on one GPU"
+ * harness that runs the collective kernels for every rank of a small communicator inside one
+ * cooperative launch, for machines with a single GPU.
+ */
+#ifndef HXCCL_EXT_H_
+#define HXCCL_EXT_H_
+
+#include "hxccl.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- diagnostics -------------------------------------------------------------------------- */
+/* kind: "none", "staged", "window" or "window+nvls". variant: what the latest AllReduce used
+ * (1 one-shot, 2 two-shot, 3 NVLS). launches: kernels launched by this communicator so far. */
+hxcclResult_t hxcclCommDeviceInfo(hxcclComm_t comm, char* kind, size_t kind_len, int* variant,
+                                  unsigned long long* launches);
+/* Forces the AllReduce variant of later calls (0 auto, 1 one-shot, 2 two-shot, 3 NVLS), the
+ * exactness mode (1 = floats match the host path bit for bit) and the largest grid (0 keeps it).
+ * Every rank must make the same call. */
+hxcclResult_t hxcclCommTune(hxcclComm_t comm, int variant, int exact, int max_ctas);
+
+/* ---- elementwise kernels on device buffers (any stream, no communicator) ------------------- */
+hxcclResult_t hxcclDevReduce(void* dst, const void* src, size_t count, hxcclDataType_t dt,
+                             hxcclRedOp_t op, hxcclStream_t stream); /* dst = dst op src */
+hxcclResult_t hxcclDevScale(void* dst, const void* src, size_t count, hxcclDataType_t dt,
+                            const void* scalar_host, hxcclStream_t stream);
+hxcclResult_t hxcclDevDivide(void* buf, size_t count, hxcclDataType_t dt, int divisor,
+                             hxcclStream_t stream);
+
+/* ---- the same rules on host buffers ---------------------------------------------------------- */
+hxcclResult_t hxcclHostReduce(void* dst, const void* src, size_t count, hxcclDataType_t dt,
+                              hxcclRedOp_t op);
+hxcclResult_t hxcclHostScale(void* dst, const void* src, size_t count, hxcclDataType_t dt,
+                             const void* scalar);
+hxcclResult_t hxcclHostDivide(void* buf, size_t count, hxcclDataType_t dt, int divisor);
+/* float -> narrow type bits and back (Float16, Bfloat16, Float8e4m3, Float8e5m2) */
+unsigned hxcclHostEncode(hxcclDataType_t dt, float value);
+float hxcclHostDecode(hxcclDataType_t dt, unsigned bits);
+/* the ring block of `count` elements over n ranks: offset and length of block i */
+void hxcclRingBlock(size_t count, int n, int i, size_t* off, size_t* len);
+
+/* ---- fault injection (host side only) ---------------------------------------------------------- */
+/* The (after+1)-th host-path send from now fails with hxcclSystemError; after < 0 disarms. */
+hxcclResult_t hxcclTestFailSends(hxcclComm_t comm, long after);
+/* Closes the control connection to `peer` as if that process had died. */
+hxcclResult_t hxcclTestSeverPeer(hxcclComm_t comm, int peer);
+
+/* ---- a whole communicator on one GPU ------------------------------------------------------------ */
+typedef struct hxcclWorld* hxcclWorld_t;
+/* n ranks (1..16) on the current device, each with a window of window_mb MiB of staging.
+ * wait_ms bounds every device-side wait. */
+hxcclResult_t hxcclWorldCreate(hxcclWorld_t* world, int n, int window_mb, int wait_ms);
+hxcclResult_t hxcclWorldDestroy(hxcclWorld_t world);
+/* variant/exact/max_ctas as in hxcclCommTune */
+hxcclResult_t hxcclWorldTune(hxcclWorld_t world, int variant, int exact, int max_ctas);
+/* send[r] / recv[r] are rank r's device buffers. op is hxcclSum..hxcclAvg; a non-null scalar
+ * (host memory, one element of dt) makes it PreMulSum. order: 0 ring, 1 recursive doubling,
+ * -1 by message size as the API does. */
+hxcclResult_t hxcclWorldAllReduce(hxcclWorld_t world, const void* const* send, void* const* recv,
+                                  size_t count, hxcclDataType_t dt, hxcclRedOp_t op,
+                                  const void* scalar, int order, hxcclStream_t stream);
+hxcclResult_t hxcclWorldReduceScatter(hxcclWorld_t world, const void* const* send,
+                                      void* const* recv, size_t recvcount, hxcclDataType_t dt,
+                                      hxcclRedOp_t op, const void* scalar, hxcclStream_t stream);
+hxcclResult_t hxcclWorldReduce(hxcclWorld_t world, const void* const* send, void* const* recv,
+                               size_t count, hxcclDataType_t dt, hxcclRedOp_t op,
+                               const void* scalar, int root, hxcclStream_t stream);
+hxcclResult_t hxcclWorldAllGather(hxcclWorld_t world, const void* const* send, void* const* recv,
+                                  size_t bytes_per_rank, hxcclStream_t stream);
+hxcclResult_t hxcclWorldBroadcast(hxcclWorld_t world, const void* const* send, void* const* recv,
+                                  size_t bytes, int root, hxcclStream_t stream);
+hxcclResult_t hxcclWorldGather(hxcclWorld_t world, const void* const* send, void* const* recv,
+                               size_t bytes_per_rank, int root, hxcclStream_t stream);
+hxcclResult_t hxcclWorldScatter(hxcclWorld_t world, const void* const* send, void* const* recv,
+                                size_t bytes_per_rank, int root, hxcclStream_t stream);
+/* bytes[r*n + j]: bytes rank r sends to rank j; soff / roff likewise (byte offsets; roff[r*n+i]
+ * is where rank r puts what rank i sent). */
+hxcclResult_t hxcclWorldAllToAllv(hxcclWorld_t world, const void* const* send, void* const* recv,
+                                  const size_t* bytes, const size_t* soff, const size_t* roff,
+                                  hxcclStream_t stream);
+/* nops transfers: transfer k sends sbytes[k] bytes from src[k] on rank from[k] into dst[k]
+ * (room rbytes[k]) on rank to[k]; all in one group. */
+hxcclResult_t hxcclWorldSendRecv(hxcclWorld_t world, int nops, const int* from, const int* to,
+                                 const void* const* src, const size_t* sbytes, void* const* dst,
+                                 const size_t* rbytes, hxcclStream_t stream);
+/* status words of rank r after the stream is synchronized: sticky (0 = fine; code in the top
+ * byte: 1 timeout, 2 remote) and soft (3 in the top byte = a receive was truncated; cleared) */
+hxcclResult_t hxcclWorldStatus(hxcclWorld_t world, int rank, unsigned long long* sticky,
+                               unsigned long long* soft);
+hxcclResult_t hxcclWorldInfo(hxcclWorld_t world, int* variant, unsigned long long* launches);
+/* Test hook: from now on rank r's stores and flags go to a private dummy window, so that its
+ * peers wait for flags that nothing sets; their bounded waits then run out and report it. */
+hxcclResult_t hxcclWorldMute(hxcclWorld_t world, int rank);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HXCCL_EXT_H_ */

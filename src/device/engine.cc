@@ -1,0 +1,202 @@
+#include "device/engine.h"
+
+#include <algorithm>
+#include <cstring>
+
+#include "math/dtypes.h"
+
+namespace hx {
+
+Engine::~Engine() {
+  if (dev_args_) cudaFree(dev_args_);
+}
+
+LaunchShape Engine::shape(const Geometry& g) const {
+  return LaunchShape{g.ctas, g.threads, world() ? int(views.size()) : 0};
+}
+
+// Production: the single argument block is passed by value. World: the blocks of all ranks go
+// to device memory first (stream-ordered copy from the caller's vector, which outlives it
+// because the copy of pageable memory returns only after the source was read).
+template <typename Args>
+const Args* Engine::stage(const std::vector<Args>& args, cudaStream_t st, cudaError_t* rc) {
+  *rc = cudaSuccess;
+  if (!world()) return args.data();
+  const size_t bytes = args.size() * sizeof(Args);
+  if (bytes > dev_args_bytes_) {
+    if (dev_args_) cudaFree(dev_args_);
+    dev_args_ = nullptr;
+    if ((*rc = cudaMalloc(&dev_args_, bytes)) != cudaSuccess) return nullptr;
+    dev_args_bytes_ = bytes;
+  }
+  // earlier launches may still read the buffer
+  if ((*rc = cudaStreamSynchronize(st)) != cudaSuccess) return nullptr;
+  *rc = cudaMemcpyAsync(dev_args_, args.data(), bytes, cudaMemcpyHostToDevice, st);
+  return static_cast<const Args*>(dev_args_);
+}
+
+cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpPlan& plan,
+                              int order, cudaStream_t st) {
+  const size_t bytes = count * dtype_size(dt);
+  int var = choose_variant(bytes, dt, plan, n(), tune, forced_variant);
+  // recursive doubling gives every rank its own operand order; only the variant in which each
+  // rank folds for itself can replay that
+  if (order == kOrderDoubling && tune.exact && !is_integer(dt)) var = kVarOneShot;
+  if (world() && var == kVarNvls) var = kVarTwoShot;
+  last_variant = var;
+  cudaError_t rc;
+  ++launches;
+  if (var == kVarOneShot) {
+    const Geometry g = plan_xchg(bytes, n(), views[0].half_bytes, tune);
+    std::vector<XchgArgs> args(views.size());
+    for (size_t r = 0; r < views.size(); ++r)
+      build_allreduce_oneshot(&args[r], views[r], epoch, g, b[r].send, b[r].recv, count, dt, plan, order);
+    epoch += g.steps;
+    const XchgArgs* a = stage(args, st, &rc);
+    return rc != cudaSuccess ? rc : launch_xchg_fold(dt, a, shape(g), st);
+  }
+  const Geometry g = plan_sliced(bytes, n(), views[0].half_bytes, tune);
+  if (var == kVarNvls) {
+    std::vector<NvlsArgs> args(1);
+    build_allreduce_nvls(&args[0], views[0], epoch, g, b[0].send, b[0].recv, count, dt, plan);
+    epoch += g.steps;
+    return launch_nvls(args.data(), shape(g), st);
+  }
+  std::vector<TwoShotArgs> args(views.size());
+  for (size_t r = 0; r < views.size(); ++r)
+    build_allreduce_twoshot(&args[r], views[r], epoch, g, b[r].send, b[r].recv, count, dt, plan,
+                            order, tune.nvls && tune.nvls_gather && bytes % 16 == 0);
+  epoch += g.steps;
+  const TwoShotArgs* a = stage(args, st, &rc);
+  return rc != cudaSuccess ? rc : launch_twoshot(dt, a, shape(g), st);
+}
+
+cudaError_t Engine::reducescatter(const RankBufs* b, size_t per, int dt, const OpPlan& plan,
+                                  cudaStream_t st) {
+  const Geometry g = plan_xchg(per * dtype_size(dt), n(), views[0].half_bytes, tune);
+  std::vector<XchgArgs> args(views.size());
+  for (size_t r = 0; r < views.size(); ++r)
+    build_reducescatter(&args[r], views[r], epoch, g, b[r].send, b[r].recv, per, dt, plan);
+  epoch += g.steps;
+  ++launches;
+  cudaError_t rc;
+  const XchgArgs* a = stage(args, st, &rc);
+  return rc != cudaSuccess ? rc : launch_xchg_fold(dt, a, shape(g), st);
+}
+
+cudaError_t Engine::reduce(const RankBufs* b, size_t count, int dt, const OpPlan& plan, int root,
+                           cudaStream_t st) {
+  const Geometry g = plan_xchg(count * dtype_size(dt), n(), views[0].half_bytes, tune);
+  std::vector<XchgArgs> args(views.size());
+  for (size_t r = 0; r < views.size(); ++r)
+    build_reduce(&args[r], views[r], epoch, g, b[r].send, b[r].recv, count, dt, plan, root);
+  epoch += g.steps;
+  ++launches;
+  cudaError_t rc;
+  const XchgArgs* a = stage(args, st, &rc);
+  return rc != cudaSuccess ? rc : launch_xchg_fold(dt, a, shape(g), st);
+}
+
+#define HX_COPY_COLLECTIVE(MAXPAIR, BUILD)                                  \
+  const Geometry g = plan_xchg(MAXPAIR, n(), views[0].half_bytes, tune);    \
+  std::vector<XchgArgs> args(views.size());                                 \
+  for (size_t r = 0; r < views.size(); ++r) { BUILD; }                      \
+  epoch += g.steps;                                                         \
+  ++launches;                                                               \
+  cudaError_t rc;                                                           \
+  const XchgArgs* a = stage(args, st, &rc);                                 \
+  return rc != cudaSuccess ? rc : launch_xchg_copy(a, shape(g), st);
+
+cudaError_t Engine::allgather(const RankBufs* b, size_t block, cudaStream_t st) {
+  HX_COPY_COLLECTIVE(block, build_allgather(&args[r], views[r], epoch, g, b[r].send, b[r].recv, block))
+}
+cudaError_t Engine::broadcast(const RankBufs* b, size_t bytes, int root, cudaStream_t st) {
+  HX_COPY_COLLECTIVE(bytes, build_broadcast(&args[r], views[r], epoch, g, b[r].send, b[r].recv, bytes, root))
+}
+cudaError_t Engine::gather(const RankBufs* b, size_t block, int root, cudaStream_t st) {
+  HX_COPY_COLLECTIVE(block, build_gather(&args[r], views[r], epoch, g, b[r].send, b[r].recv, block, root))
+}
+cudaError_t Engine::scatter(const RankBufs* b, size_t block, int root, cudaStream_t st) {
+  HX_COPY_COLLECTIVE(block, build_scatter(&args[r], views[r], epoch, g, b[r].send, b[r].recv, block, root))
+}
+cudaError_t Engine::alltoallv(const RankV* v, size_t max_pair, cudaStream_t st) {
+  HX_COPY_COLLECTIVE(max_pair, build_alltoallv(&args[r], views[r], epoch, g, v[r].send, v[r].sbytes,
+                                               v[r].soff, v[r].recv, v[r].rbytes, v[r].roff))
+}
+
+// Send/Recv: operations toward one peer in one direction share a lane and keep their order.
+// A rank's transfers to itself are paired here and become plain device copies.
+cudaError_t Engine::p2p(const RankP2p* ops, cudaStream_t st) {
+  const size_t nr = views.size();
+  std::vector<std::vector<P2pOp>> left(nr);
+  for (size_t r = 0; r < nr; ++r) {
+    const int me = views[r].rank;
+    std::vector<P2pOp> sends, recvs;
+    for (const P2pOp& o : ops[r].ops) {
+      if (o.peer != me)
+        left[r].push_back(o);
+      else
+        (o.is_send ? sends : recvs).push_back(o);
+    }
+    if (sends.size() != recvs.size()) {
+      error = "a Send to the calling rank needs a matching Recv in the same group";
+      return cudaErrorInvalidValue;
+    }
+    for (size_t k = 0; k < sends.size(); ++k) {
+      const size_t nbytes = std::min(sends[k].bytes, recvs[k].bytes);
+      if (nbytes && sends[k].buf != recvs[k].buf)
+        if (cudaError_t e = cudaMemcpyAsync(recvs[k].buf, sends[k].buf, nbytes, cudaMemcpyDeviceToDevice, st))
+          return e;
+      if (sends[k].bytes > recvs[k].bytes) {
+        error = "message truncated: the receive buffer is smaller than the message";
+        return cudaErrorInvalidValue;
+      }
+    }
+  }
+  for (;;) {  // a lane takes kMaxLaneOps operations per launch; more go into another round
+    bool any = false;
+    std::vector<P2pArgs> args(nr);
+    int max_lanes = 0;
+    for (size_t r = 0; r < nr; ++r) {
+      P2pArgs& a = args[r];
+      std::memset(&a, 0, sizeof a);
+      a.w = views[r];
+      std::vector<P2pOp> rest;
+      for (const P2pOp& o : left[r]) {
+        int lane = -1;
+        for (int k = 0; k < a.nlanes; ++k)
+          if (a.lanes[k].peer == o.peer && a.lanes[k].is_send == int(o.is_send)) lane = k;
+        if (lane < 0 && a.nlanes < kMaxLanes) {
+          lane = a.nlanes++;
+          a.lanes[lane].peer = o.peer;
+          a.lanes[lane].is_send = o.is_send;
+          a.lanes[lane].nops = 0;
+        }
+        // an operation that does not fit, or that follows one of its lane that did not fit,
+        // waits for the next round so the lane's order holds
+        const bool blocked = std::any_of(rest.begin(), rest.end(), [&](const P2pOp& q) {
+          return q.peer == o.peer && q.is_send == o.is_send;
+        });
+        if (lane < 0 || blocked || a.lanes[lane].nops == kMaxLaneOps) {
+          rest.push_back(o);
+          continue;
+        }
+        a.lanes[lane].ops[a.lanes[lane].nops++] = P2pLaneOp{static_cast<char*>(o.buf), o.bytes};
+      }
+      left[r].swap(rest);
+      int used = 0;
+      for (int k = 0; k < a.nlanes; ++k) used += a.lanes[k].nops > 0;
+      any = any || used > 0;
+      max_lanes = std::max(max_lanes, a.nlanes);
+    }
+    if (!any) return cudaSuccess;
+    ++launches;
+    cudaError_t rc;
+    const P2pArgs* a = stage(args, st, &rc);
+    if (rc != cudaSuccess) return rc;
+    rc = launch_p2p(a, LaunchShape{max_lanes * kP2pWorkers, 256, world() ? int(nr) : 0}, st);
+    if (rc != cudaSuccess) return rc;
+  }
+}
+
+}  // namespace hx

@@ -1,0 +1,85 @@
+"""Host path across real processes: AllReduce for all 12 element types, five operators, both
+algorithms, compared bit for bit with the in-process oracle (every rank's inputs are a
+function of its rank, so each test recomputes them: the reference's technique in
+tests/test_dtypes.cc:51-88), plus the exact traffic counters (tests/test_allreduce.cc:57-86)."""
+import os
+
+import numpy as np
+import pytest
+
+from hxccl_b200 import _lib as L
+from hxccl_b200.ops import oracle
+from hxccl_b200.utils import run_ranks
+
+
+def inputs_for(n, count, dt, seed):
+    es = L.DTYPE_SIZE[dt]
+    return [np.random.default_rng(seed * 1000 + r).integers(0, 256, count * es, dtype=np.uint8)
+            .view(oracle.raw_dtype(dt)) for r in range(n)]
+
+
+def _body(comm, rank, n, cases):
+    out = []
+    for (dt, op, count, algo, seed) in cases:
+        if algo:
+            os.environ["HXCCL_ALGO"] = algo
+        else:
+            os.environ.pop("HXCCL_ALGO", None)
+        x = inputs_for(n, count, dt, seed)[rank]
+        y = np.zeros_like(x)
+        comm.reset_stats()
+        comm.all_reduce(x, y, op=op, count=count, dtype=dt)
+        out.append((y, comm.stats()))
+    return out
+
+
+@pytest.mark.parametrize("n", [1, 2, 3, 4, 5, 8])
+def test_allreduce_matches_oracle(n):
+    cases = []
+    for dt in range(12):
+        for op in (L.SUM, L.PROD, L.MAX, L.MIN, L.AVG):
+            for count, algo in ((0, None), (1, "ring"), (7, "rd"), (1000, "ring"), (1000, "rd"), (4099, None)):
+                cases.append((dt, op, count, algo, len(cases)))
+    res = run_ranks(n, _body, cases)
+    for k, (dt, op, count, algo, seed) in enumerate(cases):
+        order = {"ring": 0, "rd": 1, None: -1}[algo]
+        want = oracle.allreduce(inputs_for(n, count, dt, seed), dt, op, order=order)
+        for r in range(n):
+            assert np.array_equal(res[r][k][0], want[r]), (n, dt, op, count, algo, r)
+
+
+def _traffic_body(comm, rank, n):
+    out = {}
+    x = np.ones(1000, dtype=np.float32)
+    for algo in ("ring", "rd"):
+        os.environ["HXCCL_ALGO"] = algo
+        comm.reset_stats()
+        comm.all_reduce(x.copy(), op=L.SUM)
+        out[algo] = comm.stats()
+    os.environ.pop("HXCCL_ALGO")
+    comm.reset_stats()
+    comm.all_reduce(np.ones(3, dtype=np.float64), op=L.SUM)  # fewer elements than ranks at n > 3
+    out["tiny"] = comm.stats()
+    return out
+
+
+@pytest.mark.parametrize("n", [2, 4, 5])
+def test_traffic_counters(n):
+    res = run_ranks(n, _traffic_body)
+    total = 1000 * 4
+    for r in range(n):
+        # ring: 2(n-1) messages that together carry every block but one, twice
+        blocks = [oracle.ring_block(1000, n, i)[1] * 4 for i in range(n)]
+        rs = sum(blocks[(r - h) % n] for h in range(n - 1))
+        ag = sum(blocks[(r + 1 - h) % n] for h in range(n - 1))
+        assert res[r]["ring"] == (rs + ag, 2 * (n - 1))
+        p = 1 << (n.bit_length() - 1)
+        spare = n - p
+        levels = p.bit_length() - 1
+        if r < 2 * spare and r % 2 == 0:
+            assert res[r]["rd"] == (total, 1)
+        elif r < 2 * spare:
+            assert res[r]["rd"] == (total * (levels + 1), levels + 1)
+        else:
+            assert res[r]["rd"] == (total * levels, levels)
+        assert res[r]["tiny"][1] > 0
