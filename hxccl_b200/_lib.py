@@ -121,6 +121,8 @@ def lib() -> C.CDLL:
     L.hxcclGetErrorString.restype = C.c_char_p
     L.hxcclGetLastError.argtypes = [vp]
     L.hxcclGetLastError.restype = C.c_char_p
+    L.hxcclWorldLastError.argtypes = []
+    L.hxcclWorldLastError.restype = C.c_char_p
     L.hxcclHostEncode.argtypes = [i, C.c_float]
     L.hxcclHostEncode.restype = C.c_uint
     L.hxcclHostDecode.argtypes = [i, C.c_uint]

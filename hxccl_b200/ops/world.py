@@ -51,7 +51,7 @@ class World:
 
     def _ok(self, rc: int, what: str) -> None:
         if rc:
-            raise HxcclError(rc, what)
+            raise HxcclError(rc, what, L.lib().hxcclWorldLastError().decode())
 
     def tune(self, variant: int = 0, exact: bool = True, max_ctas: int = 0) -> None:
         self._ok(L.lib().hxcclWorldTune(self._h, variant, int(exact), max_ctas), "hxcclWorldTune")

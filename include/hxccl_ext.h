@@ -93,6 +93,8 @@ hxcclResult_t hxcclWorldSendRecv(hxcclWorld_t world, int nops, const int* from, 
 hxcclResult_t hxcclWorldStatus(hxcclWorld_t world, int rank, unsigned long long* sticky,
                                unsigned long long* soft);
 hxcclResult_t hxcclWorldInfo(hxcclWorld_t world, int* variant, unsigned long long* launches);
+/* text of the CUDA error behind the latest hxcclUnhandledCudaError of a world call */
+const char* hxcclWorldLastError(void);
 /* Test hook: from now on rank r's stores and flags go to a private dummy window, so that its
  * peers wait for flags that nothing sets; their bounded waits then run out and report it. */
 hxcclResult_t hxcclWorldMute(hxcclWorld_t world, int rank);

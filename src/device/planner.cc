@@ -150,10 +150,7 @@ void build_reduce(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry&
     a->send_bytes[j] = (w.rank != root && j == root) ? bytes : 0;
   }
   a->push_scaled = plan.premul;
-  if (w.rank != root) return;  // only the root folds
-  a->fold_dst = static_cast<char*>(recv);
-  a->own_ptr = static_cast<const char*>(send);
-  a->fold_bytes = bytes;
+  // the other ranks need the operator too: their pushes carry the scaled input
   if (bytes < kTreeMaxBytes) {
     a->fold = make_fold(plan, kFoldTree);
     a->fold.root = root;
@@ -162,6 +159,10 @@ void build_reduce(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry&
     a->fold.start = (root + w.n - 1) % w.n;
     a->fold.dir = -1;
   }
+  if (w.rank != root) return;  // only the root folds
+  a->fold_dst = static_cast<char*>(recv);
+  a->own_ptr = static_cast<const char*>(send);
+  a->fold_bytes = bytes;
 }
 
 void build_allgather(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include <cstring>
+#include <string>
 #include <vector>
 
 #include "device/engine.h"
@@ -49,12 +50,22 @@ bool make_plan(int n, int dt, int op, const void* scalar, OpPlan* p) {
   return true;
 }
 
+// CTAs the whole world may use together. Kept well below the co-residency bound of the
+// heaviest kernel: a cooperative launch is refused outright when it does not fit, and other
+// work on the device can take SMs away.
+int world_cta_budget() { return std::max(1, max_resident_ctas(512) * 3 / 4); }
+
 std::vector<RankBufs> bufs(hxcclWorld* w, const void* const* send, void* const* recv) {
   std::vector<RankBufs> b(w->n);
   for (int r = 0; r < w->n; ++r) b[r] = RankBufs{send ? send[r] : nullptr, recv ? recv[r] : nullptr};
   return b;
 }
-hxcclResult_t rc_of(cudaError_t e) { return e == cudaSuccess ? hxcclSuccess : hxcclUnhandledCudaError; }
+std::string g_last_error;
+hxcclResult_t rc_of(cudaError_t e) {
+  if (e == cudaSuccess) return hxcclSuccess;
+  g_last_error = cudaGetErrorString(e);
+  return hxcclUnhandledCudaError;
+}
 }  // namespace
 
 extern "C" {
@@ -92,7 +103,7 @@ hxcclResult_t hxcclWorldCreate(hxcclWorld_t* out, int n, int window_mb, int wait
     w->eng.views.push_back(v);
   }
   // the whole world must be co-resident: a cooperative launch refuses anything larger
-  w->eng.tune.max_ctas = std::max(1, std::min(64, max_resident_ctas(512) / n));
+  w->eng.tune.max_ctas = std::max(1, std::min(64, world_cta_budget() / n));
   *out = w;
   return cudaDeviceSynchronize() == cudaSuccess ? hxcclSuccess : hxcclUnhandledCudaError;
 }
@@ -112,7 +123,7 @@ hxcclResult_t hxcclWorldTune(hxcclWorld_t w, int variant, int exact, int max_cta
   if (!w) return hxcclInvalidArgument;
   w->eng.forced_variant = variant;
   w->eng.tune.exact = exact != 0;
-  if (max_ctas > 0) w->eng.tune.max_ctas = std::min(max_ctas, std::max(1, max_resident_ctas(512) / w->n));
+  if (max_ctas > 0) w->eng.tune.max_ctas = std::min(max_ctas, std::max(1, world_cta_budget() / w->n));
   return hxcclSuccess;
 }
 
@@ -226,6 +237,8 @@ hxcclResult_t hxcclWorldInfo(hxcclWorld_t w, int* variant, unsigned long long* l
   if (launches) *launches = w->eng.launches;
   return hxcclSuccess;
 }
+
+const char* hxcclWorldLastError(void) { return g_last_error.c_str(); }
 
 hxcclResult_t hxcclWorldMute(hxcclWorld_t w, int rank) {
   if (!w || rank < 0 || rank >= w->n) return hxcclInvalidArgument;

@@ -130,15 +130,13 @@ cudaError_t launch_nvls(const NvlsArgs* args, LaunchShape s, cudaStream_t st) {
 }
 
 int max_resident_ctas(int threads) {
-  int dev = 0, sms = 0, per_sm = 0;
+  // The collective kernels differ in register use from type to type; every one of them fits
+  // one 512-thread CTA per SM (__launch_bounds__(512)), so that is what is promised.
+  (void)threads;
+  int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 1;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  // the double-precision two-shot kernel is the heaviest in registers
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_twoshot<double>, threads, 0) !=
-          cudaSuccess ||
-      per_sm < 1)
-    per_sm = 1;
-  return sms * per_sm;
+  return sms > 0 ? sms : 1;
 }
 
 }  // namespace hx
