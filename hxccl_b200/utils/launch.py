@@ -17,8 +17,16 @@ from typing import Any, Callable, Dict, List, Optional
 def _child(rank: int, n: int, fn: Callable, args: tuple, uid_recv, uid_send: List, out, env: Dict[str, str],
            gpus: bool, make_comm: bool) -> None:
     try:
+        import faulthandler  # noqa: PLC0415
+
+        faulthandler.enable()
         os.environ.update(env)
         os.environ["HXCCL_RANK"] = str(rank)
+        log_dir = os.environ.get("HXCCL_RANK_LOG_DIR")
+        if log_dir:  # per-rank stderr (native code included) for post-mortems
+            os.makedirs(log_dir, exist_ok=True)
+            fd = os.open(os.path.join(log_dir, f"rank{rank}.log"), os.O_WRONLY | os.O_CREAT | os.O_APPEND)
+            os.dup2(fd, 2)
         from hxccl_b200 import comm as hc  # noqa: PLC0415
 
         if gpus:
@@ -66,17 +74,29 @@ def run_ranks(n: int, fn: Callable, *args: Any, env: Optional[Dict[str, str]] = 
         procs.append(p)
     results: List[Any] = [None] * n
     errors = []
-    for r in range(n):
-        if outs[r][0].poll(timeout):
-            kind, val = outs[r][0].recv()
-            if kind == "ok":
-                results[r] = val
-            else:
-                errors.append(val)
-        else:
+    import time  # noqa: PLC0415
+
+    deadline = time.monotonic() + timeout
+    pending = set(range(n))
+    while pending:
+        for r in sorted(pending):
+            if outs[r][0].poll(0.05):
+                kind, val = outs[r][0].recv()
+                if kind == "ok":
+                    results[r] = val
+                else:
+                    errors.append(val)
+                pending.discard(r)
+            elif not procs[r].is_alive() and not outs[r][0].poll(0):
+                errors.append(f"rank {r}: process ended with exit code {procs[r].exitcode} and no result")
+                pending.discard(r)
+        if errors or time.monotonic() > deadline:
+            break  # one rank failed: the others would only wait for it
+    for r in sorted(pending):
+        if time.monotonic() > deadline:
             errors.append(f"rank {r}: no result within {timeout} s")
     for p in procs:
-        p.join(5)
+        p.join(0.5 if errors else 5)
         if p.is_alive():
             p.kill()  # this exact child, by handle
             p.join()
