@@ -90,11 +90,13 @@ def run_ranks(n: int, fn: Callable, *args: Any, env: Optional[Dict[str, str]] = 
             elif not procs[r].is_alive() and not outs[r][0].poll(0):
                 errors.append(f"rank {r}: process ended with exit code {procs[r].exitcode} and no result")
                 pending.discard(r)
-        if errors or time.monotonic() > deadline:
-            break  # one rank failed: the others would only wait for it
-    for r in sorted(pending):
+        if errors:  # one rank failed: give the others a moment to report, then stop waiting
+            deadline = min(deadline, time.monotonic() + 3.0)
+            errors_seen = True
         if time.monotonic() > deadline:
-            errors.append(f"rank {r}: no result within {timeout} s")
+            break
+    for r in sorted(pending):
+        errors.append(f"rank {r}: no result" + ("" if errors else f" within {timeout} s"))
     for p in procs:
         p.join(0.5 if errors else 5)
         if p.is_alive():

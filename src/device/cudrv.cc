@@ -2,6 +2,8 @@
 
 #include <dlfcn.h>
 
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 namespace hx {
@@ -9,11 +11,14 @@ namespace {
 
 using GetProc = CUresult (*)(const char*, void**, int, cuuint64_t, CUdriverProcAddressQueryResult*);
 
+// The multicast entry points arrived with CUDA 12.1; ask for the 12.4 view of the API.
+constexpr int kApiVersion = 12040;
+
 template <typename F>
 bool bind(GetProc gp, const char* name, F* slot, std::string* why) {
   void* fn = nullptr;
   CUdriverProcAddressQueryResult q;
-  if (gp(name, &fn, 12000, CU_GET_PROC_ADDRESS_DEFAULT, &q) != CUDA_SUCCESS || !fn) {
+  if (gp(name, &fn, kApiVersion, CU_GET_PROC_ADDRESS_DEFAULT, &q) != CUDA_SUCCESS || !fn) {
     *why = std::string("the CUDA driver has no ") + name;
     return false;
   }
@@ -77,7 +82,13 @@ std::string CuDriver::err(CUresult r) const {
 }
 
 const CuDriver& cu() {
-  static const CuDriver d = load();
+  static const CuDriver d = [] {
+    CuDriver x = load();
+    if (!x.ok && std::getenv("HXCCL_DEBUG"))
+      std::fprintf(stderr, "hxccl: CUDA driver unavailable (%s); every buffer is treated as host memory\n",
+                   x.why.c_str());
+    return x;
+  }();
   return d;
 }
 

@@ -51,7 +51,7 @@ def test_allreduce_exact(n):
         for op in (L.SUM, L.MAX, L.AVG):
             for count, variant in ((1, 0), (4099, 1), (4099, 2), ((2 << 20) // L.DTYPE_SIZE[dt] + 3, 0)):
                 cases.append((dt, op, count, variant, len(cases)))
-    res = run_ranks(n, _allreduce_body, cases, gpus=True, timeout=300)
+    res = run_ranks(n, _allreduce_body, cases, gpus=True, timeout=120)
     assert res[0][0]["kind"].startswith("window"), res[0][0]
     for k, (dt, op, count, variant, seed) in enumerate(cases):
         want = oracle.allreduce(inputs_for(n, count, dt, seed, tame=count > 100000), dt, op)
@@ -89,7 +89,7 @@ def _nvls_body(comm, rank, n):
 def test_allreduce_nvls(n):
     import torch
 
-    res = run_ranks(n, _nvls_body, gpus=True, timeout=300)
+    res = run_ranks(n, _nvls_body, gpus=True, timeout=120)
     if res[0][1] is None:
         pytest.skip("no NVSwitch multicast on this node: " + res[0][0]["kind"])
     count = 1 << 20
@@ -142,7 +142,7 @@ def _collectives_body(comm, rank, n):
 @needs2
 @pytest.mark.parametrize("n", WORLDS)
 def test_other_collectives(n):
-    res = run_ranks(n, _collectives_body, gpus=True, timeout=300)
+    res = run_ranks(n, _collectives_body, gpus=True, timeout=120)
     want_rs = oracle.reducescatter(inputs_for(n, 1000 * n, L.FLOAT32, 5), L.FLOAT32, L.SUM)
     for r in range(n):
         assert res[r]["ag"] and res[r]["bc"] and res[r]["shift"] and res[r]["err"] == 0, (r, res[r])
