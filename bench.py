@@ -1,0 +1,247 @@
+#!/usr/bin/env python
+"""Headline benchmark: AllReduce bus bandwidth (and small-message latency) on N B200s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--bytes B] [--dtype float32]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One step is one out-of-place fp32 sum AllReduce of `--bytes` per rank (default 256 MiB, larger
+than the 126 MB L2, so consecutive steps do not hit in cache). K steps are timed with CUDA
+events on the launching stream between barriers, the maximum over ranks is taken, and rank 0
+prints one JSON line. `value` is the bus bandwidth in GB/s by the nccl-tests convention,
+algbw * 2(N-1)/N; with one GPU that factor is zero, so there `value` is the algorithm bandwidth
+of the local AllReduce (a copy) and `config.note` says so. The `e2e` figure repeats the
+measurement through the public Python API with the input copied from pinned host memory and a
+slice of the result read back every step. `--impl reference` runs the unmodified reference
+library instead when it could be built (see baseline/README.md), else reports why not.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--bytes", type=int, default=256 << 20)
+    ap.add_argument("--dtype", default="float32")
+    ap.add_argument("--impl", default="hxccl", choices=["hxccl", "reference", "nccl"])
+    ap.add_argument("--exact", type=int, default=1, help="1: bit-exact reduction order; 0: NVLS fast mode")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the small size sweep in the extras")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of this rank's GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def reference_unavailable(reason: str) -> None:
+    print(json.dumps({"impl": "reference", "unavailable": reason}))
+
+
+def main() -> int:
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        try:
+            import ref_arm  # noqa: PLC0415
+        except Exception as e:  # noqa: BLE001
+            if rank == 0:
+                reference_unavailable(f"reference arm could not be loaded: {e!r}"[:200])
+            return 0
+        return ref_arm.run(args, rank, world, local)
+
+    import torch  # noqa: PLC0415
+    import torch.distributed as dist  # noqa: PLC0415
+
+    torch.cuda.set_device(local)
+    torch.zeros(1, device="cuda")
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    tdt = getattr(torch, args.dtype)
+    es = torch.empty(0, dtype=tdt).element_size()
+    count = args.bytes // es
+    nbytes = count * es
+
+    if args.impl == "nccl":
+        comm = None
+        os.environ.setdefault("MASTER_PORT", "29533")
+        nccl_pg = dist.new_group(backend="nccl") if world > 1 else None
+
+        def allreduce(src, dst):
+            if nccl_pg is not None:
+                dst.copy_(src)
+                dist.all_reduce(dst, group=nccl_pg)
+            else:
+                dst.copy_(src)
+        launches_of = lambda: 0  # noqa: E731
+    else:
+        import hxccl_b200 as hx  # noqa: PLC0415
+
+        uid = [hx.get_unique_id() if rank == 0 else None]
+        if world > 1:
+            dist.broadcast_object_list(uid, src=0)
+        comm = hx.Communicator.init_rank(uid[0], world, rank)
+        comm.tune(variant=0, exact=bool(args.exact))
+        info = comm.device_info()
+        if info["kind"] == "none":
+            raise RuntimeError("the hxccl device path did not start (libhxccl.so without a GPU?)")
+
+        def allreduce(src, dst):
+            comm.all_reduce(src, dst, op=hx.SUM)
+        launches_of = lambda: comm.device_info()["launches"]  # noqa: E731
+
+    g = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    src = torch.rand(count, generator=g, device="cuda", dtype=torch.float32).mul_(2).sub_(1).to(tdt)
+    dst = torch.empty_like(src)
+    stream = torch.cuda.current_stream()
+
+    def timed(fn, steps: int, warmup: int) -> float:
+        """ms per step, device-timed, max over ranks."""
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1) / steps)
+
+    # ---- headline: kernel-only -------------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        allreduce(src, dst)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    l0 = launches_of()
+    ms = timed(lambda: allreduce(src, dst), args.steps, 0)
+    launches = launches_of() - l0
+    clocks = sampler.stop() if sampler else None
+    factor = 2.0 * (world - 1) / world if world > 1 else 1.0
+    algbw = nbytes / (ms * 1e-3) / 1e9
+    value = algbw * factor
+
+    # ---- end to end: pinned host -> device, AllReduce, slice of the result back -------------
+    host_in = torch.empty(count, dtype=tdt).pin_memory()
+    host_in.copy_(src.cpu())
+    host_out = torch.empty(4096 // es, dtype=tdt).pin_memory()
+    dev_in = torch.empty_like(src)
+
+    def e2e_step():
+        dev_in.copy_(host_in, non_blocking=True)
+        allreduce(dev_in, dst)
+        host_out.copy_(dst[: host_out.numel()], non_blocking=True)
+        stream.synchronize()  # the caller reads the result every step
+
+    e2e_ms = timed(e2e_step, max(3, args.steps // 2), 3)
+    e2e_value = nbytes / (e2e_ms * 1e-3) / 1e9 * factor
+
+    # ---- extras: latency and a short sweep ------------------------------------------------------
+    sweep = []
+    if not args.no_sweep:
+        for sz in (8, 1024, 64 << 10, 1 << 20, 16 << 20, 64 << 20):
+            n_el = max(1, sz // es)
+            a, b = src[:n_el], dst[:n_el]
+            t = timed(lambda: allreduce(a, b), 50 if sz <= (1 << 20) else 20, 5)
+            sweep.append({"bytes": n_el * es, "us": round(t * 1e3, 2),
+                          "busbw_GBps": round(n_el * es / (t * 1e-3) / 1e9 * factor, 2)})
+
+    if comm is not None:
+        variant = comm.device_info()
+        err = comm.async_error()
+        comm.destroy()
+    else:
+        variant, err = {"kind": "nccl"}, 0
+    if world > 1:
+        dist.destroy_process_group()
+    if rank == 0:
+        line = {
+            "metric": "allreduce_busbw_GBps", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.dtype,
+            "data": "synthetic U(-1,1), seed 1234+rank", "impl": args.impl,
+            "config": {"model": "AllReduce sum, out of place", "global_batch": nbytes * world, "seq_len": count,
+                       "parallelism": f"{world} ranks, one per GPU", "bytes_per_rank": nbytes,
+                       "l2_policy": "message larger than L2 (126 MB): no flush needed",
+                       "exact_order": bool(args.exact), "device_path": variant,
+                       "note": ("one GPU: value is algorithm bandwidth of the local AllReduce (bus factor is 0)"
+                                if world == 1 else "value = algbw * 2(N-1)/N (nccl-tests bus bandwidth)")},
+            "algbw_GBps": round(algbw, 2),
+            "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "ms_per_step": round(e2e_ms, 4),
+                    "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": host_out.numel() * es},
+            "gpu_launches": int(launches), "clocks": clocks, "sweep": sweep, "async_error": err,
+        }
+        print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
