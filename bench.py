@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--bytes B] [--dtype float32]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-One step is one out-of-place fp32 sum AllReduce of `--bytes` per rank (default 256 MiB, larger
+One step is one in-place fp32 sum AllReduce of `--bytes` per rank (default 256 MiB, larger
 than the 126 MB L2, so consecutive steps do not hit in cache). K steps are timed with CUDA
 events on the launching stream between barriers, the maximum over ranks is taken, and rank 0
 prints one JSON line. `value` is the bus bandwidth in GB/s by the nccl-tests convention,
@@ -53,7 +53,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             pass
 
@@ -136,11 +136,11 @@ def main() -> int:
         nccl_pg = dist.new_group(backend="nccl") if world > 1 else None
 
         def allreduce(src, dst):
+            # torch's all_reduce is in place; the timed loops below pass src is dst
+            if src is not dst:
+                dst.copy_(src)
             if nccl_pg is not None:
-                dst.copy_(src)
                 dist.all_reduce(dst, group=nccl_pg)
-            else:
-                dst.copy_(src)
         launches_of = lambda: 0  # noqa: E731
     else:
         import hxccl_b200 as hx  # noqa: PLC0415
@@ -177,14 +177,15 @@ def main() -> int:
         return max_over_ranks(e0.elapsed_time(e1) / steps)
 
     # ---- headline: kernel-only -------------------------------------------------------------
+    sampler = ClockSampler(local) if rank == 0 else None
     for _ in range(max(args.warmup, 3)):
         allreduce(src, dst)
     barrier()
-    sampler = ClockSampler(local) if rank == 0 else None
     l0 = launches_of()
-    ms = timed(lambda: allreduce(src, dst), args.steps, 0)
+    # in place on `dst`, the form torch.distributed offers, so that every arm does the same work
+    dst.copy_(src)
+    ms = timed(lambda: allreduce(dst, dst), args.steps, 0)
     launches = launches_of() - l0
-    clocks = sampler.stop() if sampler else None
     factor = 2.0 * (world - 1) / world if world > 1 else 1.0
     algbw = nbytes / (ms * 1e-3) / 1e9
     value = algbw * factor
@@ -210,10 +211,11 @@ def main() -> int:
         for sz in (8, 1024, 64 << 10, 1 << 20, 16 << 20, 64 << 20):
             n_el = max(1, sz // es)
             a, b = src[:n_el], dst[:n_el]
-            t = timed(lambda: allreduce(a, b), 50 if sz <= (1 << 20) else 20, 5)
+            t = timed(lambda: allreduce(b, b), 50 if sz <= (1 << 20) else 20, 5)
             sweep.append({"bytes": n_el * es, "us": round(t * 1e3, 2),
                           "busbw_GBps": round(n_el * es / (t * 1e-3) / 1e9 * factor, 2)})
 
+    clocks = sampler.stop() if sampler else None
     if comm is not None:
         variant = comm.device_info()
         err = comm.async_error()
@@ -228,7 +230,7 @@ def main() -> int:
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.dtype,
             "data": "synthetic U(-1,1), seed 1234+rank", "impl": args.impl,
-            "config": {"model": "AllReduce sum, out of place", "global_batch": nbytes * world, "seq_len": count,
+            "config": {"model": "AllReduce sum, in place", "global_batch": nbytes * world, "seq_len": count,
                        "parallelism": f"{world} ranks, one per GPU", "bytes_per_rank": nbytes,
                        "l2_policy": "message larger than L2 (126 MB): no flush needed",
                        "exact_order": bool(args.exact), "device_path": variant,

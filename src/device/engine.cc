@@ -51,7 +51,7 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
     std::vector<XchgArgs> args(views.size());
     for (size_t r = 0; r < views.size(); ++r)
       build_allreduce_oneshot(&args[r], views[r], epoch, g, b[r].send, b[r].recv, count, dt, plan, order);
-    epoch += g.steps;
+    epoch += g.epochs;
     const XchgArgs* a = stage(args, st, &rc);
     return rc != cudaSuccess ? rc : launch_xchg_fold(dt, a, shape(g), st);
   }
@@ -59,14 +59,14 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
   if (var == kVarNvls) {
     std::vector<NvlsArgs> args(1);
     build_allreduce_nvls(&args[0], views[0], epoch, g, b[0].send, b[0].recv, count, dt, plan);
-    epoch += g.steps;
+    epoch += g.epochs;
     return launch_nvls(args.data(), shape(g), st);
   }
   std::vector<TwoShotArgs> args(views.size());
   for (size_t r = 0; r < views.size(); ++r)
     build_allreduce_twoshot(&args[r], views[r], epoch, g, b[r].send, b[r].recv, count, dt, plan,
                             order, tune.nvls && tune.nvls_gather && bytes % 16 == 0);
-  epoch += g.steps;
+  epoch += g.epochs;
   const TwoShotArgs* a = stage(args, st, &rc);
   return rc != cudaSuccess ? rc : launch_twoshot(dt, a, shape(g), st);
 }
@@ -77,7 +77,7 @@ cudaError_t Engine::reducescatter(const RankBufs* b, size_t per, int dt, const O
   std::vector<XchgArgs> args(views.size());
   for (size_t r = 0; r < views.size(); ++r)
     build_reducescatter(&args[r], views[r], epoch, g, b[r].send, b[r].recv, per, dt, plan);
-  epoch += g.steps;
+  epoch += g.epochs;
   ++launches;
   cudaError_t rc;
   const XchgArgs* a = stage(args, st, &rc);
@@ -90,7 +90,7 @@ cudaError_t Engine::reduce(const RankBufs* b, size_t count, int dt, const OpPlan
   std::vector<XchgArgs> args(views.size());
   for (size_t r = 0; r < views.size(); ++r)
     build_reduce(&args[r], views[r], epoch, g, b[r].send, b[r].recv, count, dt, plan, root);
-  epoch += g.steps;
+  epoch += g.epochs;
   ++launches;
   cudaError_t rc;
   const XchgArgs* a = stage(args, st, &rc);
@@ -101,7 +101,7 @@ cudaError_t Engine::reduce(const RankBufs* b, size_t count, int dt, const OpPlan
   const Geometry g = plan_xchg(MAXPAIR, n(), views[0].half_bytes, tune);    \
   std::vector<XchgArgs> args(views.size());                                 \
   for (size_t r = 0; r < views.size(); ++r) { BUILD; }                      \
-  epoch += g.steps;                                                         \
+  epoch += g.epochs;                                                         \
   ++launches;                                                               \
   cudaError_t rc;                                                           \
   const XchgArgs* a = stage(args, st, &rc);                                 \

@@ -14,24 +14,47 @@ size_t ceil_div(size_t a, size_t b) { return (a + b - 1) / b; }
 
 int threads_for(size_t bytes_per_cta) { return bytes_per_cta >= 32 * 1024 ? 512 : 256; }
 
+// bytes of one staging buffer: a whole half for a single step, a quarter of the staging area
+// (kRing = 4 buffers, device code: prims.cuh) for a pipelined launch
+size_t buffer_bytes(size_t half_bytes, int steps) {
+  return steps == 1 ? half_bytes : round_down(2 * half_bytes / 4, 256);
+}
+
 void clear(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g) {
   std::memset(a, 0, sizeof *a);
   a->w = w;
   a->epoch0 = epoch;
   a->steps = g.steps;
   a->sub_bytes = g.sub_bytes;
-  a->slot_stride = round_down(w.half_bytes / w.n, 256);
+  a->slot_stride = round_down(buffer_bytes(w.half_bytes, g.steps) / w.n, 256);
+}
+
+// Splits `per_cta_total` bytes (what one CTA moves for one pair / slice over the whole launch)
+// into steps. Small amounts go in one step (lowest latency); larger ones in at least eight
+// steps of 4..sub_max KiB so that the pipeline has something to overlap.
+void split_steps(Geometry* g, size_t per_cta_total, size_t fit_single, size_t fit_ring, const Tuning& t) {
+  const size_t want = std::max<size_t>(16, round_up(per_cta_total, 16));
+  if (want <= t.single_sub_max && want <= fit_single) {
+    g->sub_bytes = want;
+    g->steps = 1;
+    return;
+  }
+  size_t sub = std::min(std::max(round_up(want / 8, 16), size_t(4096)), t.sub_max);
+  sub = std::max<size_t>(16, std::min(sub, fit_ring));
+  g->sub_bytes = sub;
+  g->steps = int(ceil_div(want, sub));
+  if (g->steps == 1 && want > fit_single) g->steps = 2;  // cannot happen with sane windows
 }
 }  // namespace
 
 Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t) {
   Geometry g;
-  const size_t stride = round_down(half_bytes / n, 256);
   const int cap = std::max(1, std::min(t.max_ctas, kMaxCtas));
   g.ctas = int(std::min<size_t>(cap, std::max<size_t>(1, ceil_div(max_pair, 16 * 1024))));
-  const size_t fit = round_down(stride / g.ctas, 16);  // what a CTA's share of a slot can hold
-  g.sub_bytes = std::min(std::max<size_t>(16, round_up(ceil_div(max_pair, g.ctas), 16)), fit);
-  g.steps = int(std::max<size_t>(1, ceil_div(max_pair, g.sub_bytes * g.ctas)));
+  const size_t fit1 = round_down(round_down(buffer_bytes(half_bytes, 1) / n, 256) / g.ctas, 16);
+  const size_t fitr = round_down(round_down(buffer_bytes(half_bytes, 2) / n, 256) / g.ctas, 16);
+  split_steps(&g, ceil_div(max_pair, g.ctas), fit1, fitr, t);
+  g.epochs = g.steps == 1 ? 1 : g.steps + 2;
   g.threads = threads_for(g.sub_bytes * n);
   return g;
 }
@@ -40,10 +63,11 @@ Geometry plan_sliced(size_t bytes, int n, size_t half_bytes, const Tuning& t) {
   Geometry g;
   const int cap = std::max(1, std::min(t.max_ctas, kMaxCtas));
   g.ctas = int(std::min<size_t>(cap, std::max<size_t>(1, ceil_div(bytes, size_t(n) * 16 * 1024))));
-  const size_t fit = round_down(half_bytes / 2 / n / g.ctas, 16);  // staging per (slice, CTA)
-  g.sub_bytes =
-      std::min(std::max<size_t>(16, round_up(ceil_div(bytes, size_t(n) * g.ctas), 16)), fit);
-  g.steps = int(std::max<size_t>(1, ceil_div(bytes, g.sub_bytes * g.ctas * n)));
+  // a buffer holds the phase A slots in its first half and the phase B slots in its second
+  const size_t fit1 = round_down(round_down(buffer_bytes(half_bytes, 1) / 2, 256) / n / g.ctas, 16);
+  const size_t fitr = round_down(round_down(buffer_bytes(half_bytes, 2) / 2, 256) / n / g.ctas, 16);
+  split_steps(&g, ceil_div(bytes, size_t(n) * g.ctas), fit1, fitr, t);
+  g.epochs = g.steps == 1 ? 1 : g.steps + 2;
   g.threads = threads_for(g.sub_bytes * n);
   return g;
 }

@@ -16,6 +16,7 @@ struct Geometry {
   int ctas = 1;
   int threads = 256;
   int steps = 1;
+  int epochs = 1;  // epochs the launch consumes: 1, or steps + 2 when pipelined
   size_t sub_bytes = 16;
 };
 
@@ -29,6 +30,8 @@ struct Tuning {
   bool nvls = false;          // multicast alias available
   bool nvls_gather = true;    // two-shot publishes results through the multicast alias
   size_t nvls_min = 512 * 1024;    // AllReduce: from here NVLS, when allowed for (dtype, op)
+  size_t single_sub_max = 16 * 1024;  // per-CTA share up to which a launch runs as one step
+  size_t sub_max = 32 * 1024;         // largest per-CTA share of one pipelined step
 };
 
 // generic exchange where the largest block of any pair is `max_pair` bytes

@@ -118,7 +118,7 @@ extern "C" hxcclResult_t hxcclAllReduceNoAlloc(int nranks, const void* const* se
     w.n = nranks;
     build_allreduce_oneshot(&args[r], w, pd.epoch, g, send[r], recv[r], count, dt, plan, order);
   }
-  pd.epoch += g.steps;
+  pd.epoch += g.epochs;
   const XchgArgs* dev_args = reinterpret_cast<const XchgArgs*>(pd.base + kArgsOff);
   e = cudaMemcpyAsync(pd.base + kArgsOff, args, sizeof(XchgArgs) * nranks, cudaMemcpyHostToDevice, st);
   if (e != cudaSuccess) return fail(hxcclUnhandledCudaError, "staging the arguments", e);

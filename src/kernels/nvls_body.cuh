@@ -75,57 +75,89 @@ __device__ void nvls_body(const NvlsArgs& a, int cta, int ncta, FoldShared& sh) 
     scalar = load_scalar<T>(f);
   }
   if (threadIdx.x == 0) sh.fail = 0;
+  __syncthreads();
   char* mine = w.win[me];
+  const Staging stg(w, a.epoch0, a.steps);
+  const bool multi = a.steps > 1;
+  const unsigned long long e_step0 = multi ? a.epoch0 + 1 : a.epoch0;
   const size_t slice = size_t(ncta) * a.sub_bytes;
-  const size_t out_base = w.half_bytes / 2;
+  const size_t out_base = (stg.buf_bytes / 2) & ~size_t(255);
   const size_t in_slice = size_t(cta) * a.sub_bytes;
-  for (int step = 0; step < a.steps; ++step) {
-    const unsigned long long epoch = a.epoch0 + step;
-    const size_t half = w.half_off[epoch & 1];
-    const size_t step0 = size_t(step) * n * slice;
-    // my input, every slice's part of this CTA, into my own window
+
+  auto copy_in = [&](int step) {  // my input, every slice's part of this CTA, into my own window
+    const size_t step0 = size_t(step) * n * slice, buf = stg.at(step);
     for (int j = 0; j < n; ++j) {
       const size_t lo = step0 + size_t(j) * slice + in_slice;
       if (lo >= a.bytes) continue;
       const size_t len = min_sz(a.sub_bytes, a.bytes - lo);
-      char* to = mine + half + size_t(j) * slice + in_slice;
+      char* to = mine + buf + size_t(j) * slice + in_slice;
       if (a.premul)
         cta_scale_copy<T>(to, a.send + lo, len, scalar);
       else
         cta_copy(to, a.send + lo, len);
     }
-    if (!signal_and_wait(w, kOffFlagsA, cta, epoch, &sh.fail)) return;
-    {
-      const size_t lo = step0 + size_t(me) * slice + in_slice;
-      if (lo < a.bytes) {
-        const size_t len = min_sz(a.sub_bytes, a.bytes - lo);  // a multiple of 16 (host checks)
-        const char* in = w.mc + half + size_t(me) * slice + in_slice;
-        char* out = w.mc + half + out_base + size_t(me) * slice + in_slice;
-        const bool direct = (reinterpret_cast<uintptr_t>(a.recv + lo) & 15u) == 0;
-        for (size_t v = threadIdx.x; v < (len >> 4); v += blockDim.x) {
-          Vec16<T> r;
-          r.raw = mm_reduce16<kMode>(in + (v << 4));
-          if (a.postdiv) {
+    signal_all(w, kOffFlagsA, cta, e_step0 + step);
+  };
+  auto reduce = [&](int step) {  // my slice: the switch combines all ranks' copies
+    const size_t step0 = size_t(step) * n * slice, buf = stg.at(step);
+    const size_t lo = step0 + size_t(me) * slice + in_slice;
+    if (lo < a.bytes) {
+      const size_t len = min_sz(a.sub_bytes, a.bytes - lo);  // a multiple of 16 (the host checks)
+      const char* in = w.mc + buf + size_t(me) * slice + in_slice;
+      char* out = w.mc + buf + out_base + size_t(me) * slice + in_slice;
+      const bool direct = (reinterpret_cast<uintptr_t>(a.recv + lo) & 15u) == 0;
+      for (size_t v = threadIdx.x; v < (len >> 4); v += blockDim.x) {
+        Vec16<T> r;
+        r.raw = mm_reduce16<kMode>(in + (v << 4));
+        if (a.postdiv) {
 #pragma unroll
-            for (int l = 0; l < V; ++l) r.e[l] = div_trunc(r.e[l], a.postdiv);
-          }
-          asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(out + (v << 4)),
-                       "r"(r.raw.x), "r"(r.raw.y), "r"(r.raw.z), "r"(r.raw.w)
-                       : "memory");
-          if (direct) st16(a.recv + lo + (v << 4), r.raw);
+          for (int l = 0; l < V; ++l) r.e[l] = div_trunc(r.e[l], a.postdiv);
         }
+        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(out + (v << 4)),
+                     "r"(r.raw.x), "r"(r.raw.y), "r"(r.raw.z), "r"(r.raw.w)
+                     : "memory");
+        if (direct) st16(a.recv + lo + (v << 4), r.raw);
       }
     }
-    if (!signal_and_wait(w, kOffFlagsB, cta, epoch, &sh.fail)) return;
+    signal_all(w, kOffFlagsB, cta, e_step0 + step);
+  };
+  auto copy_out = [&](int step) {
+    const size_t step0 = size_t(step) * n * slice, buf = stg.at(step);
     for (int ii = 0; ii < n; ++ii) {
       const int i = (me + ii) % n;
       const size_t lo = step0 + size_t(i) * slice + in_slice;
       if (lo >= a.bytes) continue;
       if (i == me && (reinterpret_cast<uintptr_t>(a.recv + lo) & 15u) == 0) continue;  // stored directly
-      cta_copy(a.recv + lo, mine + half + out_base + size_t(i) * slice + in_slice,
+      cta_copy(a.recv + lo, mine + buf + out_base + size_t(i) * slice + in_slice,
                min_sz(a.sub_bytes, a.bytes - lo));
     }
+  };
+
+  if (!multi) {
+    copy_in(0);
+    if (!wait_all(w, kOffFlagsA, cta, e_step0, &sh.fail)) return;
+    reduce(0);
+    if (!wait_all(w, kOffFlagsB, cta, e_step0, &sh.fail)) return;
+    copy_out(0);
+    return;
   }
+  // the same software pipeline as the two-shot kernel (see coll_body.cuh): copy_in(k+1)
+  // overwrites the input slots of step k-3, which every rank finished reducing before its
+  // B(k-3); reduce(k) overwrites result slots of step k-4, copied out before A(k-1)
+  if (!signal_and_wait(w, kOffFlagsA, cta, a.epoch0, &sh.fail)) return;
+  copy_in(0);
+  for (int k = 0; k < a.steps; ++k) {
+    if (k + 1 < a.steps) copy_in(k + 1);
+    if (!wait_all(w, kOffFlagsA, cta, e_step0 + k, &sh.fail)) return;
+    reduce(k);
+    if (k > 0) {
+      if (!wait_all(w, kOffFlagsB, cta, e_step0 + k - 1, &sh.fail)) return;
+      copy_out(k - 1);
+    }
+  }
+  if (!wait_all(w, kOffFlagsB, cta, e_step0 + a.steps - 1, &sh.fail)) return;
+  copy_out(a.steps - 1);
+  signal_and_wait(w, kOffFlagsA, cta, e_step0 + a.steps, &sh.fail);
 }
 
 }  // namespace hx

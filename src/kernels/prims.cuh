@@ -66,21 +66,53 @@ __device__ inline bool wait_flag(const WinView& w, const unsigned long long* fla
   }
 }
 
-// One step's hand-over, called by every thread of the CTA. Threads 0..n-1 each signal one
-// peer (after the CTA's stores are fenced), then wait for that peer's signal of the same
-// epoch. Returns false (to all threads) when any wait gave up.
-__device__ inline bool signal_and_wait(const WinView& w, size_t flag_base, int cta,
-                                       unsigned long long epoch, int* sh_fail) {
+// Hand-over between ranks, called by every thread of the CTA. signal_all: threads 0..n-1 each
+// tell one peer "my stores up to here are in your window" (the CTA's stores are fenced first).
+// wait_all: the same threads wait for their peer's signal of `epoch`; false (to all threads)
+// when any wait gave up.
+__device__ inline void signal_all(const WinView& w, size_t flag_base, int cta, unsigned long long epoch) {
   __syncthreads();
   const int t = threadIdx.x;
   if (t < w.n && t != w.rank) {
     __threadfence_system();
     st_release_sys(flag_at(w.win[t], flag_base, cta, w.rank), epoch);
-    if (!wait_flag(w, flag_at(w.win[w.rank], flag_base, cta, t), epoch, t)) *sh_fail = 1;
   }
+}
+__device__ inline bool wait_all(const WinView& w, size_t flag_base, int cta, unsigned long long epoch,
+                                int* sh_fail) {
+  const int t = threadIdx.x;
+  if (t < w.n && t != w.rank)
+    if (!wait_flag(w, flag_at(w.win[w.rank], flag_base, cta, t), epoch, t)) *sh_fail = 1;
   __syncthreads();
   return *sh_fail == 0;
 }
+__device__ inline bool signal_and_wait(const WinView& w, size_t flag_base, int cta,
+                                       unsigned long long epoch, int* sh_fail) {
+  signal_all(w, flag_base, cta, epoch);
+  return wait_all(w, flag_base, cta, epoch, sh_fail);
+}
+
+// Where step k of a launch stages its data. A single-step launch uses the half picked by its
+// epoch's parity (see proto.h). A multi-step launch owns the whole staging area between its
+// entry hand-shake and its closing one and cycles through kRing buffers, so that step k+1 can
+// be pushed while step k is still being consumed.
+constexpr int kRing = 4;
+struct Staging {
+  size_t base0, buf_bytes;
+  int ring;
+  __device__ Staging(const WinView& w, unsigned long long epoch0, int steps) {
+    if (steps == 1) {
+      base0 = w.half_off[epoch0 & 1];
+      buf_bytes = w.half_bytes;
+      ring = 1;
+    } else {
+      base0 = w.half_off[0];
+      buf_bytes = (2 * w.half_bytes / kRing) & ~size_t(255);
+      ring = kRing;
+    }
+  }
+  __device__ size_t at(int step) const { return base0 + size_t(step % ring) * buf_bytes; }
+};
 
 // ---- bulk copies (all threads of the CTA take part) --------------------------------------------
 
