@@ -39,7 +39,7 @@ void split_steps(Geometry* g, size_t per_cta_total, size_t fit_single, size_t fi
     g->steps = 1;
     return;
   }
-  size_t sub = std::min(std::max(round_up(want / 8, 16), size_t(4096)), t.sub_max);
+  size_t sub = std::min(std::max(round_up(want / std::max(2, t.min_steps), 16), size_t(4096)), t.sub_max);
   sub = std::max<size_t>(16, std::min(sub, fit_ring));
   g->sub_bytes = sub;
   g->steps = int(ceil_div(want, sub));
@@ -55,7 +55,7 @@ Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t) {
   const size_t fitr = round_down(round_down(buffer_bytes(half_bytes, 2) / n, 256) / g.ctas, 16);
   split_steps(&g, ceil_div(max_pair, g.ctas), fit1, fitr, t);
   g.epochs = g.steps == 1 ? 1 : g.steps + 2;
-  g.threads = threads_for(g.sub_bytes * n);
+  g.threads = t.threads && g.steps > 1 ? t.threads : threads_for(g.sub_bytes * n);
   return g;
 }
 
@@ -68,7 +68,7 @@ Geometry plan_sliced(size_t bytes, int n, size_t half_bytes, const Tuning& t) {
   const size_t fitr = round_down(round_down(buffer_bytes(half_bytes, 2) / 2, 256) / n / g.ctas, 16);
   split_steps(&g, ceil_div(bytes, size_t(n) * g.ctas), fit1, fitr, t);
   g.epochs = g.steps == 1 ? 1 : g.steps + 2;
-  g.threads = threads_for(g.sub_bytes * n);
+  g.threads = t.threads && g.steps > 1 ? t.threads : threads_for(g.sub_bytes * n);
   return g;
 }
 

@@ -32,6 +32,8 @@ struct Tuning {
   size_t nvls_min = 512 * 1024;    // AllReduce: from here NVLS, when allowed for (dtype, op)
   size_t single_sub_max = 16 * 1024;  // per-CTA share up to which a launch runs as one step
   size_t sub_max = 32 * 1024;         // largest per-CTA share of one pipelined step
+  int min_steps = 8;                  // a pipelined launch aims at this many steps at least
+  int threads = 0;                    // CTA width of the large launches, 0 = choose
 };
 
 // generic exchange where the largest block of any pair is `max_pair` bytes

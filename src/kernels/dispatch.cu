@@ -132,11 +132,12 @@ cudaError_t launch_nvls(const NvlsArgs* args, LaunchShape s, cudaStream_t st) {
 int max_resident_ctas(int threads) {
   // The collective kernels differ in register use from type to type; every one of them fits
   // one 512-thread CTA per SM (__launch_bounds__(512)), so that is what is promised.
-  (void)threads;
+  // (at most 128 registers per thread), hence two CTAs of 256 threads.
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 1;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  return sms > 0 ? sms : 1;
+  if (sms < 1) sms = 1;
+  return threads <= 256 ? 2 * sms : sms;
 }
 
 }  // namespace hx

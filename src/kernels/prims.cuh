@@ -133,15 +133,12 @@ __device__ inline void cta_copy(char* dst, const char* src, size_t n) {
   if (((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15u) == 0) {
     const size_t nv = n >> 4;
     size_t i = t;
-    for (; i + 3 * size_t(nt) < nv; i += 4 * size_t(nt)) {  // four loads in flight per thread
-      const uint4 a = ld16(src + (i << 4));
-      const uint4 b = ld16(src + ((i + nt) << 4));
-      const uint4 c = ld16(src + ((i + 2 * size_t(nt)) << 4));
-      const uint4 d = ld16(src + ((i + 3 * size_t(nt)) << 4));
-      st16(dst + (i << 4), a);
-      st16(dst + ((i + nt) << 4), b);
-      st16(dst + ((i + 2 * size_t(nt)) << 4), c);
-      st16(dst + ((i + 3 * size_t(nt)) << 4), d);
+    for (; i + 7 * size_t(nt) < nv; i += 8 * size_t(nt)) {  // eight loads in flight per thread
+      uint4 r[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) r[u] = ld16(src + ((i + u * size_t(nt)) << 4));
+#pragma unroll
+      for (int u = 0; u < 8; ++u) st16(dst + ((i + u * size_t(nt)) << 4), r[u]);
     }
     for (; i < nv; i += nt) st16(dst + (i << 4), ld16(src + (i << 4)));
     for (size_t k = (nv << 4) + t; k < n; k += nt) dst[k] = src[k];
