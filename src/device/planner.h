@@ -24,15 +24,15 @@ struct Geometry {
 enum : int { kVarAuto = 0, kVarOneShot = 1, kVarTwoShot = 2, kVarNvls = 3 };
 
 struct Tuning {
-  int max_ctas = 64;          // upper bound of any collective grid
+  int max_ctas = 128;         // upper bound of any collective grid
   size_t oneshot_max = 256 * 1024;  // AllReduce: up to here every rank pushes everything
   bool exact = true;          // floats must match the host path bit for bit
   bool nvls = false;          // multicast alias available
   bool nvls_gather = true;    // two-shot publishes results through the multicast alias
   size_t nvls_min = 512 * 1024;    // AllReduce: from here NVLS, when allowed for (dtype, op)
-  size_t single_sub_max = 16 * 1024;  // per-CTA share up to which a launch runs as one step
-  size_t sub_max = 32 * 1024;         // largest per-CTA share of one pipelined step
-  int min_steps = 8;                  // a pipelined launch aims at this many steps at least
+  size_t single_sub_max = 256 * 1024;  // per-CTA share up to which a launch runs as one step
+  size_t sub_max = 512 * 1024;        // largest per-CTA share of one pipelined step
+  int min_steps = 2;                  // a pipelined launch aims at this many steps at least
   int threads = 0;                    // CTA width of the large launches, 0 = choose
 };
 

@@ -73,7 +73,7 @@ hxcclResult_t WindowPath::setup_local() {
   if (cudaEventCreateWithFlags(&order_event_, cudaEventDisableTiming) != cudaSuccess)
     return fail(hxcclUnhandledCudaError, "cannot create an event");
   Tuning& t = eng_.tune;
-  t.max_ctas = int(std::max(1L, std::min<long>(env_long("HXCCL_MAX_CTAS", 64), kMaxCtas)));
+  t.max_ctas = int(std::max(1L, std::min<long>(env_long("HXCCL_MAX_CTAS", t.max_ctas), kMaxCtas)));
   t.threads = int(env_long("HXCCL_THREADS", 0));
   if (t.threads != 256 && t.threads != 512) t.threads = 0;
   t.max_ctas = std::min(t.max_ctas, max_resident_ctas(t.threads ? t.threads : 512));

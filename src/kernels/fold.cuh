@@ -83,6 +83,102 @@ __device__ inline T fold_one(const T* x, int n, int rank, const FoldSpec& f, int
   return acc[0];
 }
 
+// One 16-byte vector through the general path: any fold kind, any rank count.
+template <typename T>
+__device__ inline void fold_vector_general(Vec16<T>& out, const FoldShared& sh, size_t v, size_t e_first,
+                                           const FoldSpec& f, int rank, int n, T scalar) {
+  constexpr int V = 16 / sizeof(T);
+  Vec16<T> in[kMaxRanks];
+  for (int i = 0; i < n; ++i) in[i].raw = ld16(sh.src[i] + (v << 4));
+  for (int l = 0; l < V; ++l) {
+    T x[kMaxRanks];
+    for (int i = 0; i < n; ++i) x[i] = in[i].e[l];
+    if (f.premul) x[rank] = scale(x[rank], scalar);
+    const int b = (f.kind == kFoldLinear && f.ring) ? ring_block_of(sh, e_first + l, n) : 0;
+    out.e[l] = fold_one(x, n, rank, f, b);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void fold_store(char* dst, const FoldShared& sh, int nremote, size_t v,
+                                           Vec16<T>& out, const FoldSpec& f) {
+  constexpr int V = 16 / sizeof(T);
+  if (f.postdiv) {
+#pragma unroll
+    for (int l = 0; l < V; ++l) out.e[l] = div_trunc(out.e[l], f.postdiv);
+  }
+  st16(dst + (v << 4), out.raw);
+  if (sh.mc_dst) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(sh.mc_dst + (v << 4)),
+                 "r"(out.raw.x), "r"(out.raw.y), "r"(out.raw.z), "r"(out.raw.w)
+                 : "memory");
+  } else {
+    for (int r = 0; r < nremote; ++r) st16(sh.remote[r] + (v << 4), out.raw);
+  }
+}
+
+// The streaming loop of the linear orders for N ranks known at compile time: U vectors per
+// thread and iteration, all N * U loads issued before the first combine.
+template <typename T, int N, int U>
+__device__ inline void fold_linear_vectors(char* dst, const FoldShared& sh, int nremote, size_t nvec,
+                                           size_t elem0, const FoldSpec& f, int rank, T scalar) {
+  constexpr int V = 16 / sizeof(T);
+  const size_t t = threadIdx.x, nt = blockDim.x;
+  for (size_t v0 = t; v0 < nvec; v0 += nt * U) {
+    Vec16<T> in[U][N];
+    int first[U];
+    bool general[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t v = v0 + u * nt;
+      general[u] = false;
+      first[u] = f.start;
+      if (v >= nvec) continue;
+      if (f.ring) {
+        const size_t e_first = elem0 + v * V;
+        const int block = ring_block_of(sh, e_first, N);
+        general[u] = ring_block_of(sh, e_first + V - 1, N) != block;
+        first[u] = (f.start + block) % N;
+      }
+      if (general[u]) continue;
+      int idx = first[u];
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        in[u][k].raw = ld16(sh.src[idx] + (v << 4));
+        idx += f.dir;
+        idx = idx >= N ? idx - N : (idx < 0 ? idx + N : idx);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t v = v0 + u * nt;
+      if (v >= nvec) continue;
+      Vec16<T> out;
+      if (general[u]) {  // the vector straddles two ring blocks: element by element
+        fold_vector_general<T>(out, sh, v, elem0 + v * V, f, rank, N, scalar);
+      } else {
+        int idx = first[u];
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+          if (f.premul && idx == rank) {
+#pragma unroll
+            for (int l = 0; l < V; ++l) in[u][k].e[l] = scale(in[u][k].e[l], scalar);
+          }
+          if (k == 0) {
+            out = in[u][0];
+          } else {
+#pragma unroll
+            for (int l = 0; l < V; ++l) out.e[l] = apply(in[u][k].e[l], out.e[l], f.op);
+          }
+          idx += f.dir;
+          idx = idx >= N ? idx - N : (idx < 0 ? idx + N : idx);
+        }
+      }
+      fold_store<T>(dst, sh, nremote, v, out, f);
+    }
+  }
+}
+
 // Folds `nbytes` bytes (whole elements). sh.src[i] points at rank i's data for this range
 // (sh.src[rank] is the unscaled local input), elem0 is the index of the first element in the
 // full vector. The result goes to dst and to each of sh.remote[0..nremote); when sh.mc_dst is
@@ -96,63 +192,16 @@ __device__ inline void cta_fold(char* dst, FoldShared& sh, int nremote, size_t n
   bool aligned = (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
   for (int i = 0; i < n; ++i) aligned = aligned && (reinterpret_cast<uintptr_t>(sh.src[i]) & 15u) == 0;
   const size_t nvec = aligned ? nbytes >> 4 : 0;
-  const bool fast = f.kind == kFoldLinear && n <= kFastRanks;
 
-  for (size_t v = t; v < nvec; v += nt) {
-    const size_t e_first = elem0 + v * V;
-    int block = 0;
-    bool uniform = true;
-    if (f.kind == kFoldLinear && f.ring) {
-      block = ring_block_of(sh, e_first, n);
-      uniform = ring_block_of(sh, e_first + V - 1, n) == block;
-    }
-    Vec16<T> out;
-    if (fast && uniform) {
-      Vec16<T> in[kFastRanks];
-      int idx = (f.start + block) % n;
-#pragma unroll
-      for (int k = 0; k < kFastRanks; ++k) {
-        if (k < n) {
-          in[k].raw = ld16(sh.src[idx] + (v << 4));
-          if (f.premul && idx == rank) {
-#pragma unroll
-            for (int l = 0; l < V; ++l) in[k].e[l] = scale(in[k].e[l], scalar);
-          }
-          idx += f.dir;
-          idx = idx >= n ? idx - n : (idx < 0 ? idx + n : idx);
-        }
-      }
-      out = in[0];
-#pragma unroll
-      for (int k = 1; k < kFastRanks; ++k) {
-        if (k < n) {
-#pragma unroll
-          for (int l = 0; l < V; ++l) out.e[l] = apply(in[k].e[l], out.e[l], f.op);
-        }
-      }
-    } else {
-      Vec16<T> in[kMaxRanks];
-      for (int i = 0; i < n; ++i) in[i].raw = ld16(sh.src[i] + (v << 4));
-      for (int l = 0; l < V; ++l) {
-        T x[kMaxRanks];
-        for (int i = 0; i < n; ++i) x[i] = in[i].e[l];
-        if (f.premul) x[rank] = scale(x[rank], scalar);
-        const int b = (f.kind == kFoldLinear && f.ring) ? ring_block_of(sh, e_first + l, n) : 0;
-        out.e[l] = fold_one(x, n, rank, f, b);
-      }
-    }
-    if (f.postdiv) {
-#pragma unroll
-      for (int l = 0; l < V; ++l) out.e[l] = div_trunc(out.e[l], f.postdiv);
-    }
-    st16(dst + (v << 4), out.raw);
-    if (sh.mc_dst) {
-      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(
-                       sh.mc_dst + (v << 4)),
-                   "r"(out.raw.x), "r"(out.raw.y), "r"(out.raw.z), "r"(out.raw.w)
-                   : "memory");
-    } else {
-      for (int r = 0; r < nremote; ++r) st16(sh.remote[r] + (v << 4), out.raw);
+  if (f.kind == kFoldLinear && (n == 2 || n == 4 || n == 8)) {
+    if (n == 2) fold_linear_vectors<T, 2, 4>(dst, sh, nremote, nvec, elem0, f, rank, scalar);
+    else if (n == 4) fold_linear_vectors<T, 4, 2>(dst, sh, nremote, nvec, elem0, f, rank, scalar);
+    else fold_linear_vectors<T, 8, 1>(dst, sh, nremote, nvec, elem0, f, rank, scalar);
+  } else {
+    for (size_t v = t; v < nvec; v += nt) {
+      Vec16<T> out;
+      fold_vector_general<T>(out, sh, v, elem0 + v * V, f, rank, n, scalar);
+      fold_store<T>(dst, sh, nremote, v, out, f);
     }
   }
 

@@ -66,7 +66,6 @@ __device__ inline void p2p_body(const P2pArgs& a, int lane_idx, int wk, int* sh_
         __syncthreads();
         if (threadIdx.x == 0) {
           st_relaxed_sys(p2p_hdr(theirs, me, wk, tx & 1), total);
-          __threadfence_system();
           st_release_sys(ready, tx + 1);
         }
       }

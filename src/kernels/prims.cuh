@@ -73,10 +73,10 @@ __device__ inline bool wait_flag(const WinView& w, const unsigned long long* fla
 __device__ inline void signal_all(const WinView& w, size_t flag_base, int cta, unsigned long long epoch) {
   __syncthreads();
   const int t = threadIdx.x;
-  if (t < w.n && t != w.rank) {
-    __threadfence_system();
-    st_release_sys(flag_at(w.win[t], flag_base, cta, w.rank), epoch);
-  }
+  // st.release.sys orders the flag after every store the CTA made before the barrier above
+  // (release is cumulative over what the barrier made visible to this thread); no separate
+  // fence.sc is needed, and it is expensive at system scope
+  if (t < w.n && t != w.rank) st_release_sys(flag_at(w.win[t], flag_base, cta, w.rank), epoch);
 }
 __device__ inline bool wait_all(const WinView& w, size_t flag_base, int cta, unsigned long long epoch,
                                 int* sh_fail) {

@@ -1,0 +1,87 @@
+"""The torch.distributed "hxccl" backend on CPU tensors (host path), against gloo on the same
+inputs: the reference's python/tests/test_backend.py:24-77 strategy. The CUDA side of the
+backend is exercised by tests/test_torch_backend_gpu.py."""
+import os
+
+import pytest
+
+torch = pytest.importorskip("torch")
+import torch.distributed as dist  # noqa: E402
+import torch.multiprocessing as mp  # noqa: E402
+
+
+def _worker(rank, world, port, q):
+    try:
+        import hxccl_b200.parallel as hp
+
+        hp.register()
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("hxccl", rank=rank, world_size=world)
+        ref = dist.new_group(backend="gloo")
+        torch.manual_seed(rank)
+        for dtype in (torch.float32, torch.int32, torch.bfloat16, torch.float16):
+            for op in (dist.ReduceOp.SUM, dist.ReduceOp.MAX):
+                for n in (1, 1000, 100000):
+                    x = (torch.rand(n) * 10).to(dtype)
+                    a, b = x.clone(), x.clone()
+                    dist.all_reduce(a, op=op)
+                    dist.all_reduce(b, op=op, group=ref)
+                    tol = 0 if dtype in (torch.int32,) or op == dist.ReduceOp.MAX else 2e-2
+                    assert torch.allclose(a.float(), b.float(), rtol=tol, atol=tol), (dtype, op, n)
+        x = torch.arange(6, dtype=torch.float32) + rank
+        y = x.clone()
+        dist.all_reduce(y, op=dist.ReduceOp.AVG)
+        assert torch.allclose(y, torch.arange(6, dtype=torch.float32) + (world - 1) / 2)
+        out = torch.empty(world * 4)
+        dist.all_gather_into_tensor(out, torch.full((4,), float(rank)))
+        assert out.tolist() == [float(r) for r in range(world) for _ in range(4)]
+        outs = [torch.empty(3) for _ in range(world)]
+        dist.all_gather(outs, torch.full((3,), float(rank)))
+        assert [o[0].item() for o in outs] == [float(r) for r in range(world)]
+        rs = torch.empty(5)
+        dist.reduce_scatter_tensor(rs, torch.arange(5 * world, dtype=torch.float32))
+        assert torch.allclose(rs, world * (torch.arange(5, dtype=torch.float32) + 5 * rank))
+        b = torch.full((7,), float(rank))
+        dist.broadcast(b, src=world - 1)
+        assert b.tolist() == [float(world - 1)] * 7
+        a2a = torch.empty(world * 2)
+        dist.all_to_all_single(a2a, torch.arange(world * 2, dtype=torch.float32) + 100 * rank)
+        assert a2a.tolist() == [100.0 * r + 2 * rank + k for r in range(world) for k in range(2)]
+        if rank == 0:
+            dist.send(torch.tensor([42.0]), dst=1)
+        elif rank == 1:
+            t = torch.zeros(1)
+            dist.recv(t, src=0)
+            assert t.item() == 42.0
+        g = [torch.empty(2) for _ in range(world)] if rank == 0 else None
+        dist.gather(torch.full((2,), float(rank)), g, dst=0)
+        if rank == 0:
+            assert [t[0].item() for t in g] == [float(r) for r in range(world)]
+        sc = torch.empty(2)
+        dist.scatter(sc, [torch.full((2,), float(r)) for r in range(world)] if rank == 0 else None, src=0)
+        assert sc.tolist() == [float(rank)] * 2
+        dist.barrier()
+        with pytest.raises((ValueError, RuntimeError)):
+            dist.all_reduce(torch.zeros(4, 4).t())  # not contiguous
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except BaseException as e:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, f"{e!r}\n{traceback.format_exc()}"))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_backend_matches_gloo(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29650 + world
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=180) for _ in range(world)]
+    for p in procs:
+        p.join(10)
+        if p.is_alive():
+            p.kill()
+    assert all(m == "ok" for _, m in got), got
