@@ -132,7 +132,7 @@ hxcclResult_t hxcclCommShrink(hxcclComm_t comm, int* excl, int nexcl, hxcclComm_
   }
   const int me = int(std::find(members.begin(), members.end(), comm->rank) - members.begin());
   return make_comm(newcomm,
-                   comm->chan->child(members, me, mix_id(comm->chan->id(), comm->derived++, salt)));
+                   comm->chan->child(members, me, mix_id(comm->chan->id(), comm->shrunk[salt]++, salt)));
 }
 
 hxcclResult_t hxcclCommAbort(hxcclComm_t comm) {

@@ -2,6 +2,7 @@
 // (Reference: src/comm.h:11-42, src/checks.h:8-33.)
 #pragma once
 #include <functional>
+#include <map>
 #include <memory>
 #include <string>
 #include <vector>
@@ -35,7 +36,10 @@ struct hxcclComm {
   std::string last_error;
   std::vector<hx::UserOp> user_ops;
   int op_tag = 0;        // 1..0x7ffe, per communicator of this process
-  uint64_t derived = 0;  // Split/Shrink calls so far; feeds the children's channel ids
+  uint64_t derived = 0;  // Split calls so far; feeds the children's channel ids
+  // Shrink calls so far per exclude list. Only the survivors of a list call Shrink, so a count
+  // shared with Split would drift apart between ranks that were and were not excluded.
+  std::map<uint64_t, uint64_t> shrunk;
   bool finalized = false;
   hxcclResult_t async_error = hxcclSuccess;
   uint64_t dev_bytes = 0, dev_msgs = 0;  // device-path traffic under the reference schedule
