@@ -88,6 +88,8 @@ def lib() -> C.CDLL:
         # extensions
         "hxcclCommDeviceInfo": [vp, C.c_char_p, sz, C.POINTER(i), C.POINTER(C.c_ulonglong)],
         "hxcclCommTune": [vp, i, i, i],
+        "hxcclCommTuneKnob": [vp, C.c_char_p, C.c_long],
+        "hxcclWorldTuneKnob": [vp, C.c_char_p, C.c_long],
         "hxcclDevReduce": [vp, vp, sz, i, i, vp],
         "hxcclDevScale": [vp, vp, sz, i, vp, vp],
         "hxcclDevDivide": [vp, sz, i, i, vp],

@@ -182,6 +182,10 @@ class Communicator:
     def tune(self, variant: int = 0, exact: bool = True, max_ctas: int = 0) -> int:
         return L.lib().hxcclCommTune(self._h, variant, int(exact), max_ctas)
 
+    def knob(self, name: str, value: int) -> int:
+        """One tuning knob of the device path by name (same call on every rank)."""
+        return L.lib().hxcclCommTuneKnob(self._h, name.encode(), value)
+
     def _ok(self, rc: int, what: str, check: bool = True) -> int:
         if rc and check:
             raise HxcclError(rc, what, self.last_error() if self._h else "")

@@ -56,6 +56,9 @@ class World:
     def tune(self, variant: int = 0, exact: bool = True, max_ctas: int = 0) -> None:
         self._ok(L.lib().hxcclWorldTune(self._h, variant, int(exact), max_ctas), "hxcclWorldTune")
 
+    def knob(self, name: str, value: int) -> None:
+        self._ok(L.lib().hxcclWorldTuneKnob(self._h, name.encode(), value), "hxcclWorldTuneKnob")
+
     def info(self) -> dict:
         v, n = C.c_int(), C.c_ulonglong()
         L.lib().hxcclWorldInfo(self._h, C.byref(v), C.byref(n))

@@ -24,6 +24,11 @@ hxcclResult_t hxcclCommDeviceInfo(hxcclComm_t comm, char* kind, size_t kind_len,
  * Every rank must make the same call. */
 hxcclResult_t hxcclCommTune(hxcclComm_t comm, int variant, int exact, int max_ctas);
 
+/* Sets one tuning knob of the device path by name (see src/device/planner.h: set_knob), e.g.
+ * "roles_min" (bytes from which AllReduce runs as a three-role pipeline). Same call on every
+ * rank. hxcclInvalidArgument for an unknown name. */
+hxcclResult_t hxcclCommTuneKnob(hxcclComm_t comm, const char* name, long value);
+
 /* ---- elementwise kernels on device buffers (any stream, no communicator) ------------------- */
 hxcclResult_t hxcclDevReduce(void* dst, const void* src, size_t count, hxcclDataType_t dt,
                              hxcclRedOp_t op, hxcclStream_t stream); /* dst = dst op src */
@@ -58,6 +63,7 @@ hxcclResult_t hxcclWorldCreate(hxcclWorld_t* world, int n, int window_mb, int wa
 hxcclResult_t hxcclWorldDestroy(hxcclWorld_t world);
 /* variant/exact/max_ctas as in hxcclCommTune */
 hxcclResult_t hxcclWorldTune(hxcclWorld_t world, int variant, int exact, int max_ctas);
+hxcclResult_t hxcclWorldTuneKnob(hxcclWorld_t world, const char* name, long value);
 /* send[r] / recv[r] are rank r's device buffers. op is hxcclSum..hxcclAvg; a non-null scalar
  * (host memory, one element of dt) makes it PreMulSum. order: 0 ring, 1 recursive doubling,
  * -1 by message size as the API does. */

@@ -55,12 +55,15 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
     const XchgArgs* a = stage(args, st, &rc);
     return rc != cudaSuccess ? rc : launch_xchg_fold(dt, a, shape(g), st);
   }
-  const Geometry g = plan_sliced(bytes, n(), views[0].half_bytes, tune);
+  const bool roles = bytes >= tune.roles_min && tune.max_ctas >= 3 && n() > 1;
+  const Geometry g = roles ? plan_roles(bytes, n(), views[0].half_bytes, tune)
+                           : plan_sliced(bytes, n(), views[0].half_bytes, tune);
   if (var == kVarNvls) {
     std::vector<NvlsArgs> args(1);
     build_allreduce_nvls(&args[0], views[0], epoch, g, b[0].send, b[0].recv, count, dt, plan);
     epoch += g.epochs;
-    return launch_nvls(args.data(), shape(g), st);
+    if (roles) last_variant = kVarNvlsRoles;
+    return launch_nvls(args.data(), shape(g), st, roles);
   }
   std::vector<TwoShotArgs> args(views.size());
   for (size_t r = 0; r < views.size(); ++r)
@@ -68,7 +71,9 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
                             order, tune.nvls && tune.nvls_gather && bytes % 16 == 0);
   epoch += g.epochs;
   const TwoShotArgs* a = stage(args, st, &rc);
-  return rc != cudaSuccess ? rc : launch_twoshot(dt, a, shape(g), st);
+  if (rc != cudaSuccess) return rc;
+  if (roles) last_variant = kVarTwoShotRoles;
+  return roles ? launch_twoshot_roles(dt, a, shape(g), st) : launch_twoshot(dt, a, shape(g), st);
 }
 
 cudaError_t Engine::reducescatter(const RankBufs* b, size_t per, int dt, const OpPlan& plan,

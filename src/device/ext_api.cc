@@ -37,6 +37,13 @@ hxcclResult_t hxcclCommTune(hxcclComm_t c, int variant, int exact, int max_ctas)
   return hxcclSuccess;
 }
 
+hxcclResult_t hxcclCommTuneKnob(hxcclComm_t c, const char* name, long value) {
+  if (!c) return hxcclInvalidArgument;
+  auto* w = dynamic_cast<WindowPath*>(c->dev.get());
+  if (!w) return hxcclInvalidUsage;
+  return set_knob(&w->engine().tune, name, value) ? hxcclSuccess : hxcclInvalidArgument;
+}
+
 static hxcclResult_t cuda_rc(cudaError_t e) { return e == cudaSuccess ? hxcclSuccess : hxcclUnhandledCudaError; }
 
 hxcclResult_t hxcclDevReduce(void* dst, const void* src, size_t count, hxcclDataType_t dt,

@@ -2,6 +2,7 @@
 
 #include <algorithm>
 #include <cstring>
+#include <string>
 
 #include "device/nvls_modes.h"
 #include "math/dtypes.h"
@@ -47,6 +48,23 @@ void split_steps(Geometry* g, size_t per_cta_total, size_t fit_single, size_t fi
 }
 }  // namespace
 
+bool set_knob(Tuning* t, const char* name, long v) {
+  const std::string k(name ? name : "");
+  if (k == "max_ctas") t->max_ctas = int(std::max(1L, std::min<long>(v, kMaxCtas)));
+  else if (k == "oneshot_max") t->oneshot_max = size_t(v);
+  else if (k == "nvls_min") t->nvls_min = size_t(v);
+  else if (k == "single_sub_max") t->single_sub_max = size_t(v);
+  else if (k == "sub_max") t->sub_max = size_t(std::max(16L, v / 16 * 16));
+  else if (k == "min_steps") t->min_steps = int(std::max(2L, v));
+  else if (k == "threads") t->threads = (v == 256 || v == 512) ? int(v) : 0;
+  else if (k == "roles_min") t->roles_min = size_t(v);
+  else if (k == "roles_sub") t->roles_sub = size_t(std::max(16L, v / 16 * 16));
+  else if (k == "exact") t->exact = v != 0;
+  else if (k == "nvls_gather") t->nvls_gather = v != 0;
+  else return false;
+  return true;
+}
+
 Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t) {
   Geometry g;
   const int cap = std::max(1, std::min(t.max_ctas, kMaxCtas));
@@ -69,6 +87,22 @@ Geometry plan_sliced(size_t bytes, int n, size_t half_bytes, const Tuning& t) {
   split_steps(&g, ceil_div(bytes, size_t(n) * g.ctas), fit1, fitr, t);
   g.epochs = g.steps == 1 ? 1 : g.steps + 2;
   g.threads = t.threads && g.steps > 1 ? t.threads : threads_for(g.sub_bytes * n);
+  return g;
+}
+
+Geometry plan_roles(size_t bytes, int n, size_t half_bytes, const Tuning& t) {
+  Geometry g;
+  const int cap = std::max(3, std::min(t.max_ctas, kMaxCtas));
+  int lanes = std::max(1, cap / 3);
+  lanes = int(std::min<size_t>(lanes, std::max<size_t>(1, ceil_div(bytes, size_t(n) * 16 * 1024))));
+  // a ring buffer holds the staged inputs in its first half and the results in its second
+  const size_t fit = round_down(round_down(buffer_bytes(half_bytes, 2) / 2, 256) / n / lanes, 16);
+  g.sub_bytes = std::max<size_t>(16, std::min(std::min(round_up(t.roles_sub, 16), fit),
+                                              round_up(ceil_div(bytes, size_t(n) * lanes), 16)));
+  g.ctas = 3 * lanes;
+  g.steps = int(std::max<size_t>(1, ceil_div(bytes, g.sub_bytes * lanes * n)));
+  g.epochs = g.steps + 1;
+  g.threads = t.threads ? t.threads : 512;
   return g;
 }
 

@@ -21,7 +21,7 @@ struct Geometry {
 };
 
 // AllReduce transport variants
-enum : int { kVarAuto = 0, kVarOneShot = 1, kVarTwoShot = 2, kVarNvls = 3 };
+enum : int { kVarAuto = 0, kVarOneShot = 1, kVarTwoShot = 2, kVarNvls = 3, kVarTwoShotRoles = 4, kVarNvlsRoles = 5 };
 
 struct Tuning {
   int max_ctas = 128;         // upper bound of any collective grid
@@ -34,12 +34,21 @@ struct Tuning {
   size_t sub_max = 512 * 1024;        // largest per-CTA share of one pipelined step
   int min_steps = 2;                  // a pipelined launch aims at this many steps at least
   int threads = 0;                    // CTA width of the large launches, 0 = choose
+  size_t roles_min = 96u << 20;       // AllReduce: from here the three-role pipeline
+  size_t roles_sub = 64 * 1024;       // its per-lane share of a slice per step
 };
+
+// Sets one tuning knob by name ("max_ctas", "oneshot_max", "nvls_min", "single_sub_max",
+// "sub_max", "min_steps", "threads", "roles_min", "roles_sub", "exact", "nvls_gather");
+// false for an unknown name.
+bool set_knob(Tuning* t, const char* name, long value);
 
 // generic exchange where the largest block of any pair is `max_pair` bytes
 Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t);
 // two-shot / NVLS AllReduce of `bytes`
 Geometry plan_sliced(size_t bytes, int n, size_t half_bytes, const Tuning& t);
+// the same as a three-role pipeline: ctas = 3 * lanes, epochs = steps + 1
+Geometry plan_roles(size_t bytes, int n, size_t half_bytes, const Tuning& t);
 
 FoldSpec make_fold(const OpPlan& plan, int kind);
 

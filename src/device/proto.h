@@ -10,6 +10,7 @@
 //   [control]  abort word, Send/Recv counters and flags
 //   [flags A]  one 64-bit epoch per (CTA, source rank): "my step-e data is in your window"
 //   [flags B]  same, for the second phase of two-phase kernels
+//   [flags C]  same, for the third role of the three-role pipeline (kernels/roles_body.cuh)
 //   [p2p]      double-buffered Send/Recv slots, one set per (sender, worker)
 //   [half 0] [half 1]  collective staging, alternating per step
 //
@@ -42,7 +43,9 @@ constexpr size_t kOffP2pDone = 16384;   // u64 [receiver][worker], written by th
 constexpr size_t kOffP2pHdr = 20480;    // u64 [sender][worker][2]: message bytes per slot
 constexpr size_t kOffFlagsA = 64 * 1024;
 constexpr size_t kOffFlagsB = kOffFlagsA + size_t(kMaxCtas) * kMaxRanks * 8;
+constexpr size_t kOffFlagsC = kOffFlagsB + size_t(kMaxCtas) * kMaxRanks * 8;
 constexpr size_t kHeaderBytes = 1u << 20;
+static_assert(kOffFlagsC + size_t(kMaxCtas) * kMaxRanks * 8 <= kHeaderBytes, "flag pages must fit the header");
 constexpr size_t kOffP2pSlots = kHeaderBytes;
 
 inline constexpr size_t p2p_region_bytes(int n) {

@@ -127,6 +127,13 @@ hxcclResult_t hxcclWorldTune(hxcclWorld_t w, int variant, int exact, int max_cta
   return hxcclSuccess;
 }
 
+hxcclResult_t hxcclWorldTuneKnob(hxcclWorld_t w, const char* name, long value) {
+  if (!w) return hxcclInvalidArgument;
+  if (!set_knob(&w->eng.tune, name, value)) return hxcclInvalidArgument;
+  w->eng.tune.max_ctas = std::min(w->eng.tune.max_ctas, std::max(1, world_cta_budget() / w->n));
+  return hxcclSuccess;
+}
+
 hxcclResult_t hxcclWorldAllReduce(hxcclWorld_t w, const void* const* send, void* const* recv,
                                   size_t count, hxcclDataType_t dt, hxcclRedOp_t op,
                                   const void* scalar, int order, hxcclStream_t stream) {

@@ -32,6 +32,11 @@ __global__ void __launch_bounds__(512) k_nvls(const __grid_constant__ NvlsArgs a
   __shared__ FoldShared sh;
   nvls_body<T, kMode>(a, blockIdx.x, gridDim.x, sh);
 }
+template <typename T, int kMode>
+__global__ void __launch_bounds__(512) k_nvls_roles(const __grid_constant__ NvlsArgs a) {
+  __shared__ FoldShared sh;
+  nvls_roles_body<T, kMode>(a, blockIdx.x, gridDim.x, sh);
+}
 
 cudaError_t launch_xchg_copy(const XchgArgs* args, LaunchShape s, cudaStream_t st) {
   if (s.world) return launch_world(reinterpret_cast<const void*>(&k_xchg_copy_world), args, s, st);
@@ -48,6 +53,7 @@ cudaError_t launch_p2p(const P2pArgs* args, LaunchShape s, cudaStream_t st) {
 #define HX_EXTERN_TYPE(T)                                                                       \
   extern template cudaError_t launch_xchg_fold_t<T>(const XchgArgs*, LaunchShape, cudaStream_t); \
   extern template cudaError_t launch_twoshot_t<T>(const TwoShotArgs*, LaunchShape, cudaStream_t); \
+  extern template cudaError_t launch_twoshot_roles_t<T>(const TwoShotArgs*, LaunchShape, cudaStream_t); \
   extern template cudaError_t launch_reduce_t<T>(void*, const void*, size_t, int, cudaStream_t); \
   extern template cudaError_t launch_scale_t<T>(void*, const void*, size_t, unsigned long long, \
                                                 cudaStream_t);                                  \
@@ -75,6 +81,11 @@ cudaError_t launch_twoshot(int dt, const TwoShotArgs* args, LaunchShape s, cudaS
   HX_DISPATCH_DTYPE(dt, rc = launch_twoshot_t<T>(args, s, st))
   return rc;
 }
+cudaError_t launch_twoshot_roles(int dt, const TwoShotArgs* args, LaunchShape s, cudaStream_t st) {
+  cudaError_t rc = cudaErrorInvalidValue;
+  HX_DISPATCH_DTYPE(dt, rc = launch_twoshot_roles_t<T>(args, s, st))
+  return rc;
+}
 cudaError_t launch_reduce(void* dst, const void* src, size_t count, int dt, int op, cudaStream_t st) {
   cudaError_t rc = cudaErrorInvalidValue;
   HX_DISPATCH_DTYPE(dt, rc = launch_reduce_t<T>(dst, src, count, op, st))
@@ -94,11 +105,14 @@ cudaError_t launch_divide(void* buf, size_t count, int dt, int divisor, cudaStre
   return rc;
 }
 
-#define HX_NVLS_CASE(MODE, T)                             \
-  case MODE:                                              \
-    k_nvls<T, MODE><<<s.ctas, s.threads, 0, st>>>(*args); \
+#define HX_NVLS_CASE(MODE, T)                                         \
+  case MODE:                                                          \
+    if (roles)                                                        \
+      k_nvls_roles<T, MODE><<<s.ctas, s.threads, 0, st>>>(*args);     \
+    else                                                              \
+      k_nvls<T, MODE><<<s.ctas, s.threads, 0, st>>>(*args);           \
     break;
-cudaError_t launch_nvls(const NvlsArgs* args, LaunchShape s, cudaStream_t st) {
+cudaError_t launch_nvls(const NvlsArgs* args, LaunchShape s, cudaStream_t st, bool roles) {
   switch (nvls_mode(args->dt, args->op)) {
     HX_NVLS_CASE(kNvF32Add, float)
     HX_NVLS_CASE(kNvF64Add, double)

@@ -2,6 +2,7 @@
 // compile in parallel.
 #pragma once
 #include "kernels/coll_body.cuh"
+#include "kernels/roles_body.cuh"
 #include "kernels/launch.h"
 
 namespace hx {
@@ -27,6 +28,17 @@ __global__ void __launch_bounds__(512) k_twoshot_world(const TwoShotArgs* a) {
   twoshot_body<T>(a[blockIdx.y], blockIdx.x, gridDim.x, sh);
 }
 
+template <typename T>
+__global__ void __launch_bounds__(512) k_twoshot_roles(const __grid_constant__ TwoShotArgs a) {
+  __shared__ FoldShared sh;
+  twoshot_roles_body<T>(a, blockIdx.x, gridDim.x, sh);
+}
+template <typename T>
+__global__ void __launch_bounds__(512) k_twoshot_roles_world(const TwoShotArgs* a) {
+  __shared__ FoldShared sh;
+  twoshot_roles_body<T>(a[blockIdx.y], blockIdx.x, gridDim.x, sh);
+}
+
 template <typename Args>
 cudaError_t launch_world(const void* kernel, const Args* dev_args, LaunchShape s, cudaStream_t st) {
   void* params[] = {const_cast<Args**>(&dev_args)};
@@ -45,6 +57,14 @@ cudaError_t launch_twoshot_t(const TwoShotArgs* args, LaunchShape s, cudaStream_
   if (s.world)
     return launch_world(reinterpret_cast<const void*>(&k_twoshot_world<T>), args, s, st);
   k_twoshot<T><<<s.ctas, s.threads, 0, st>>>(*args);
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_twoshot_roles_t(const TwoShotArgs* args, LaunchShape s, cudaStream_t st) {
+  if (s.world)
+    return launch_world(reinterpret_cast<const void*>(&k_twoshot_roles_world<T>), args, s, st);
+  k_twoshot_roles<T><<<s.ctas, s.threads, 0, st>>>(*args);
   return cudaGetLastError();
 }
 
@@ -116,6 +136,7 @@ cudaError_t launch_divide_t(void* buf, size_t count, int divisor, cudaStream_t s
 #define HX_INSTANTIATE_TYPE(T)                                                               \
   template cudaError_t launch_xchg_fold_t<T>(const XchgArgs*, LaunchShape, cudaStream_t);    \
   template cudaError_t launch_twoshot_t<T>(const TwoShotArgs*, LaunchShape, cudaStream_t);   \
+  template cudaError_t launch_twoshot_roles_t<T>(const TwoShotArgs*, LaunchShape, cudaStream_t); \
   template cudaError_t launch_reduce_t<T>(void*, const void*, size_t, int, cudaStream_t);    \
   template cudaError_t launch_scale_t<T>(void*, const void*, size_t, unsigned long long,     \
                                          cudaStream_t);                                      \

@@ -19,7 +19,10 @@ struct LaunchShape {
 cudaError_t launch_xchg_copy(const XchgArgs* args, LaunchShape s, cudaStream_t st);
 cudaError_t launch_xchg_fold(int dt, const XchgArgs* args, LaunchShape s, cudaStream_t st);
 cudaError_t launch_twoshot(int dt, const TwoShotArgs* args, LaunchShape s, cudaStream_t st);
-cudaError_t launch_nvls(const NvlsArgs* args, LaunchShape s, cudaStream_t st);  // production only
+// three-role pipeline for large messages (grid = 3 * lanes)
+cudaError_t launch_twoshot_roles(int dt, const TwoShotArgs* args, LaunchShape s, cudaStream_t st);
+// production only; roles = three-role pipeline
+cudaError_t launch_nvls(const NvlsArgs* args, LaunchShape s, cudaStream_t st, bool roles = false);
 cudaError_t launch_p2p(const P2pArgs* args, LaunchShape s, cudaStream_t st);
 
 // standalone elementwise kernels (dst op= src, dst = src*scalar, buf /= divisor)

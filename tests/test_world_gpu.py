@@ -89,6 +89,34 @@ def test_allreduce_large_multistep_inplace(worlds, n):
 
 
 @pytest.mark.parametrize("n", [2, 3, 8])
+def test_allreduce_three_role_pipeline(worlds, n):
+    """The large-message variant (one CTA each for staging in, combining and staging out per
+    lane), forced onto small messages: many steps, ring reuse, odd sizes, in place."""
+    w = worlds(n)
+    w.tune(variant=2, exact=True)
+    w.knob("roles_min", 1)
+    w.knob("roles_sub", 4096)
+    try:
+        for dt, op, count in ((L.FLOAT32, L.SUM, (3 << 20) // 4 + 3), (L.BFLOAT16, L.AVG, 700001),
+                              (L.INT64, L.MAX, 40001), (L.FLOAT8E5M2, L.SUM, 1 << 20), (L.FLOAT32, L.PROD, 5)):
+            xs = rand_inputs(n, count, dt, seed=31 + dt)
+            if dt in FLOATS:
+                for x in xs:
+                    x &= x.dtype.type(~(1 << (8 * L.DTYPE_SIZE[dt] - 2)) & ((1 << (8 * L.DTYPE_SIZE[dt])) - 1))
+            buf = [to_dev(x) for x in xs]
+            w.all_reduce(buf, buf, count, dt, op=op, order=0)
+            torch.cuda.synchronize()
+            assert w.info()["variant"] == 4
+            want = oracle.allreduce(xs, dt, op, order=0)
+            for r in range(n):
+                assert np.array_equal(back(buf[r], dt), want[r]), (n, dt, op, count, r)
+        assert all(w.status(r) == (0, 0) for r in range(n))
+    finally:
+        w.knob("roles_min", 96 << 20)
+        w.knob("roles_sub", 65536)
+
+
+@pytest.mark.parametrize("n", [2, 3, 8])
 def test_reducescatter_and_reduce(worlds, n):
     w = worlds(n)
     for dt in (L.INT8, L.INT64, L.FLOAT32, L.FLOAT64, L.BFLOAT16, L.FLOAT8E5M2):
