@@ -103,7 +103,16 @@ def main() -> int:
                 per = max(1, n_el // world)
                 fn = lambda: comm.all_to_all(buf[: per * world], out[: per * world], count=per)  # noqa: E731
             ms = timed(fn, args.iters if size >= (1 << 20) else 5 * args.iters)
-            report(cfg or "default", size, ms, {"variant": comm.device_info()["variant"], "err": comm.async_error()})
+            extra = {"variant": comm.device_info()["variant"], "err": comm.async_error()}
+            if os.environ.get("HXCCL_TRACE"):
+                tr = comm.read_trace()
+                used = tr[tr[:, 7] > 0]
+                if len(used):
+                    calls = 5 + (args.iters if size >= (1 << 20) else 5 * args.iters)
+                    names = ["in", "sigA", "waitA", "mid", "sigB", "waitB", "out", "all"]
+                    extra["trace_us"] = {k: round(float(used[:, i].mean()) / calls / 1e3, 1) for i, k in enumerate(names)}
+                    extra["ctas"] = int(len(used))
+            report(cfg or "default", size, ms, extra)
         comm.destroy()
         for k, v in saved.items():
             if v is None:

@@ -89,6 +89,7 @@ def lib() -> C.CDLL:
         "hxcclCommDeviceInfo": [vp, C.c_char_p, sz, C.POINTER(i), C.POINTER(C.c_ulonglong)],
         "hxcclCommTune": [vp, i, i, i],
         "hxcclCommTuneKnob": [vp, C.c_char_p, C.c_long],
+        "hxcclCommReadTrace": [vp, C.POINTER(C.c_ulonglong), i],
         "hxcclWorldTuneKnob": [vp, C.c_char_p, C.c_long],
         "hxcclDevReduce": [vp, vp, sz, i, i, vp],
         "hxcclDevScale": [vp, vp, sz, i, vp, vp],

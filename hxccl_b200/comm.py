@@ -186,6 +186,12 @@ class Communicator:
         """One tuning knob of the device path by name (same call on every rank)."""
         return L.lib().hxcclCommTuneKnob(self._h, name.encode(), value)
 
+    def read_trace(self, max_ctas: int = 512):
+        """Phase timers (HXCCL_TRACE=1): array [ctas, 16] of nanosecond sums since the last read."""
+        buf = (C.c_ulonglong * (16 * max_ctas))()
+        rows = L.lib().hxcclCommReadTrace(self._h, buf, max_ctas)
+        return np.frombuffer(buf, dtype=np.uint64).reshape(max_ctas, 16)[:rows].copy()
+
     def _ok(self, rc: int, what: str, check: bool = True) -> int:
         if rc and check:
             raise HxcclError(rc, what, self.last_error() if self._h else "")

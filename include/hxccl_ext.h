@@ -29,6 +29,12 @@ hxcclResult_t hxcclCommTune(hxcclComm_t comm, int variant, int exact, int max_ct
  * rank. hxcclInvalidArgument for an unknown name. */
 hxcclResult_t hxcclCommTuneKnob(hxcclComm_t comm, const char* name, long value);
 
+/* Phase timers of the collective kernels (communicators created with HXCCL_TRACE=1): 16
+ * nanosecond sums per CTA since the previous read (staging in, first flag, first wait,
+ * combining, second flag, second wait, staging out, whole kernel, rest unused). Waits for the
+ * enqueued work first. Returns the number of CTA rows written to `out` (0 when tracing is off). */
+int hxcclCommReadTrace(hxcclComm_t comm, unsigned long long* out, int max_ctas);
+
 /* ---- elementwise kernels on device buffers (any stream, no communicator) ------------------- */
 hxcclResult_t hxcclDevReduce(void* dst, const void* src, size_t count, hxcclDataType_t dt,
                              hxcclRedOp_t op, hxcclStream_t stream); /* dst = dst op src */

@@ -44,6 +44,11 @@ hxcclResult_t hxcclCommTuneKnob(hxcclComm_t c, const char* name, long value) {
   return set_knob(&w->engine().tune, name, value) ? hxcclSuccess : hxcclInvalidArgument;
 }
 
+int hxcclCommReadTrace(hxcclComm_t c, unsigned long long* out, int max_ctas) {
+  auto* w = c ? dynamic_cast<WindowPath*>(c->dev.get()) : nullptr;
+  return w && out && max_ctas > 0 ? w->read_trace(out, max_ctas) : 0;
+}
+
 static hxcclResult_t cuda_rc(cudaError_t e) { return e == cudaSuccess ? hxcclSuccess : hxcclUnhandledCudaError; }
 
 hxcclResult_t hxcclDevReduce(void* dst, const void* src, size_t count, hxcclDataType_t dt,

@@ -119,12 +119,12 @@ FoldSpec make_fold(const OpPlan& plan, int kind) {
 }
 
 int choose_variant(size_t bytes, int dt, const OpPlan& plan, int n, const Tuning& t, int forced) {
-  (void)n;
   const bool nvls_ok = t.nvls && bytes % 16 == 0 && bytes > 0 &&
                        nvls_mode(dt, plan.base) != kNvNone && (is_integer(dt) || !t.exact);
   if (forced == kVarNvls && nvls_ok) return kVarNvls;
   if (forced == kVarOneShot || forced == kVarTwoShot) return forced;
-  if (nvls_ok && bytes >= t.nvls_min) return kVarNvls;
+  // with two ranks the multicast reduction measured slower than two-shot at every size
+  if (nvls_ok && bytes >= t.nvls_min && n > 2) return kVarNvls;
   return bytes <= t.oneshot_max ? kVarOneShot : kVarTwoShot;
 }
 

@@ -64,8 +64,15 @@ struct WinView {
   size_t half_off[2];     // offsets of the two staging halves
   size_t half_bytes;
   unsigned long long wait_ns;  // limit of every device-side wait
+  // Optional phase timing (HXCCL_TRACE=1): kTraceSlots accumulators of nanoseconds per CTA,
+  // filled by thread 0 of each CTA from %globaltimer; null when off.
+  unsigned long long* trace;
   int rank, n;
 };
+constexpr int kTraceSlots = 16;
+// what the slots hold (single-role kernels): time spent staging in, raising the first flag,
+// waiting for it, combining, raising / waiting for the second flag, staging out; slot 7 = whole kernel
+enum : int { kTrIn = 0, kTrSigA = 1, kTrWaitA = 2, kTrMid = 3, kTrSigB = 4, kTrWaitB = 5, kTrOut = 6, kTrAll = 7 };
 
 // How a fold combines the ranks' values for one element (see core/schedule.h):
 //   Linear   acc = x[s0]; then x[s0+dir], x[s0+2dir], ... each as the LEFT operand. With

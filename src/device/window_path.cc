@@ -114,6 +114,11 @@ hxcclResult_t WindowPath::init() {
   w.wait_ns = uint64_t(std::max(1L, env_long("HXCCL_WAIT_LIMIT_MS", 20000))) * 1000000ull;
   w.rank = rank_;
   w.n = n_;
+  if (env_long("HXCCL_TRACE", 0) != 0) {
+    const size_t bytes = size_t(kMaxCtas) * kTraceSlots * sizeof(unsigned long long);
+    if (cudaMalloc(reinterpret_cast<void**>(&trace_), bytes) == cudaSuccess) cudaMemset(trace_, 0, bytes);
+  }
+  w.trace = trace_;
   eng_.views.assign(1, w);
   eng_.tune.nvls = nvls_;
   if (std::getenv("HXCCL_DEBUG") && rank_ == 0)
@@ -328,6 +333,7 @@ void WindowPath::release() {
   const CuDriver& d = cu();
   cudaSetDevice(dev_);
   if (scratch_) cudaFree(scratch_), scratch_ = nullptr;
+  if (trace_) cudaFree(trace_), trace_ = nullptr;
   if (mc_va_) {
     d.MemUnmap(mc_va_, win_bytes_);
     d.MemAddressFree(mc_va_, win_bytes_);
@@ -480,6 +486,16 @@ hxcclResult_t WindowPath::alltoallv(const char* send, const size_t* sbytes, cons
 hxcclResult_t WindowPath::p2p_batch(const std::vector<P2pOp>& ops, void* stream) {
   RankP2p r{ops};
   return done(eng_.p2p(&r, enter(stream)), "Send/Recv launch");
+}
+
+int WindowPath::read_trace(unsigned long long* out, int max_ctas) {
+  if (!trace_) return 0;
+  drain();
+  const int rows = std::min(max_ctas, kMaxCtas);
+  const size_t bytes = size_t(rows) * kTraceSlots * sizeof(unsigned long long);
+  if (cudaMemcpy(out, trace_, bytes, cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
+  cudaMemset(trace_, 0, size_t(kMaxCtas) * kTraceSlots * sizeof(unsigned long long));
+  return rows;
 }
 
 hxcclResult_t WindowPath::drain() {

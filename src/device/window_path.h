@@ -44,6 +44,9 @@ class WindowPath : public DevicePath {
   hxcclResult_t drain() override;
 
   Engine& engine() { return eng_; }
+  // Phase timers (HXCCL_TRACE=1): copies kTraceSlots nanosecond sums per CTA to `out` (up to
+  // `max_ctas` rows) after draining the stream, and clears them. Returns the rows copied.
+  int read_trace(unsigned long long* out, int max_ctas);
 
  private:
   hxcclResult_t fail(hxcclResult_t r, const std::string& why);
@@ -73,6 +76,7 @@ class WindowPath : public DevicePath {
   cudaStream_t last_stream_ = nullptr;
   bool used_ = false;
   cudaEvent_t order_event_ = nullptr;
+  unsigned long long* trace_ = nullptr;
   void* scratch_ = nullptr;  // private copy of an overlapping AlltoAll send side
   size_t scratch_bytes_ = 0;
   hxcclResult_t broken_ = hxcclSuccess;

@@ -39,6 +39,7 @@ __device__ void xchg_body(const XchgArgs& a, int cta, int ncta, FoldShared& sh) 
   const bool multi = a.steps > 1;
   const unsigned long long e_step0 = multi ? a.epoch0 + 1 : a.epoch0;
   const size_t in_slot = size_t(cta) * a.sub_bytes;
+  PhaseTimer tm(w, cta);
 
   auto push = [&](int step) {
     const size_t lo = (size_t(step) * ncta + cta) * a.sub_bytes;  // offset inside a pair's block
@@ -53,7 +54,10 @@ __device__ void xchg_body(const XchgArgs& a, int cta, int ncta, FoldShared& sh) 
       else
         cta_copy(to, a.send_ptr[j] + lo, len);
     }
+    __syncthreads();
+    tm.lap(kTrIn);
     signal_all(w, kOffFlagsA, cta, e_step0 + step);
+    tm.lap(kTrSigA);
   };
   auto consume = [&](int step) {
     const size_t lo = (size_t(step) * ncta + cta) * a.sub_bytes;
@@ -82,19 +86,29 @@ __device__ void xchg_body(const XchgArgs& a, int cta, int ncta, FoldShared& sh) 
   if (!multi) {
     push(0);
     if (!wait_all(w, kOffFlagsA, cta, e_step0, &sh.fail)) return;
+    tm.lap(kTrWaitA);
     consume(0);
+    __syncthreads();
+    tm.lap(kTrOut);
+    tm.done();
     return;
   }
   if (!signal_and_wait(w, kOffFlagsA, cta, a.epoch0, &sh.fail)) return;  // entry
+  tm.lap(kTrWaitB);
   push(0);
   for (int k = 0; k < a.steps; ++k) {
     // push(k+1) reuses the buffer of step k-3. The owner consumed that step before it pushed
     // step k-1, and this CTA saw the owner's signal of step k-1 in the previous iteration.
     if (k + 1 < a.steps) push(k + 1);
     if (!wait_all(w, kOffFlagsA, cta, e_step0 + k, &sh.fail)) return;
+    tm.lap(kTrWaitA);
     consume(k);
+    __syncthreads();
+    tm.lap(kTrOut);
   }
   signal_and_wait(w, kOffFlagsA, cta, e_step0 + a.steps, &sh.fail);  // closing
+  tm.lap(kTrWaitB);
+  tm.done();
 }
 
 // ---- two-shot AllReduce ------------------------------------------------------------------------
@@ -120,8 +134,12 @@ __device__ void twoshot_body(const TwoShotArgs& a, int cta, int ncta, FoldShared
   const size_t slice = size_t(ncta) * a.sub_bytes;  // bytes of one slice per step
   const size_t ag_base = (stg.buf_bytes / 2) & ~size_t(255);
   const size_t in_slice = size_t(cta) * a.sub_bytes;
+  PhaseTimer tm(w, cta);
 
-  auto push = [&](int step) {  // phase A: my contribution to every other owner's slice
+  // In the pipelined loop the flag of push(k+1) is raised only after fold(k): the release has
+  // to wait until the pushed bytes have landed on the peers, and that wait then overlaps the
+  // fold instead of stalling the CTA twice per step.
+  auto push = [&](int step, bool signal) {  // phase A: my contribution to every other owner's slice
     const size_t step0 = size_t(step) * n * slice, buf = stg.at(step);
     for (int jj = 1; jj < n; ++jj) {
       const int j = (me + jj) % n;
@@ -134,9 +152,14 @@ __device__ void twoshot_body(const TwoShotArgs& a, int cta, int ncta, FoldShared
       else
         cta_copy(to, a.send + lo, len);
     }
-    signal_all(w, kOffFlagsA, cta, e_step0 + step);
+    __syncthreads();
+    tm.lap(kTrIn);
+    if (signal) {
+      signal_all(w, kOffFlagsA, cta, e_step0 + step);
+      tm.lap(kTrSigA);
+    }
   };
-  auto fold = [&](int step) {  // my slice: combine, keep, and fan the result out
+  auto fold = [&](int step, bool also_signal_next_push) {  // my slice: combine, keep, fan out
     const size_t step0 = size_t(step) * n * slice, buf = stg.at(step);
     const size_t lo = step0 + size_t(me) * slice + in_slice;
     __syncthreads();
@@ -152,7 +175,11 @@ __device__ void twoshot_body(const TwoShotArgs& a, int cta, int ncta, FoldShared
     if (lo < a.bytes)
       cta_fold<T>(a.recv + lo, sh, n - 1, min_sz(a.sub_bytes, a.bytes - lo), lo / sizeof(T), a.fold,
                   me, n, scalar);
+    __syncthreads();
+    tm.lap(kTrMid);
     signal_all(w, kOffFlagsB, cta, e_step0 + step);
+    if (also_signal_next_push) signal_all(w, kOffFlagsA, cta, e_step0 + step + 1);
+    tm.lap(kTrSigB);
   };
   auto gather = [&](int step) {  // phase B: the other owners' results
     const size_t step0 = size_t(step) * n * slice, buf = stg.at(step);
@@ -163,34 +190,44 @@ __device__ void twoshot_body(const TwoShotArgs& a, int cta, int ncta, FoldShared
       cta_copy(a.recv + lo, mine + buf + ag_base + size_t(i) * slice + in_slice,
                min_sz(a.sub_bytes, a.bytes - lo));
     }
+    __syncthreads();
+    tm.lap(kTrOut);
   };
 
   if (!multi) {
-    push(0);
+    push(0, true);
     if (!wait_all(w, kOffFlagsA, cta, e_step0, &sh.fail)) return;
-    fold(0);
+    tm.lap(kTrWaitA);
+    fold(0, false);
     if (!wait_all(w, kOffFlagsB, cta, e_step0, &sh.fail)) return;
+    tm.lap(kTrWaitB);
     gather(0);
+    tm.done();
     return;
   }
   if (!signal_and_wait(w, kOffFlagsA, cta, a.epoch0, &sh.fail)) return;  // entry
-  push(0);
+  push(0, true);
   for (int k = 0; k < a.steps; ++k) {
     // push(k+1) overwrites phase A slots of step k-3: their owners folded that step before
     // they signalled B(k-3), which this CTA waited for two iterations ago.
-    if (k + 1 < a.steps) push(k + 1);
+    if (k + 1 < a.steps) push(k + 1, false);
     if (!wait_all(w, kOffFlagsA, cta, e_step0 + k, &sh.fail)) return;
+    tm.lap(kTrWaitA);
     // fold(k) overwrites phase B slots of step k-4 on the peers: a peer copied those out
     // before it pushed step k-1 (signal A(k-1)), which is older than the A(k) just seen.
-    fold(k);
+    fold(k, k + 1 < a.steps);
     if (k > 0) {
       if (!wait_all(w, kOffFlagsB, cta, e_step0 + k - 1, &sh.fail)) return;
+      tm.lap(kTrWaitB);
       gather(k - 1);
     }
   }
   if (!wait_all(w, kOffFlagsB, cta, e_step0 + a.steps - 1, &sh.fail)) return;
+  tm.lap(kTrWaitB);
   gather(a.steps - 1);
   signal_and_wait(w, kOffFlagsA, cta, e_step0 + a.steps, &sh.fail);  // closing
+  tm.lap(kTrWaitB);
+  tm.done();
 }
 
 }  // namespace hx

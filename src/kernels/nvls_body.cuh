@@ -62,11 +62,40 @@ __device__ __forceinline__ uint4 mm_reduce16(const char* p) {
   return v;
 }
 
+// Reduces `len` bytes (a multiple of 16) at multicast address `in`, applies the integer
+// post-divide, publishes the result at multicast address `out` and, when `direct` is set, also
+// stores it at `direct`. Four reductions are in flight per thread: a multimem.ld_reduce is a
+// round trip through the switch, far longer than a local load.
+template <typename T, int kMode>
+__device__ inline void mm_reduce_range(const char* in, char* out, char* direct, size_t len, int postdiv) {
+  constexpr int V = 16 / sizeof(T);
+  constexpr int U = 4;
+  const size_t nvec = len >> 4, nt = blockDim.x;
+  for (size_t v0 = threadIdx.x; v0 < nvec; v0 += nt * U) {
+    Vec16<T> r[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (v0 + u * nt < nvec) r[u].raw = mm_reduce16<kMode>(in + ((v0 + u * nt) << 4));
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t v = v0 + u * nt;
+      if (v >= nvec) continue;
+      if (postdiv) {
+#pragma unroll
+        for (int l = 0; l < V; ++l) r[u].e[l] = div_trunc(r[u].e[l], postdiv);
+      }
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(out + (v << 4)),
+                   "r"(r[u].raw.x), "r"(r[u].raw.y), "r"(r[u].raw.z), "r"(r[u].raw.w)
+                   : "memory");
+      if (direct) st16(direct + (v << 4), r[u].raw);
+    }
+  }
+}
+
 template <typename T, int kMode>
 __device__ void nvls_body(const NvlsArgs& a, int cta, int ncta, FoldShared& sh) {
   const WinView& w = a.w;
   const int me = w.rank, n = w.n;
-  constexpr int V = 16 / sizeof(T);
   T scalar{};
   if (a.premul) {
     FoldSpec f{};
@@ -83,6 +112,7 @@ __device__ void nvls_body(const NvlsArgs& a, int cta, int ncta, FoldShared& sh) 
   const size_t slice = size_t(ncta) * a.sub_bytes;
   const size_t out_base = (stg.buf_bytes / 2) & ~size_t(255);
   const size_t in_slice = size_t(cta) * a.sub_bytes;
+  PhaseTimer tm(w, cta);
 
   auto copy_in = [&](int step) {  // my input, every slice's part of this CTA, into my own window
     const size_t step0 = size_t(step) * n * slice, buf = stg.at(step);
@@ -96,7 +126,10 @@ __device__ void nvls_body(const NvlsArgs& a, int cta, int ncta, FoldShared& sh) 
       else
         cta_copy(to, a.send + lo, len);
     }
+    __syncthreads();
+    tm.lap(kTrIn);
     signal_all(w, kOffFlagsA, cta, e_step0 + step);
+    tm.lap(kTrSigA);
   };
   auto reduce = [&](int step) {  // my slice: the switch combines all ranks' copies
     const size_t step0 = size_t(step) * n * slice, buf = stg.at(step);
@@ -106,20 +139,12 @@ __device__ void nvls_body(const NvlsArgs& a, int cta, int ncta, FoldShared& sh) 
       const char* in = w.mc + buf + size_t(me) * slice + in_slice;
       char* out = w.mc + buf + out_base + size_t(me) * slice + in_slice;
       const bool direct = (reinterpret_cast<uintptr_t>(a.recv + lo) & 15u) == 0;
-      for (size_t v = threadIdx.x; v < (len >> 4); v += blockDim.x) {
-        Vec16<T> r;
-        r.raw = mm_reduce16<kMode>(in + (v << 4));
-        if (a.postdiv) {
-#pragma unroll
-          for (int l = 0; l < V; ++l) r.e[l] = div_trunc(r.e[l], a.postdiv);
-        }
-        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(out + (v << 4)),
-                     "r"(r.raw.x), "r"(r.raw.y), "r"(r.raw.z), "r"(r.raw.w)
-                     : "memory");
-        if (direct) st16(a.recv + lo + (v << 4), r.raw);
-      }
+      mm_reduce_range<T, kMode>(in, out, direct ? a.recv + lo : nullptr, len, a.postdiv);
     }
+    __syncthreads();
+    tm.lap(kTrMid);
     signal_all(w, kOffFlagsB, cta, e_step0 + step);
+    tm.lap(kTrSigB);
   };
   auto copy_out = [&](int step) {
     const size_t step0 = size_t(step) * n * slice, buf = stg.at(step);
@@ -131,14 +156,19 @@ __device__ void nvls_body(const NvlsArgs& a, int cta, int ncta, FoldShared& sh) 
       cta_copy(a.recv + lo, mine + buf + out_base + size_t(i) * slice + in_slice,
                min_sz(a.sub_bytes, a.bytes - lo));
     }
+    __syncthreads();
+    tm.lap(kTrOut);
   };
 
   if (!multi) {
     copy_in(0);
     if (!wait_all(w, kOffFlagsA, cta, e_step0, &sh.fail)) return;
+    tm.lap(kTrWaitA);
     reduce(0);
     if (!wait_all(w, kOffFlagsB, cta, e_step0, &sh.fail)) return;
+    tm.lap(kTrWaitB);
     copy_out(0);
+    tm.done();
     return;
   }
   // the same software pipeline as the two-shot kernel (see coll_body.cuh): copy_in(k+1)
@@ -149,15 +179,20 @@ __device__ void nvls_body(const NvlsArgs& a, int cta, int ncta, FoldShared& sh) 
   for (int k = 0; k < a.steps; ++k) {
     if (k + 1 < a.steps) copy_in(k + 1);
     if (!wait_all(w, kOffFlagsA, cta, e_step0 + k, &sh.fail)) return;
+    tm.lap(kTrWaitA);
     reduce(k);
     if (k > 0) {
       if (!wait_all(w, kOffFlagsB, cta, e_step0 + k - 1, &sh.fail)) return;
+      tm.lap(kTrWaitB);
       copy_out(k - 1);
     }
   }
   if (!wait_all(w, kOffFlagsB, cta, e_step0 + a.steps - 1, &sh.fail)) return;
+  tm.lap(kTrWaitB);
   copy_out(a.steps - 1);
   signal_and_wait(w, kOffFlagsA, cta, e_step0 + a.steps, &sh.fail);
+  tm.lap(kTrWaitB);
+  tm.done();
 }
 
 }  // namespace hx

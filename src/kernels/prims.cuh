@@ -114,6 +114,28 @@ struct Staging {
   __device__ size_t at(int step) const { return base0 + size_t(step % ring) * buf_bytes; }
 };
 
+// Phase timer of one CTA (see WinView::trace). lap(slot) adds the time since the previous lap.
+struct PhaseTimer {
+  unsigned long long* acc;
+  unsigned long long last, first;
+  __device__ PhaseTimer(const WinView& w, int cta) : acc(nullptr), last(0), first(0) {
+    if (w.trace && threadIdx.x == 0) {
+      acc = w.trace + size_t(cta) * kTraceSlots;
+      last = first = now_ns();
+    }
+  }
+  __device__ __forceinline__ void lap(int slot) {
+    if (acc) {
+      const unsigned long long t = now_ns();
+      acc[slot] += t - last;
+      last = t;
+    }
+  }
+  __device__ __forceinline__ void done() {
+    if (acc) acc[kTrAll] += now_ns() - first;
+  }
+};
+
 // ---- bulk copies (all threads of the CTA take part) --------------------------------------------
 
 __device__ __forceinline__ uint4 ld16(const void* p) { return *reinterpret_cast<const uint4*>(p); }

@@ -178,7 +178,6 @@ struct NvlsRoleOps {
     }
   }
   __device__ void combine(int k) {
-    constexpr int V = 16 / sizeof(T);
     const WinView& w = a.w;
     const size_t step0 = size_t(k) * w.n * g.slice, buf = g.buf(k);
     const size_t lo = step0 + size_t(w.rank) * g.slice + g.in_slice;
@@ -186,17 +185,7 @@ struct NvlsRoleOps {
     const size_t len = min_sz(a.sub_bytes, a.bytes - lo);
     const char* in = w.mc + buf + size_t(w.rank) * g.slice + g.in_slice;
     char* out = w.mc + buf + g.second + size_t(w.rank) * g.slice + g.in_slice;
-    for (size_t v = threadIdx.x; v < (len >> 4); v += blockDim.x) {
-      Vec16<T> r;
-      r.raw = mm_reduce16<kMode>(in + (v << 4));
-      if (a.postdiv) {
-#pragma unroll
-        for (int l = 0; l < V; ++l) r.e[l] = div_trunc(r.e[l], a.postdiv);
-      }
-      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(out + (v << 4)),
-                   "r"(r.raw.x), "r"(r.raw.y), "r"(r.raw.z), "r"(r.raw.w)
-                   : "memory");
-    }
+    mm_reduce_range<T, kMode>(in, out, nullptr, len, a.postdiv);
   }
   __device__ void stage_out(int k) {  // every slice, the own one included (it came back through the switch)
     const WinView& w = a.w;
