@@ -1,0 +1,84 @@
+"""GPT-2 in plain PyTorch, the model of the data-parallel training benchmark (small: 12
+layers, d_model 768, 12 heads, MLP 3072, vocabulary 50257, context 1024). It is the workload
+that produces gradient buckets for the collectives, not part of the communication library:
+its matrix products and attention are PyTorch's own kernels."""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+@dataclass
+class GPT2Config:
+    vocab_size: int = 50257
+    n_ctx: int = 1024
+    n_layer: int = 12
+    n_head: int = 12
+    d_model: int = 768
+    d_mlp: int = 3072
+    dropout: float = 0.0
+
+    @classmethod
+    def small(cls) -> "GPT2Config":
+        return cls()
+
+    @classmethod
+    def tiny(cls) -> "GPT2Config":  # for smoke tests
+        return cls(vocab_size=512, n_ctx=64, n_layer=2, n_head=2, d_model=64, d_mlp=256)
+
+
+class Block(nn.Module):
+    def __init__(self, c: GPT2Config):
+        super().__init__()
+        self.ln1 = nn.LayerNorm(c.d_model)
+        self.qkv = nn.Linear(c.d_model, 3 * c.d_model)
+        self.proj = nn.Linear(c.d_model, c.d_model)
+        self.ln2 = nn.LayerNorm(c.d_model)
+        self.fc = nn.Linear(c.d_model, c.d_mlp)
+        self.out = nn.Linear(c.d_mlp, c.d_model)
+        self.n_head = c.n_head
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        b, t, d = x.shape
+        q, k, v = self.qkv(self.ln1(x)).view(b, t, 3, self.n_head, d // self.n_head).permute(2, 0, 3, 1, 4)
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        x = x + self.proj(a.transpose(1, 2).reshape(b, t, d))
+        return x + self.out(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))
+
+
+class GPT2(nn.Module):
+    def __init__(self, c: GPT2Config):
+        super().__init__()
+        self.config = c
+        self.wte = nn.Embedding(c.vocab_size, c.d_model)
+        self.wpe = nn.Embedding(c.n_ctx, c.d_model)
+        self.blocks = nn.ModuleList(Block(c) for _ in range(c.n_layer))
+        self.ln_f = nn.LayerNorm(c.d_model)
+        self.apply(self._init)
+        for blk in self.blocks:  # GPT-2's scaled init of the residual projections
+            for lin in (blk.proj, blk.out):
+                nn.init.normal_(lin.weight, std=0.02 / math.sqrt(2 * c.n_layer))
+
+    @staticmethod
+    def _init(m: nn.Module) -> None:
+        if isinstance(m, (nn.Linear, nn.Embedding)):
+            nn.init.normal_(m.weight, std=0.02)
+        if isinstance(m, nn.Linear) and m.bias is not None:
+            nn.init.zeros_(m.bias)
+
+    def forward(self, idx: torch.Tensor, targets: torch.Tensor | None = None):
+        b, t = idx.shape
+        x = self.wte(idx) + self.wpe(torch.arange(t, device=idx.device))
+        for blk in self.blocks:
+            x = blk(x)
+        logits = F.linear(self.ln_f(x), self.wte.weight)  # tied output embedding
+        if targets is None:
+            return logits
+        return F.cross_entropy(logits.view(-1, logits.size(-1)).float(), targets.view(-1))
+
+    def num_params(self) -> int:
+        return sum(p.numel() for p in self.parameters())

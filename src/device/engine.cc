@@ -67,8 +67,11 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
   }
   std::vector<TwoShotArgs> args(views.size());
   for (size_t r = 0; r < views.size(); ++r)
+    // Publishing results with one multimem.st per vector saves link egress, but measured
+    // slower than peer stores wherever the kernel is not egress-bound: it pays off only in
+    // the three-role pipeline on more than two ranks.
     build_allreduce_twoshot(&args[r], views[r], epoch, g, b[r].send, b[r].recv, count, dt, plan,
-                            order, tune.nvls && tune.nvls_gather && bytes % 16 == 0);
+                            order, tune.nvls && tune.nvls_gather && roles && n() > 2 && bytes % 16 == 0);
   epoch += g.epochs;
   const TwoShotArgs* a = stage(args, st, &rc);
   if (rc != cudaSuccess) return rc;

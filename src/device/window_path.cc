@@ -129,7 +129,7 @@ hxcclResult_t WindowPath::init() {
 
 hxcclResult_t WindowPath::setup_windows() {
   const CuDriver& d = cu();
-  const long half_mb = std::max(1L, env_long("HXCCL_WINDOW_MB", 64) / 2);
+  const long half_mb = std::max(1L, env_long("HXCCL_WINDOW_MB", 512) / 2);
   const size_t want = kHeaderBytes + round_up(p2p_region_bytes(n_), 1u << 20) + 2 * (size_t(half_mb) << 20);
   va_.assign(n_, 0);
   peer_h_.assign(n_, 0);
