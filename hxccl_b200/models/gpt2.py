@@ -78,7 +78,7 @@ class GPT2(nn.Module):
         logits = F.linear(self.ln_f(x), self.wte.weight)  # tied output embedding
         if targets is None:
             return logits
-        return F.cross_entropy(logits.view(-1, logits.size(-1)).float(), targets.view(-1))
+        return F.cross_entropy(logits.reshape(-1, logits.size(-1)).float(), targets.reshape(-1))
 
     def num_params(self) -> int:
         return sum(p.numel() for p in self.parameters())
