@@ -77,6 +77,23 @@ def build_lib(verbose: bool = False, jobs: int | None = None) -> Path:
     return LIB
 
 
+def build_perf(verbose: bool = False) -> Path:
+    """Builds bench/hx_perf, the native sweep tool, against libhxccl.so."""
+    build_lib(verbose)
+    src = ROOT / "bench" / "hx_perf.cc"
+    out = ROOT / "bench" / "hx_perf"
+    if out.exists() and out.stat().st_mtime > max(src.stat().st_mtime, LIB.stat().st_mtime):
+        return out
+    cmd = [NVCC, "-std=c++17", "-O2", *INCLUDES, str(src), "-o", str(out), f"-L{LIB_DIR}", "-lhxccl",
+           "-Xlinker", f"-rpath={LIB_DIR}", "-Xlinker", "-rpath=$ORIGIN/../hxccl_b200/lib", "-cudart", "static"]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"building hx_perf failed:\n{res.stdout}\n{res.stderr}")
+    return out
+
+
 def build_torch_ext(verbose: bool = False) -> Path:
     """Builds hxccl_b200/_hxccl_c10d.so, the torch.distributed backend, against libhxccl.so."""
     build_lib(verbose)
@@ -108,12 +125,15 @@ def build_torch_ext(verbose: bool = False) -> Path:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--torch", action="store_true", help="also build the torch.distributed backend")
+    ap.add_argument("--perf", action="store_true", help="also build bench/hx_perf")
     ap.add_argument("-v", "--verbose", action="store_true")
     ap.add_argument("-j", "--jobs", type=int, default=None)
     args = ap.parse_args()
     print(build_lib(args.verbose, args.jobs))
     if args.torch:
         print(build_torch_ext(args.verbose))
+    if args.perf:
+        print(build_perf(args.verbose))
 
 
 if __name__ == "__main__":

@@ -55,7 +55,8 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
     const XchgArgs* a = stage(args, st, &rc);
     return rc != cudaSuccess ? rc : launch_xchg_fold(dt, a, shape(g), st);
   }
-  const bool roles = bytes >= tune.roles_min && tune.max_ctas >= 3 && n() > 1;
+  // the three-role pipeline measured faster than the single-role kernels only beyond two ranks
+  const bool roles = bytes >= tune.roles_min && tune.max_ctas >= 3 && n() > 2;
   const Geometry g = roles ? plan_roles(bytes, n(), views[0].half_bytes, tune)
                            : plan_sliced(bytes, n(), views[0].half_bytes, tune);
   if (var == kVarNvls) {

@@ -149,3 +149,39 @@ def test_other_collectives(n):
         assert np.array_equal(res[r]["rs"], want_rs[r])
         first = [int(np.random.default_rng(r).integers(0, 256, 3 << 20, dtype=np.uint8)[0])] * n
         assert res[r]["a2a"] == [(first[0] + i) % 256 for i in range(n)] or True  # layout checked below
+
+
+def _departure_body(comm, rank, n):
+    """Rank 1 leaves between two steps (nothing of its in flight); rank 0's next collective must
+    end with an error status after the bounded wait, and its CUDA context must stay usable."""
+    import time
+
+    import torch
+
+    x = torch.ones(1 << 16, device="cuda")
+    comm.all_reduce(x)
+    torch.cuda.synchronize()
+    assert float(x[0]) == n
+    if rank == 1:
+        return "left"
+    time.sleep(1.0)  # the peer is gone by now (it destroys its communicator when it returns)
+    t0 = time.time()
+    rc = comm.all_reduce(x, check=False)
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    err = comm.async_error()
+    later = comm.all_reduce(x, check=False)  # the path stays failed: no new launch
+    alive = float(torch.ones(8, device="cuda").sum())
+    return rc, err, later, comm.last_error(), waited, alive
+
+
+@needs2
+def test_peer_departure_is_reported_not_hung():
+    env = {"HXCCL_NVLS": "0", "NCCL_NVLS_ENABLE": "0", "HXCCL_WAIT_LIMIT_MS": "1500"}
+    res = run_ranks(2, _departure_body, gpus=True, timeout=120, env=env)
+    assert res[1] == "left"
+    rc, err, later, msg, waited, alive = res[0]
+    assert rc == 0                      # the launch itself succeeds: calls enqueue and return
+    assert err == L.TIMEOUT and later == L.TIMEOUT, (err, later, msg)
+    assert "ran out of time" in msg and 1.0 < waited < 20.0
+    assert alive == 8.0
