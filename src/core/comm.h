@@ -47,8 +47,9 @@ struct hxcclComm {
 
 namespace hx {
 
-// Records `msg` as the communicator's last error; System/Internal/Remote also become the
-// sticky asynchronous error. Returns r.
+// Records `msg` as the communicator's last error; System/Internal/Remote (and Timeout, which
+// only the bounded device-side waits produce) also become the sticky asynchronous error.
+// Returns r.
 hxcclResult_t comm_fail(hxcclComm* c, hxcclResult_t r, const std::string& msg);
 long user_op_slot(const hxcclComm* c, hxcclRedOp_t op);  // -1 when not a live op of c
 

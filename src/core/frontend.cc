@@ -12,7 +12,7 @@ namespace hx {
 hxcclResult_t comm_fail(hxcclComm* c, hxcclResult_t r, const std::string& msg) {
   if (c) {
     c->last_error = msg;
-    if (r == hxcclSystemError || r == hxcclInternalError || r == hxcclRemoteError)
+    if (r == hxcclSystemError || r == hxcclInternalError || r == hxcclRemoteError || r == hxcclTimeout)
       c->async_error = r;
   }
   return r;

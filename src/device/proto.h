@@ -31,8 +31,8 @@ namespace hx {
 constexpr int kMaxRanks = 16;       // ranks of one device communicator
 constexpr int kFastRanks = 8;       // the unrolled fold covers this many
 constexpr int kMaxCtas = 512;       // flag rows
-constexpr int kP2pWorkers = 8;      // independent sub-channels per directed pair
-constexpr size_t kP2pSlotBytes = 128 * 1024;  // per (sender, worker, parity)
+constexpr int kP2pWorkers = 16;     // independent sub-channels per directed pair
+constexpr size_t kP2pSlotBytes = 512 * 1024;  // per (sender, worker, parity)
 
 // byte offsets inside a window
 constexpr size_t kOffAbort = 0;
@@ -41,6 +41,8 @@ constexpr size_t kOffP2pRx = 8192;    // u64 [kMaxRanks][kP2pWorkers]  chunk-slo
 constexpr size_t kOffP2pReady = 12288;  // u64 [sender][worker], written by the sender
 constexpr size_t kOffP2pDone = 16384;   // u64 [receiver][worker], written by the receiver
 constexpr size_t kOffP2pHdr = 20480;    // u64 [sender][worker][2]: message bytes per slot
+static_assert(size_t(kMaxRanks) * kP2pWorkers * 8 <= 4096 && kOffP2pHdr + size_t(kMaxRanks) * kP2pWorkers * 16 <= 64 * 1024,
+              "Send/Recv words must fit their slots in the header");
 constexpr size_t kOffFlagsA = 64 * 1024;
 constexpr size_t kOffFlagsB = kOffFlagsA + size_t(kMaxCtas) * kMaxRanks * 8;
 constexpr size_t kOffFlagsC = kOffFlagsB + size_t(kMaxCtas) * kMaxRanks * 8;
