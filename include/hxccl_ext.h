@@ -55,6 +55,12 @@ float hxcclHostDecode(hxcclDataType_t dt, unsigned bits);
 /* the ring block of `count` elements over n ranks: offset and length of block i */
 void hxcclRingBlock(size_t count, int n, int i, size_t* off, size_t* len);
 
+/* Device self-check: runs the device's float -> dt encoder over all 2^32 float bit patterns and
+ * its decoder over all codes of dt (Float16, Bfloat16, Float8e4m3, Float8e5m2) and counts the
+ * inputs where it differs from the host rules; *first_bad_bits is the smallest such float. */
+hxcclResult_t hxcclTestNarrowConvert(hxcclDataType_t dt, unsigned long long* mismatches,
+                                     unsigned int* first_bad_bits);
+
 /* ---- fault injection (host side only) ---------------------------------------------------------- */
 /* The (after+1)-th host-path send from now fails with hxcclSystemError; after < 0 disarms. */
 hxcclResult_t hxcclTestFailSends(hxcclComm_t comm, long after);

@@ -122,8 +122,27 @@ HX_HD float to_f32(f16 v) {
 #endif
 }
 HX_HD float to_f32(bf16 v) { return bits_f32(static_cast<uint32_t>(v.b) << 16); }
-HX_HD float to_f32(e4m3 v) { return FmtE4M3::decode(v.b); }
-HX_HD float to_f32(e5m2 v) { return FmtE5M2::decode(v.b); }
+HX_HD float to_f32(e4m3 v) {
+#if defined(__CUDA_ARCH__)
+  // hardware decode of a pair (exact); the low byte lands in the low half
+  unsigned int pair;
+  float f;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(pair) : "h"(static_cast<unsigned short>(v.b)));
+  asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(static_cast<unsigned short>(pair & 0xffffu)));
+  return f;
+#else
+  return FmtE4M3::decode(v.b);
+#endif
+}
+HX_HD float to_f32(e5m2 v) {
+#if defined(__CUDA_ARCH__)
+  float f;  // e5m2 is the upper byte of an fp16
+  asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(static_cast<unsigned short>(v.b << 8)));
+  return f;
+#else
+  return FmtE5M2::decode(v.b);
+#endif
+}
 
 HX_HD void from_f32(float x, f16* out) {
 #if defined(__CUDA_ARCH__)
@@ -146,7 +165,35 @@ HX_HD void from_f32(float x, bf16* out) {
   // exponent, up to and including inf
   out->b = static_cast<uint16_t>((u + 0x7fffu + ((u >> 16) & 1u)) >> 16);
 }
-HX_HD void from_f32(float x, e4m3* out) { out->b = static_cast<uint8_t>(FmtE4M3::encode(x)); }
-HX_HD void from_f32(float x, e5m2* out) { out->b = static_cast<uint8_t>(FmtE5M2::encode(x)); }
+// On the device the fp8 encoders use the hardware converter, which rounds to nearest even
+// (subnormals included) but saturates at the largest finite value; the library's rule for
+// values that round past it (NaN with the sign for e4m3fn, infinity for e5m2) and its
+// canonical NaN codes are patched in. 464 is the tie that still rounds down to 448;
+// 61440 is the tie that rounds up past 57344. Checked against the software encoder for all
+// 2^32 inputs by tests/test_device_math_gpu.py.
+HX_HD void from_f32(float x, e4m3* out) {
+#if defined(__CUDA_ARCH__)
+  unsigned short pair;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(0.0f), "f"(x));
+  const uint32_t u = f32_bits(x), a = u & 0x7fffffffu;
+  uint8_t r = static_cast<uint8_t>(pair & 0xffu);
+  if (a > 0x43e80000u) r = a > 0x7f800000u ? 0x7f : static_cast<uint8_t>(((u >> 24) & 0x80u) | 0x7fu);
+  out->b = r;
+#else
+  out->b = static_cast<uint8_t>(FmtE4M3::encode(x));
+#endif
+}
+HX_HD void from_f32(float x, e5m2* out) {
+#if defined(__CUDA_ARCH__)
+  unsigned short pair;
+  asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(0.0f), "f"(x));
+  const uint32_t u = f32_bits(x), a = u & 0x7fffffffu;
+  uint8_t r = static_cast<uint8_t>(pair & 0xffu);
+  if (a >= 0x47700000u) r = a > 0x7f800000u ? 0x7e : static_cast<uint8_t>(((u >> 24) & 0x80u) | 0x7cu);
+  out->b = r;
+#else
+  out->b = static_cast<uint8_t>(FmtE5M2::encode(x));
+#endif
+}
 
 }  // namespace hx
