@@ -205,6 +205,17 @@ def main() -> int:
     e2e_ms = timed(e2e_step, max(3, args.steps // 2), 3)
     e2e_value = nbytes / (e2e_ms * 1e-3) / 1e9 * factor
 
+    # ---- extras: the same step with bit-exactness switched off (NVLS in-switch reduction) -------
+    fast = None
+    if comm is not None and world > 2 and args.exact and "nvls" in info["kind"]:
+        comm.tune(variant=0, exact=False)
+        dst.copy_(src)
+        fast_ms = timed(lambda: allreduce(dst, dst), args.steps, 3)
+        fast = {"value": round(nbytes / (fast_ms * 1e-3) / 1e9 * factor, 2), "unit": "GB/s",
+                "ms_per_step": round(fast_ms, 4), "variant": comm.device_info()["variant"],
+                "note": "HXCCL_EXACT=0: float sums combined by the switch, order unspecified"}
+        comm.tune(variant=0, exact=True)
+
     # ---- extras: latency and a short sweep ------------------------------------------------------
     sweep = []
     if not args.no_sweep:
@@ -239,7 +250,7 @@ def main() -> int:
             "algbw_GBps": round(algbw, 2),
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "ms_per_step": round(e2e_ms, 4),
                     "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": host_out.numel() * es},
-            "gpu_launches": int(launches), "clocks": clocks, "sweep": sweep, "async_error": err,
+            "gpu_launches": int(launches), "clocks": clocks, "fast_mode": fast, "sweep": sweep, "async_error": err,
         }
         print(json.dumps(line))
     return 0

@@ -1,6 +1,8 @@
 // Narrow floating-point formats: fp16, bf16, fp8 e4m3fn and fp8 e5m2, converted to and from
-// fp32 with integer bit operations only, so the host build and the sm_100a kernels give the
-// same bits for every input.
+// fp32. The reference implementation (NarrowFmt) uses integer bit operations only and runs on
+// host and device alike; the device entry points (to_f32 / from_f32) take the hardware
+// converters where they exist and patch the cases in which hardware and rules differ, and are
+// checked against NarrowFmt for every input on the GPU.
 //
 // Rules (they are the reference's, src/fp.h:12-59, stated here as a specification):
 //   * decode is exact; an IEEE-style format (fp16, bf16, e5m2) has inf and NaN in its all-ones
@@ -61,7 +63,9 @@ struct NarrowFmt {
     if (IEEE && e == kExpMask) return bits_f32(m ? 0x7fc00000u : (s | 0x7f800000u));
     if (!IEEE && e == kExpMask && m == kManMask) return bits_f32(0x7fc00000u);
     if (e == 0) {
-      // subnormal: m * 2^(kEmin - M), exact in fp32 for every format here
+      // a format with fp32's exponent range (bf16) has fp32's subnormals: only the width differs
+      if (kBias == 127) return bits_f32(s | (m << (23 - M)));
+      // subnormal: m * 2^(kEmin - M), exact in fp32 for every other format here
       const float scale = bits_f32(static_cast<uint32_t>(kEmin - M + 127) << 23);
       const float mag = static_cast<float>(m) * scale;
       return bits_f32(f32_bits(mag) | s);
