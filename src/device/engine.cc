@@ -55,8 +55,10 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
     const XchgArgs* a = stage(args, st, &rc);
     return rc != cudaSuccess ? rc : launch_xchg_fold(dt, a, shape(g), st);
   }
-  // the three-role pipeline measured faster than the single-role kernels only beyond two ranks
-  const bool roles = bytes >= tune.roles_min && tune.max_ctas >= 3 && n() > 2;
+  // The three-role pipeline wins for the multicast reduction from three ranks on; for the
+  // exact two-shot it measured faster than the single-role kernel only on eight ranks.
+  const bool roles = bytes >= tune.roles_min && tune.max_ctas >= 3 &&
+                     (var == kVarNvls ? n() > 2 : n() >= tune.roles_min_ranks);
   const Geometry g = roles ? plan_roles(bytes, n(), views[0].half_bytes, tune)
                            : plan_sliced(bytes, n(), views[0].half_bytes, tune);
   if (var == kVarNvls) {

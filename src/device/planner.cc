@@ -59,6 +59,7 @@ bool set_knob(Tuning* t, const char* name, long v) {
   else if (k == "threads") t->threads = (v == 256 || v == 512) ? int(v) : 0;
   else if (k == "roles_min") t->roles_min = size_t(v);
   else if (k == "roles_sub") t->roles_sub = size_t(std::max(16L, v / 16 * 16));
+  else if (k == "roles_min_ranks") t->roles_min_ranks = int(std::max(2L, v));
   else if (k == "exact") t->exact = v != 0;
   else if (k == "nvls_gather") t->nvls_gather = v != 0;
   else return false;
@@ -92,7 +93,11 @@ Geometry plan_sliced(size_t bytes, int n, size_t half_bytes, const Tuning& t) {
 
 Geometry plan_roles(size_t bytes, int n, size_t half_bytes, const Tuning& t) {
   Geometry g;
-  const int cap = std::max(3, std::min(t.max_ctas, kMaxCtas));
+  // Unless told otherwise the pipeline runs 256-thread CTAs, two per SM: each role then has
+  // twice as many CTAs issuing link traffic, which measured faster than 512-thread CTAs.
+  g.threads = t.threads ? t.threads : 256;
+  const int per_sm = g.threads <= 256 ? 2 : 1;
+  const int cap = std::max(3, std::min(std::min(per_sm * t.max_ctas, per_sm * t.sm_count - 2), kMaxCtas));
   int lanes = std::max(1, cap / 3);
   lanes = int(std::min<size_t>(lanes, std::max<size_t>(1, ceil_div(bytes, size_t(n) * 16 * 1024))));
   // a ring buffer holds the staged inputs in its first half and the results in its second
@@ -102,7 +107,6 @@ Geometry plan_roles(size_t bytes, int n, size_t half_bytes, const Tuning& t) {
   g.ctas = 3 * lanes;
   g.steps = int(std::max<size_t>(1, ceil_div(bytes, g.sub_bytes * lanes * n)));
   g.epochs = g.steps + 1;
-  g.threads = t.threads ? t.threads : 512;
   return g;
 }
 

@@ -34,6 +34,8 @@ struct Tuning {
   size_t sub_max = 512 * 1024;        // largest per-CTA share of one pipelined step
   int min_steps = 2;                  // a pipelined launch aims at this many steps at least
   int threads = 0;                    // CTA width of the large launches, 0 = choose
+  int sm_count = 148;                 // SMs of the device (set by the device path)
+  int roles_min_ranks = 8;            // exact two-shot: role pipeline only from this many ranks
   size_t roles_min = 96u << 20;       // AllReduce: from here the three-role pipeline
   size_t roles_sub = 64 * 1024;       // its per-lane share of a slice per step
 };

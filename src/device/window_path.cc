@@ -78,6 +78,8 @@ hxcclResult_t WindowPath::setup_local() {
   if (t.threads != 256 && t.threads != 512) t.threads = 0;
   t.max_ctas = std::min(t.max_ctas, max_resident_ctas(t.threads ? t.threads : 512));
   t.min_steps = int(std::max(2L, env_long("HXCCL_MIN_STEPS", t.min_steps)));
+  t.sm_count = max_resident_ctas(512);
+  t.roles_min_ranks = int(std::max(2L, env_long("HXCCL_ROLES_MIN_RANKS", t.roles_min_ranks)));
   t.oneshot_max = size_t(env_long("HXCCL_ONESHOT_MAX", long(t.oneshot_max)));
   t.nvls_min = size_t(env_long("HXCCL_NVLS_MIN", long(t.nvls_min)));
   t.single_sub_max = size_t(env_long("HXCCL_SINGLE_SUB_MAX", long(t.single_sub_max)));

@@ -104,6 +104,8 @@ hxcclResult_t hxcclWorldCreate(hxcclWorld_t* out, int n, int window_mb, int wait
   }
   // the whole world must be co-resident: a cooperative launch refuses anything larger
   w->eng.tune.max_ctas = std::max(1, std::min(64, world_cta_budget() / n));
+  w->eng.tune.threads = 512;  // one CTA per SM: the budget above counts on it
+  w->eng.tune.roles_min_ranks = 2;
   *out = w;
   return cudaDeviceSynchronize() == cudaSuccess ? hxcclSuccess : hxcclUnhandledCudaError;
 }
