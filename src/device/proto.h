@@ -14,11 +14,13 @@
 //   [p2p]      double-buffered Send/Recv slots, one set per (sender, worker)
 //   [half 0] [half 1]  collective staging, alternating per step
 //
-// Steps. A collective launch runs K >= 1 steps; the communicator numbers all steps of all its
-// launches with one increasing epoch, the same on every rank. Step e stages in half e & 1.
-// In every step each rank signals each rank, so a writer that reached step e+2 has seen the
-// step e+1 signal of the window's owner, which that owner sent only after it finished reading
-// step e: the half is free again without any extra handshake. Flags only ever grow.
+// Steps. A collective launch runs K >= 1 steps; the communicator numbers the steps (and the
+// opening / closing hand-shakes of multi-step launches) of all its launches with one increasing
+// epoch, the same on every rank. A single-step launch stages in half e & 1: in every step each
+// rank signals each rank, so a writer that reached epoch e+2 has seen the e+1 signal of the
+// window's owner, which that owner sent only after it finished reading epoch e, and the half is
+// free again without any extra hand-shake. A multi-step launch owns both halves as a ring of
+// four buffers between its two hand-shakes (kernels/coll_body.cuh). Flags only ever grow.
 //
 // All waits are bounded: a wait that runs out of time records a status in pinned host memory,
 // raises the abort word in every peer's window (so they stop too) and the kernel returns.
