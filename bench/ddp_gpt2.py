@@ -31,7 +31,7 @@ def main() -> int:
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--tiny", action="store_true", help="a two-layer toy model (smoke tests)")
     ap.add_argument("--exact", type=int, default=1)
-    ap.add_argument("--max-ctas", type=int, default=32, help="grid bound of the hxccl kernels during training")
+    ap.add_argument("--max-ctas", type=int, default=48, help="grid bound of the hxccl kernels during training")
     ap.add_argument("--check", action="store_true", help="print the loss of every step")
     args = ap.parse_args()
 

@@ -19,6 +19,8 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--n", type=int, default=2)
     ap.add_argument("--mb", type=int, default=256, help="message size per rank in MiB")
+    ap.add_argument("--bytes", type=int, default=0, help="message size per rank in bytes (overrides --mb)")
+    ap.add_argument("--order", type=int, default=0, help="0 ring order, 1 recursive doubling, -1 by size")
     ap.add_argument("--variant", type=int, default=2, help="1 one-shot, 2 two-shot")
     ap.add_argument("--dtype", default="float32")
     ap.add_argument("--iters", type=int, default=3)
@@ -33,7 +35,7 @@ def main() -> int:
     from hxccl_b200.ops.world import World
 
     tdt = getattr(torch, args.dtype)
-    count = (args.mb << 20) // torch.empty(0, dtype=tdt).element_size()
+    count = max(1, (args.bytes or (args.mb << 20)) // torch.empty(0, dtype=tdt).element_size())
     xs = [(torch.rand(count, device="cuda") * 2 - 1).to(tdt) for _ in range(args.n)]
     ys = [torch.empty_like(x) for x in xs]
     with World(args.n, window_mb=args.window_mb, wait_ms=20000) as w:
@@ -45,7 +47,7 @@ def main() -> int:
         for _ in range(args.iters):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            w.all_reduce(xs, ys, count, dt, op=hx.SUM, order=0)
+            w.all_reduce(xs, ys, count, dt, op=hx.SUM, order=args.order)
             e1.record()
             torch.cuda.synchronize()
             times.append(e0.elapsed_time(e1))
@@ -53,7 +55,7 @@ def main() -> int:
         info = w.info()
     ref = sum(x.double() for x in xs)
     err = float((ys[0].double() - ref).abs().max())
-    print(json.dumps({"n": args.n, "bytes_per_rank": args.mb << 20, "dtype": args.dtype, "variant": info["variant"],
+    print(json.dumps({"n": args.n, "bytes_per_rank": args.bytes or (args.mb << 20), "order": args.order, "dtype": args.dtype, "variant": info["variant"],
                       "ms": [round(t, 3) for t in times], "status_ok": ok, "max_abs_err": err}))
     return 0 if ok else 1
 

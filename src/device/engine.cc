@@ -47,7 +47,9 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
   cudaError_t rc;
   ++launches;
   if (var == kVarOneShot) {
-    const Geometry g = plan_xchg(bytes, n(), views[0].half_bytes, tune);
+    // the recursive-doubling order costs n log n combines per element: give a CTA less of it
+    const Geometry g = plan_xchg(bytes, n(), views[0].half_bytes, tune,
+                                 order == kOrderDoubling ? 2 * 1024 : 16 * 1024);
     std::vector<XchgArgs> args(views.size());
     for (size_t r = 0; r < views.size(); ++r)
       build_allreduce_oneshot(&args[r], views[r], epoch, g, b[r].send, b[r].recv, count, dt, plan, order);

@@ -66,10 +66,10 @@ bool set_knob(Tuning* t, const char* name, long v) {
   return true;
 }
 
-Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t) {
+Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t, size_t cta_bytes) {
   Geometry g;
   const int cap = std::max(1, std::min(t.max_ctas, kMaxCtas));
-  g.ctas = int(std::min<size_t>(cap, std::max<size_t>(1, ceil_div(max_pair, 16 * 1024))));
+  g.ctas = int(std::min<size_t>(cap, std::max<size_t>(1, ceil_div(max_pair, std::max<size_t>(256, cta_bytes)))));
   const size_t fit1 = round_down(round_down(buffer_bytes(half_bytes, 1) / n, 256) / g.ctas, 16);
   const size_t fitr = round_down(round_down(buffer_bytes(half_bytes, 2) / n, 256) / g.ctas, 16);
   split_steps(&g, ceil_div(max_pair, g.ctas), fit1, fitr, t);

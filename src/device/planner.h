@@ -46,7 +46,7 @@ struct Tuning {
 bool set_knob(Tuning* t, const char* name, long value);
 
 // generic exchange where the largest block of any pair is `max_pair` bytes
-Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t);
+Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t, size_t cta_bytes = 16 * 1024);
 // two-shot / NVLS AllReduce of `bytes`
 Geometry plan_sliced(size_t bytes, int n, size_t half_bytes, const Tuning& t);
 // the same as a three-role pipeline: ctas = 3 * lanes, epochs = steps + 1

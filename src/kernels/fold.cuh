@@ -179,6 +179,49 @@ __device__ inline void fold_linear_vectors(char* dst, const FoldShared& sh, int 
   }
 }
 
+// Recursive doubling over N = 2, 4 or 8 ranks (no spare ranks) with everything in registers:
+// the butterfly keeps all N partial values per level because every rank combines with its own
+// value on the left, so the values differ between ranks for non-commutative cases.
+template <typename T, int N>
+__device__ __forceinline__ T fold_doubling_pow2(const T (&x)[N], int rank, int op) {
+  T lv[N];
+#pragma unroll
+  for (int q = 0; q < N; ++q) lv[q] = x[q];
+#pragma unroll
+  for (int bit = 1; bit < N; bit <<= 1) {
+    T nx[N];
+#pragma unroll
+    for (int q = 0; q < N; ++q) nx[q] = apply(lv[q], lv[q ^ bit], op);
+#pragma unroll
+    for (int q = 0; q < N; ++q) lv[q] = nx[q];
+  }
+  T r = lv[0];
+#pragma unroll
+  for (int q = 1; q < N; ++q)
+    if (q == rank) r = lv[q];
+  return r;
+}
+
+// Element-per-thread loop for that order: small messages spread over many threads instead of
+// 16-byte vectors walked lane by lane.
+template <typename T, int N>
+__device__ inline void fold_doubling_elems(char* dst, const FoldShared& sh, int nremote, size_t nbytes,
+                                           const FoldSpec& f, int rank, T scalar) {
+  const size_t total = nbytes / sizeof(T);
+  for (size_t e = threadIdx.x; e < total; e += blockDim.x) {
+    T x[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      x[i] = reinterpret_cast<const T*>(sh.src[i])[e];
+      if (f.premul && i == rank) x[i] = scale(x[i], scalar);
+    }
+    T r = fold_doubling_pow2<T, N>(x, rank, f.op);
+    if (f.postdiv) r = div_trunc(r, f.postdiv);
+    reinterpret_cast<T*>(dst)[e] = r;
+    for (int q = 0; q < nremote; ++q) reinterpret_cast<T*>(sh.remote[q])[e] = r;
+  }
+}
+
 // Folds `nbytes` bytes (whole elements). sh.src[i] points at rank i's data for this range
 // (sh.src[rank] is the unscaled local input), elem0 is the index of the first element in the
 // full vector. The result goes to dst and to each of sh.remote[0..nremote); when sh.mc_dst is
@@ -193,6 +236,12 @@ __device__ inline void cta_fold(char* dst, FoldShared& sh, int nremote, size_t n
   for (int i = 0; i < n; ++i) aligned = aligned && (reinterpret_cast<uintptr_t>(sh.src[i]) & 15u) == 0;
   const size_t nvec = aligned ? nbytes >> 4 : 0;
 
+  if (f.kind == kFoldDoubling && !sh.mc_dst && (n == 2 || n == 4 || n == 8)) {
+    if (n == 2) fold_doubling_elems<T, 2>(dst, sh, nremote, nbytes, f, rank, scalar);
+    else if (n == 4) fold_doubling_elems<T, 4>(dst, sh, nremote, nbytes, f, rank, scalar);
+    else fold_doubling_elems<T, 8>(dst, sh, nremote, nbytes, f, rank, scalar);
+    return;
+  }
   if (f.kind == kFoldLinear && (n == 2 || n == 4 || n == 8)) {
     if (n == 2) fold_linear_vectors<T, 2, 4>(dst, sh, nremote, nvec, elem0, f, rank, scalar);
     else if (n == 4) fold_linear_vectors<T, 4, 2>(dst, sh, nremote, nvec, elem0, f, rank, scalar);
