@@ -3,7 +3,7 @@
 // interpreter overhead). The program forks its own ranks, hands the unique id around through
 // pipes, and times with CUDA events between barriers; every figure is the maximum over ranks.
 //
-//   hx_perf -g 8 [-o allreduce|allgather|reducescatter|alltoall|broadcast|sendrecv]
+//   hx_perf -g 8 [-o allreduce|allgather|reducescatter|alltoall|broadcast|reduce|gather|scatter|sendrecv]
 //           [-b 8] [-e 1073741824] [-f 2] [-n 20] [-w 5] [-t float|bf16|half|int32|...] [-r sum|max|avg|...]
 //           [-H]   host buffers instead of device buffers
 //
@@ -85,7 +85,8 @@ int run_rank(const Options& o, int rank, const hxcclUniqueId& id) {
   size_t es = 4;
   const hxcclDataType_t dt = parse_type(o.type, &es);
   const hxcclRedOp_t red = parse_red(o.red);
-  const bool gathers = o.op == "allgather", scatters = o.op == "reducescatter" || o.op == "alltoall";
+  const bool gathers = o.op == "allgather" || o.op == "gather";
+  const bool scatters = o.op == "reducescatter" || o.op == "alltoall" || o.op == "scatter";
   const size_t cap = o.max_bytes * (gathers || scatters ? 1 : 1) + 256;
   char *send = nullptr, *recv = nullptr;
   if (o.host) {
@@ -121,6 +122,9 @@ int run_rank(const Options& o, int rank, const hxcclUniqueId& id) {
       else if (o.op == "reducescatter") CK(hxcclReduceScatter(send, recv, count, dt, red, g_comm, st));
       else if (o.op == "alltoall") CK(hxcclAlltoAll(send, recv, count, dt, g_comm, st));
       else if (o.op == "broadcast") CK(hxcclBroadcast(send, recv, count, dt, 0, g_comm, st));
+      else if (o.op == "reduce") CK(hxcclReduce(send, recv, count, dt, red, 0, g_comm, st));
+      else if (o.op == "gather") CK(hxcclGather(send, recv, count, dt, 0, g_comm, st));
+      else if (o.op == "scatter") CK(hxcclScatter(send, recv, count, dt, 0, g_comm, st));
       else if (o.op == "sendrecv") {
         CK(hxcclGroupStart());
         CK(hxcclSend(send, count, dt, (rank + 1) % n, g_comm, st));
@@ -156,7 +160,7 @@ int run_rank(const Options& o, int rank, const hxcclUniqueId& id) {
     const double moved = double(count) * es * (gathers || scatters ? n : 1);
     const double algbw = moved / (worst * 1e-6) / 1e9;
     const double f = o.op == "allreduce" ? 2.0 * (n - 1) / n
-                     : (o.op == "broadcast" || o.op == "sendrecv") ? 1.0 : double(n - 1) / n;
+                     : (o.op == "broadcast" || o.op == "sendrecv" || o.op == "reduce") ? 1.0 : double(n - 1) / n;
     if (rank == 0)
       std::printf("  %12zu %12zu %12.2f %12.2f %12.2f\n", size_t(moved), count, worst, algbw, algbw * f);
     barrier();

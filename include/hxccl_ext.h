@@ -19,7 +19,8 @@ extern "C" {
  * (1 one-shot, 2 two-shot, 3 NVLS). launches: kernels launched by this communicator so far. */
 hxcclResult_t hxcclCommDeviceInfo(hxcclComm_t comm, char* kind, size_t kind_len, int* variant,
                                   unsigned long long* launches);
-/* Forces the AllReduce variant of later calls (0 auto, 1 one-shot, 2 two-shot, 3 NVLS), the
+/* Forces the AllReduce variant of later calls (0 auto, 1 one-shot, 2 two-shot, 3 NVLS,
+ * 6 neighbour ring), the
  * exactness mode (1 = floats match the host path bit for bit) and the largest grid (0 keeps it).
  * Every rank must make the same call. */
 hxcclResult_t hxcclCommTune(hxcclComm_t comm, int variant, int exact, int max_ctas);

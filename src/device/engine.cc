@@ -57,6 +57,16 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
     const XchgArgs* a = stage(args, st, &rc);
     return rc != cudaSuccess ? rc : launch_xchg_fold(dt, a, shape(g), st);
   }
+  if (var == kVarRing) {
+    const size_t es = dtype_size(dt);
+    const Geometry g = plan_ring((count + n() - 1) / n() * es, n(), views[0].half_bytes, tune);
+    std::vector<TwoShotArgs> args(views.size());
+    for (size_t r = 0; r < views.size(); ++r)
+      build_allreduce_twoshot(&args[r], views[r], epoch, g, b[r].send, b[r].recv, count, dt, plan, order, false);
+    epoch += g.epochs;
+    const TwoShotArgs* a = stage(args, st, &rc);
+    return rc != cudaSuccess ? rc : launch_ring(dt, a, shape(g), st);
+  }
   // The three-role pipeline wins for the multicast reduction from three ranks on; for the
   // exact two-shot it measured faster than the single-role kernel only on eight ranks.
   const bool roles = bytes >= tune.roles_min && tune.max_ctas >= 3 &&

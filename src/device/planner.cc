@@ -110,6 +110,21 @@ Geometry plan_roles(size_t bytes, int n, size_t half_bytes, const Tuning& t) {
   return g;
 }
 
+Geometry plan_ring(size_t max_block, int n, size_t half_bytes, const Tuning& t) {
+  Geometry g;
+  const int cap = std::max(1, std::min(t.max_ctas, kMaxCtas));
+  g.ctas = int(std::min<size_t>(cap, std::max<size_t>(1, ceil_div(max_block, 16 * 1024))));
+  // the staging area holds one slot per hop (2n - 2) and CTA
+  const size_t hops = size_t(2 * n - 2);
+  const size_t fit = round_down(2 * half_bytes / std::max<size_t>(1, hops) / g.ctas, 256);
+  const size_t want = std::max<size_t>(16, round_up(ceil_div(max_block, g.ctas), 16));
+  g.sub_bytes = std::max<size_t>(16, std::min(want, std::min(round_up(t.sub_max, 16), fit)));
+  g.steps = int(std::max<size_t>(1, ceil_div(want, g.sub_bytes)));
+  g.epochs = g.steps * int(hops) + 2;
+  g.threads = t.threads ? t.threads : threads_for(g.sub_bytes);
+  return g;
+}
+
 FoldSpec make_fold(const OpPlan& plan, int kind) {
   FoldSpec f{};
   f.kind = kind;
@@ -127,6 +142,7 @@ int choose_variant(size_t bytes, int dt, const OpPlan& plan, int n, const Tuning
                        nvls_mode(dt, plan.base) != kNvNone && (is_integer(dt) || !t.exact);
   if (forced == kVarNvls && nvls_ok) return kVarNvls;
   if (forced == kVarOneShot || forced == kVarTwoShot) return forced;
+  if (forced == kVarRing && n >= 2 && bytes > 0) return kVarRing;
   // with two ranks the multicast reduction measured slower than two-shot at every size
   if (nvls_ok && bytes >= t.nvls_min && n > 2) return kVarNvls;
   return bytes <= t.oneshot_max ? kVarOneShot : kVarTwoShot;

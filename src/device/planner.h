@@ -21,7 +21,8 @@ struct Geometry {
 };
 
 // AllReduce transport variants
-enum : int { kVarAuto = 0, kVarOneShot = 1, kVarTwoShot = 2, kVarNvls = 3, kVarTwoShotRoles = 4, kVarNvlsRoles = 5 };
+enum : int { kVarAuto = 0, kVarOneShot = 1, kVarTwoShot = 2, kVarNvls = 3, kVarTwoShotRoles = 4, kVarNvlsRoles = 5,
+       kVarRing = 6 };
 
 struct Tuning {
   int max_ctas = 128;         // upper bound of any collective grid
@@ -51,6 +52,10 @@ Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t, s
 Geometry plan_sliced(size_t bytes, int n, size_t half_bytes, const Tuning& t);
 // the same as a three-role pipeline: ctas = 3 * lanes, epochs = steps + 1
 Geometry plan_roles(size_t bytes, int n, size_t half_bytes, const Tuning& t);
+
+// neighbour ring over blocks of at most `max_block` bytes: steps = rounds,
+// epochs = rounds * (2n - 2) + 2
+Geometry plan_ring(size_t max_block, int n, size_t half_bytes, const Tuning& t);
 
 FoldSpec make_fold(const OpPlan& plan, int kind);
 

@@ -92,6 +92,7 @@ hxcclResult_t WindowPath::setup_local() {
     if (!std::strcmp(v, "oneshot")) eng_.forced_variant = kVarOneShot;
     if (!std::strcmp(v, "twoshot")) eng_.forced_variant = kVarTwoShot;
     if (!std::strcmp(v, "nvls")) eng_.forced_variant = kVarNvls;
+    if (!std::strcmp(v, "ring")) eng_.forced_variant = kVarRing;
   }
   return hxcclSuccess;
 }

@@ -54,6 +54,7 @@ cudaError_t launch_p2p(const P2pArgs* args, LaunchShape s, cudaStream_t st) {
   extern template cudaError_t launch_xchg_fold_t<T>(const XchgArgs*, LaunchShape, cudaStream_t); \
   extern template cudaError_t launch_twoshot_t<T>(const TwoShotArgs*, LaunchShape, cudaStream_t); \
   extern template cudaError_t launch_twoshot_roles_t<T>(const TwoShotArgs*, LaunchShape, cudaStream_t); \
+  extern template cudaError_t launch_ring_t<T>(const TwoShotArgs*, LaunchShape, cudaStream_t);  \
   extern template cudaError_t launch_reduce_t<T>(void*, const void*, size_t, int, cudaStream_t); \
   extern template cudaError_t launch_scale_t<T>(void*, const void*, size_t, unsigned long long, \
                                                 cudaStream_t);                                  \
@@ -84,6 +85,11 @@ cudaError_t launch_twoshot(int dt, const TwoShotArgs* args, LaunchShape s, cudaS
 cudaError_t launch_twoshot_roles(int dt, const TwoShotArgs* args, LaunchShape s, cudaStream_t st) {
   cudaError_t rc = cudaErrorInvalidValue;
   HX_DISPATCH_DTYPE(dt, rc = launch_twoshot_roles_t<T>(args, s, st))
+  return rc;
+}
+cudaError_t launch_ring(int dt, const TwoShotArgs* args, LaunchShape s, cudaStream_t st) {
+  cudaError_t rc = cudaErrorInvalidValue;
+  HX_DISPATCH_DTYPE(dt, rc = launch_ring_t<T>(args, s, st))
   return rc;
 }
 cudaError_t launch_reduce(void* dst, const void* src, size_t count, int dt, int op, cudaStream_t st) {

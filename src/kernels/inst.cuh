@@ -3,6 +3,7 @@
 #pragma once
 #include "kernels/coll_body.cuh"
 #include "kernels/roles_body.cuh"
+#include "kernels/ring_body.cuh"
 #include "kernels/launch.h"
 
 namespace hx {
@@ -39,6 +40,17 @@ __global__ void __launch_bounds__(512) k_twoshot_roles_world(const TwoShotArgs* 
   twoshot_roles_body<T>(a[blockIdx.y], blockIdx.x, gridDim.x, sh);
 }
 
+template <typename T>
+__global__ void __launch_bounds__(512) k_ring(const __grid_constant__ TwoShotArgs a) {
+  __shared__ FoldShared sh;
+  ring_body<T>(a, blockIdx.x, gridDim.x, sh);
+}
+template <typename T>
+__global__ void __launch_bounds__(512) k_ring_world(const TwoShotArgs* a) {
+  __shared__ FoldShared sh;
+  ring_body<T>(a[blockIdx.y], blockIdx.x, gridDim.x, sh);
+}
+
 template <typename Args>
 cudaError_t launch_world(const void* kernel, const Args* dev_args, LaunchShape s, cudaStream_t st) {
   void* params[] = {const_cast<Args**>(&dev_args)};
@@ -65,6 +77,13 @@ cudaError_t launch_twoshot_roles_t(const TwoShotArgs* args, LaunchShape s, cudaS
   if (s.world)
     return launch_world(reinterpret_cast<const void*>(&k_twoshot_roles_world<T>), args, s, st);
   k_twoshot_roles<T><<<s.ctas, s.threads, 0, st>>>(*args);
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_ring_t(const TwoShotArgs* args, LaunchShape s, cudaStream_t st) {
+  if (s.world) return launch_world(reinterpret_cast<const void*>(&k_ring_world<T>), args, s, st);
+  k_ring<T><<<s.ctas, s.threads, 0, st>>>(*args);
   return cudaGetLastError();
 }
 
@@ -137,6 +156,7 @@ cudaError_t launch_divide_t(void* buf, size_t count, int divisor, cudaStream_t s
   template cudaError_t launch_xchg_fold_t<T>(const XchgArgs*, LaunchShape, cudaStream_t);    \
   template cudaError_t launch_twoshot_t<T>(const TwoShotArgs*, LaunchShape, cudaStream_t);   \
   template cudaError_t launch_twoshot_roles_t<T>(const TwoShotArgs*, LaunchShape, cudaStream_t); \
+  template cudaError_t launch_ring_t<T>(const TwoShotArgs*, LaunchShape, cudaStream_t);      \
   template cudaError_t launch_reduce_t<T>(void*, const void*, size_t, int, cudaStream_t);    \
   template cudaError_t launch_scale_t<T>(void*, const void*, size_t, unsigned long long,     \
                                          cudaStream_t);                                      \

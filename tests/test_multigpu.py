@@ -49,7 +49,8 @@ def test_allreduce_exact(n):
     cases = []
     for dt in range(12):
         for op in (L.SUM, L.MAX, L.AVG):
-            for count, variant in ((1, 0), (4099, 1), (4099, 2), ((2 << 20) // L.DTYPE_SIZE[dt] + 3, 0)):
+            for count, variant in ((1, 0), (4099, 1), (4099, 2), ((2 << 20) // L.DTYPE_SIZE[dt] + 3, 0),
+                                   ((300 << 10) // L.DTYPE_SIZE[dt] + 5, 6)):  # 6 = neighbour ring
                 cases.append((dt, op, count, variant, len(cases)))
     res = run_ranks(n, _allreduce_body, cases, gpus=True, timeout=120)
     assert res[0][0]["kind"].startswith("window"), res[0][0]

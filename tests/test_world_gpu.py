@@ -116,6 +116,45 @@ def test_allreduce_three_role_pipeline(worlds, n):
         w.knob("roles_sub", 65536)
 
 
+@pytest.mark.parametrize("n", [2, 3, 4, 8])
+def test_allreduce_neighbour_ring(worlds, n):
+    """The ring kernel (every hop a store into the right neighbour's window): every type and
+    operator on small counts (blocks of zero and one element included), then many rounds with
+    small slots, odd sizes, in place, PreMulSum and both Avg forms."""
+    w = worlds(n)
+    w.tune(variant=6, exact=True)
+    for dt in ALL_DT:
+        for op in (L.SUM, L.PROD, L.MAX, L.MIN, L.AVG):
+            for count in (1, 7, 4099):
+                xs = rand_inputs(n, count, dt, seed=dt * 100 + op * 10 + n + 5)
+                send = [to_dev(x) for x in xs]
+                recv = [torch.zeros_like(s) for s in send]
+                w.all_reduce(send, recv, count, dt, op=op, order=0)
+                torch.cuda.synchronize()
+                assert w.info()["variant"] == 6
+                want = oracle.allreduce(xs, dt, op, order=0)
+                for r in range(n):
+                    assert np.array_equal(back(recv[r], dt), want[r]), (n, dt, op, count, r)
+    w.knob("sub_max", 4096)
+    try:
+        for dt, op, scalar, count in ((L.FLOAT32, L.SUM, None, (3 << 20) // 4 + 3), (L.BFLOAT16, L.AVG, None, 700001),
+                                      (L.INT32, L.AVG, None, 400003), (L.FLOAT8E4M3, L.SUM, None, 1 << 20),
+                                      (L.FLOAT16, L.SUM, np.array([0x3000], dtype=np.uint16), 500000)):
+            xs = rand_inputs(n, count, dt, seed=57 + dt)
+            if dt in FLOATS:
+                for x in xs:
+                    x &= x.dtype.type(~(1 << (8 * L.DTYPE_SIZE[dt] - 2)) & ((1 << (8 * L.DTYPE_SIZE[dt])) - 1))
+            buf = [to_dev(x) for x in xs]
+            w.all_reduce(buf, buf, count, dt, op=op, scalar=scalar, order=0)
+            torch.cuda.synchronize()
+            want = oracle.allreduce(xs, dt, op, order=0, scalar=scalar)
+            for r in range(n):
+                assert np.array_equal(back(buf[r], dt), want[r]), (n, dt, op, count, r)
+        assert all(w.status(r) == (0, 0) for r in range(n))
+    finally:
+        w.knob("sub_max", 512 * 1024)
+
+
 @pytest.mark.parametrize("n", [2, 3, 8])
 def test_reducescatter_and_reduce(worlds, n):
     w = worlds(n)
