@@ -216,6 +216,17 @@ def main() -> int:
                 "note": "HXCCL_EXACT=0: float sums combined by the switch, order unspecified"}
         comm.tune(variant=0, exact=True)
 
+    # ---- extras: the same step through the neighbour-ring kernel (bit-exact like the headline) --
+    ring = None
+    if comm is not None and world > 1 and args.exact:
+        comm.tune(variant=6, exact=True)
+        dst.copy_(src)
+        ring_ms = timed(lambda: allreduce(dst, dst), args.steps, 3)
+        ring = {"value": round(nbytes / (ring_ms * 1e-3) / 1e9 * factor, 2), "unit": "GB/s",
+                "ms_per_step": round(ring_ms, 4), "variant": comm.device_info()["variant"],
+                "note": "HXCCL_VARIANT=ring: reduce-scatter and all-gather around the ring, same bits"}
+        comm.tune(variant=0, exact=True)
+
     # ---- extras: latency and a short sweep ------------------------------------------------------
     sweep = []
     if not args.no_sweep:
@@ -250,7 +261,7 @@ def main() -> int:
             "algbw_GBps": round(algbw, 2),
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "ms_per_step": round(e2e_ms, 4),
                     "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": host_out.numel() * es},
-            "gpu_launches": int(launches), "clocks": clocks, "fast_mode": fast, "sweep": sweep, "async_error": err,
+            "gpu_launches": int(launches), "clocks": clocks, "fast_mode": fast, "ring_mode": ring, "sweep": sweep, "async_error": err,
         }
         print(json.dumps(line))
     return 0

@@ -59,6 +59,8 @@ bool set_knob(Tuning* t, const char* name, long v) {
   else if (k == "threads") t->threads = (v == 256 || v == 512) ? int(v) : 0;
   else if (k == "roles_min") t->roles_min = size_t(v);
   else if (k == "roles_sub") t->roles_sub = size_t(std::max(16L, v / 16 * 16));
+  else if (k == "ring_min") t->ring_min = size_t(std::max(0L, v));
+  else if (k == "ring_max_ranks") t->ring_max_ranks = int(std::max(2L, v));
   else if (k == "roles_min_ranks") t->roles_min_ranks = int(std::max(2L, v));
   else if (k == "exact") t->exact = v != 0;
   else if (k == "nvls_gather") t->nvls_gather = v != 0;
@@ -145,6 +147,7 @@ int choose_variant(size_t bytes, int dt, const OpPlan& plan, int n, const Tuning
   if (forced == kVarRing && n >= 2 && bytes > 0) return kVarRing;
   // with two ranks the multicast reduction measured slower than two-shot at every size
   if (nvls_ok && bytes >= t.nvls_min && n > 2) return kVarNvls;
+  if (t.ring_min && bytes >= t.ring_min && n >= 2 && n <= t.ring_max_ranks) return kVarRing;
   return bytes <= t.oneshot_max ? kVarOneShot : kVarTwoShot;
 }
 

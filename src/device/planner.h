@@ -39,10 +39,13 @@ struct Tuning {
   int roles_min_ranks = 8;            // exact two-shot: role pipeline only from this many ranks
   size_t roles_min = 96u << 20;       // AllReduce: from here the three-role pipeline
   size_t roles_sub = 64 * 1024;       // its per-lane share of a slice per step
+  size_t ring_min = 0;                // AllReduce: from here the neighbour ring (0 = only when forced)
+  int ring_max_ranks = 2;             // ... on communicators of at most this many ranks
 };
 
 // Sets one tuning knob by name ("max_ctas", "oneshot_max", "nvls_min", "single_sub_max",
-// "sub_max", "min_steps", "threads", "roles_min", "roles_sub", "exact", "nvls_gather");
+// "sub_max", "min_steps", "threads", "roles_min", "roles_sub", "ring_min", "ring_max_ranks",
+// "exact", "nvls_gather");
 // false for an unknown name.
 bool set_knob(Tuning* t, const char* name, long value);
 

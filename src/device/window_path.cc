@@ -86,6 +86,8 @@ hxcclResult_t WindowPath::setup_local() {
   t.sub_max = size_t(std::max(16L, env_long("HXCCL_SUB_MAX", long(t.sub_max)) / 16 * 16));
   t.roles_min = size_t(env_long("HXCCL_ROLES_MIN", long(t.roles_min)));
   t.roles_sub = size_t(std::max(16L, env_long("HXCCL_ROLES_SUB", long(t.roles_sub))));
+  t.ring_min = size_t(std::max(0L, env_long("HXCCL_RING_MIN", long(t.ring_min))));
+  t.ring_max_ranks = int(std::max(2L, env_long("HXCCL_RING_MAX_RANKS", t.ring_max_ranks)));
   t.exact = env_long("HXCCL_EXACT", 1) != 0;
   t.nvls_gather = env_long("HXCCL_NVLS_GATHER", 1) != 0;
   if (const char* v = std::getenv("HXCCL_VARIANT")) {

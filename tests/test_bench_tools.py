@@ -1,0 +1,29 @@
+"""The plotting tool turns benchmark output (JSON lines of bench/sweep.py, tables of
+bench/hx_perf) into well-formed SVG."""
+import json
+import os
+import subprocess
+import sys
+import xml.dom.minidom
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_plot_curves_and_phases(tmp_path):
+    src = tmp_path / "rows.jsonl"
+    rows = [{"config": c, "bytes": b, "us": 10.0, "busbw_GBps": v,
+             "trace_us": {"in": 1, "sigA": 0.5, "waitA": 2, "mid": 3, "sigB": 0.5, "waitB": 1, "out": 2, "all": 10}}
+            for c, b, v in (("default", 65536, 5.0), ("default", 1 << 28, 570.0), ("nccl", 65536, 4.0), ("nccl", 1 << 28, 630.0))]
+    text = "\n".join(json.dumps(r) for r in rows)
+    text += ("\n# hx_perf  op=allreduce type=float red=sum ranks=2 buffers=device path=window iters=20 warmup=5\n"
+             "#        bytes        count     time(us)  algbw(GB/s)  busbw(GB/s)\n"
+             "         65536        16384        17.07         3.84         3.84\n"
+             "       1048576       262144        26.12        40.15        40.15\n")
+    src.write_text(text)
+    for kind, tag, least in (("curves", "path", 3), ("phases", "rect", 4 * 7)):
+        out = tmp_path / f"{kind}.svg"
+        subprocess.run([sys.executable, os.path.join(ROOT, "bench", "plot.py"), kind, str(src), "-o", str(out)],
+                       check=True, timeout=60)
+        doc = xml.dom.minidom.parse(str(out))
+        assert doc.documentElement.tagName == "svg"
+        assert len(doc.getElementsByTagName(tag)) >= least
