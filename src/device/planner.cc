@@ -60,6 +60,7 @@ bool set_knob(Tuning* t, const char* name, long v) {
   else if (k == "roles_min") t->roles_min = size_t(v);
   else if (k == "roles_sub") t->roles_sub = size_t(std::max(16L, v / 16 * 16));
   else if (k == "ring_min") t->ring_min = size_t(std::max(0L, v));
+  else if (k == "ring_sub") t->ring_sub = size_t(std::max(16L, v / 16 * 16));
   else if (k == "ring_max_ranks") t->ring_max_ranks = int(std::max(2L, v));
   else if (k == "roles_min_ranks") t->roles_min_ranks = int(std::max(2L, v));
   else if (k == "exact") t->exact = v != 0;
@@ -120,7 +121,7 @@ Geometry plan_ring(size_t max_block, int n, size_t half_bytes, const Tuning& t) 
   const size_t hops = size_t(2 * n - 2);
   const size_t fit = round_down(2 * half_bytes / std::max<size_t>(1, hops) / g.ctas, 256);
   const size_t want = std::max<size_t>(16, round_up(ceil_div(max_block, g.ctas), 16));
-  g.sub_bytes = std::max<size_t>(16, std::min(want, std::min(round_up(t.sub_max, 16), fit)));
+  g.sub_bytes = std::max<size_t>(16, std::min(want, std::min(round_up(t.ring_sub, 16), fit)));
   g.steps = int(std::max<size_t>(1, ceil_div(want, g.sub_bytes)));
   g.epochs = g.steps * int(hops) + 2;
   g.threads = t.threads ? t.threads : threads_for(g.sub_bytes);

@@ -32,19 +32,20 @@ struct Tuning {
   bool nvls_gather = true;    // two-shot publishes results through the multicast alias
   size_t nvls_min = 512 * 1024;    // AllReduce: from here NVLS, when allowed for (dtype, op)
   size_t single_sub_max = 256 * 1024;  // per-CTA share up to which a launch runs as one step
-  size_t sub_max = 512 * 1024;        // largest per-CTA share of one pipelined step
-  int min_steps = 2;                  // a pipelined launch aims at this many steps at least
+  size_t sub_max = 256 * 1024;        // largest per-CTA share of one pipelined step
+  int min_steps = 4;                  // a pipelined launch aims at this many steps at least
   int threads = 0;                    // CTA width of the large launches, 0 = choose
   int sm_count = 148;                 // SMs of the device (set by the device path)
   int roles_min_ranks = 8;            // exact two-shot: role pipeline only from this many ranks
   size_t roles_min = 96u << 20;       // AllReduce: from here the three-role pipeline
   size_t roles_sub = 64 * 1024;       // its per-lane share of a slice per step
-  size_t ring_min = 0;                // AllReduce: from here the neighbour ring (0 = only when forced)
+  size_t ring_min = 128u << 20;       // AllReduce: from here the neighbour ring (0 = only when forced)
   int ring_max_ranks = 2;             // ... on communicators of at most this many ranks
+  size_t ring_sub = 512 * 1024;       // largest per-CTA share of one ring hop
 };
 
 // Sets one tuning knob by name ("max_ctas", "oneshot_max", "nvls_min", "single_sub_max",
-// "sub_max", "min_steps", "threads", "roles_min", "roles_sub", "ring_min", "ring_max_ranks",
+// "sub_max", "min_steps", "threads", "roles_min", "roles_sub", "ring_min", "ring_max_ranks", "ring_sub",
 // "exact", "nvls_gather");
 // false for an unknown name.
 bool set_knob(Tuning* t, const char* name, long value);

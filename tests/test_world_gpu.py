@@ -135,7 +135,7 @@ def test_allreduce_neighbour_ring(worlds, n):
                 want = oracle.allreduce(xs, dt, op, order=0)
                 for r in range(n):
                     assert np.array_equal(back(recv[r], dt), want[r]), (n, dt, op, count, r)
-    w.knob("sub_max", 4096)
+    w.knob("ring_sub", 4096)
     try:
         for dt, op, scalar, count in ((L.FLOAT32, L.SUM, None, (3 << 20) // 4 + 3), (L.BFLOAT16, L.AVG, None, 700001),
                                       (L.INT32, L.AVG, None, 400003), (L.FLOAT8E4M3, L.SUM, None, 1 << 20),
@@ -152,7 +152,7 @@ def test_allreduce_neighbour_ring(worlds, n):
                 assert np.array_equal(back(buf[r], dt), want[r]), (n, dt, op, count, r)
         assert all(w.status(r) == (0, 0) for r in range(n))
     finally:
-        w.knob("sub_max", 512 * 1024)
+        w.knob("ring_sub", 512 * 1024)
 
 
 @pytest.mark.parametrize("n", [2, 3, 8])
