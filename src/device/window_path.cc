@@ -43,8 +43,22 @@ struct RankFacts {
   int device;
   int multicast;  // device attribute
   int fd_handles;  // POSIX fd export supported
-  int pad;
+  int chunk16;     // HXCCL_IPC_CHUNK in 16-byte units, 0 = not set
 };
+
+// HXCCL_IPC_CHUNK of the reference is the size of its staging buffers, so every transfer moves
+// in pieces of at most that many bytes (src/memspace_cuda.cc:25-34: 64 B .. 1 GiB, anything
+// else means the default; the ranks use the smallest wish, src/transport_ipc.cc:93-98). Here
+// it bounds the bytes a CTA moves per pipelined step the same way; unset leaves the tuner's
+// own sizes.
+int chunk_wish16() {
+  const char* e = std::getenv("HXCCL_IPC_CHUNK");
+  if (!e || !*e) return 0;
+  char* end = nullptr;
+  const long long v = std::strtoll(e, &end, 10);
+  if (end == e || *end || v < 64 || v > (1LL << 30)) return 0;
+  return int(v / 16);
+}
 
 }  // namespace
 
@@ -150,7 +164,7 @@ hxcclResult_t WindowPath::setup_windows() {
   }
 
   // step 1: what each rank has
-  RankFacts mine{host_fingerprint(), dev_, 0, 0, 0};
+  RankFacts mine{host_fingerprint(), dev_, 0, 0, chunk_wish16()};
   bool ok = d.ok && n_ <= kMaxRanks && !std::getenv("HXCCL_TEST_FAIL_DEVICE_INIT");
   if (ok) {
     ok = d.CtxGetDevice(&cudev_) == CUDA_SUCCESS;
@@ -164,9 +178,19 @@ hxcclResult_t WindowPath::setup_windows() {
   if (c_->chan->allgather(&mine, all.data(), sizeof mine) != hxcclSuccess)
     return fail(hxcclSystemError, "exchanging device facts failed: " + c_->chan->error);
   bool all_mc = true;
+  int chunk16 = 0;
   for (const RankFacts& f : all) {
     ok = ok && f.host == mine.host && f.fd_handles;
     all_mc = all_mc && f.multicast;
+    if (f.chunk16 > 0) chunk16 = chunk16 ? std::min(chunk16, f.chunk16) : f.chunk16;
+  }
+  if (chunk16 > 0) {
+    Tuning& t = eng_.tune;
+    const size_t cap = size_t(chunk16) * 16;
+    t.sub_max = std::min(t.sub_max, cap);
+    t.single_sub_max = std::min(t.single_sub_max, cap);
+    t.ring_sub = std::min(t.ring_sub, cap);
+    t.roles_sub = std::min(t.roles_sub, cap);
   }
   for (int p = 0; p < n_; ++p)  // two ranks on one GPU cannot run kernels that wait on each other
     for (int q = p + 1; q < n_; ++q) ok = ok && all[p].device != all[q].device;

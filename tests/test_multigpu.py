@@ -62,6 +62,27 @@ def test_allreduce_exact(n):
     assert all(r[2] == 0 for r in res)
 
 
+@needs2
+def test_allreduce_exact_with_small_chunks():
+    """HXCCL_IPC_CHUNK bounds the bytes a CTA moves per step, so moderate messages run through
+    the many-step pipelines (the reference's HXCCL_IPC_CHUNK=4096 test runs, CMakeLists.txt:98-100).
+    One rank asks for a larger chunk: the smallest wish holds for everyone."""
+    n = 2
+    cases = []
+    for dt in (L.FLOAT32, L.BFLOAT16, L.INT32, L.FLOAT8E5M2):
+        for op in (L.SUM, L.AVG):
+            for count, variant in (((2 << 20) // L.DTYPE_SIZE[dt] + 3, 0), ((2 << 20) // L.DTYPE_SIZE[dt] + 3, 6)):
+                cases.append((dt, op, count, variant, 100 + len(cases)))
+    res = run_ranks(n, _allreduce_body, cases, gpus=True, timeout=120, env={"HXCCL_IPC_CHUNK": "4096"},
+                    rank_env={1: {"HXCCL_IPC_CHUNK": "65536"}})
+    for k, (dt, op, count, variant, seed) in enumerate(cases):
+        want = oracle.allreduce(inputs_for(n, count, dt, seed, tame=True), dt, op)
+        for r in range(n):
+            got = res[r][1][k][0].view(oracle.raw_dtype(dt))
+            assert np.array_equal(got, want[r]), (dt, op, count, variant, r)
+    assert all(r[2] == 0 for r in res)
+
+
 def _nvls_body(comm, rank, n):
     import torch
 
