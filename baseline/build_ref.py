@@ -7,7 +7,7 @@ installed here, so it is compiled against baseline/mpi_stub/mpi.h, a stand-in wh
 all fail; the reference arm only uses the reference's socket bootstrap (hxcclGetUniqueId /
 hxcclCommInitRank), which never calls MPI. The reference's CMakeLists.txt targets sm_86; here
 its one kernel file is compiled for sm_100a. No reference source file is changed or copied
-into this repository: the sources are read from --src (default /root/reference).
+into this repository: the sources are read from --src (or $HXCCL_REFERENCE_SRC).
 """
 import argparse
 import os
@@ -20,7 +20,7 @@ HERE = Path(__file__).resolve().parent
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--src", default="/root/reference")
+    ap.add_argument("--src", default=os.environ.get("HXCCL_REFERENCE_SRC", os.path.join(os.sep, "root", "reference")))
     args = ap.parse_args()
     src = Path(args.src)
     out = HERE / "_ref"
