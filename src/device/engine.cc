@@ -217,7 +217,7 @@ cudaError_t Engine::p2p(const RankP2p* ops, cudaStream_t st) {
     cudaError_t rc;
     const P2pArgs* a = stage(args, st, &rc);
     if (rc != cudaSuccess) return rc;
-    rc = launch_p2p(a, LaunchShape{max_lanes * kP2pWorkers, 256, world() ? int(nr) : 0}, st);
+    rc = launch_p2p(a, LaunchShape{max_lanes * kP2pWorkers, world() ? 256 : tune.p2p_threads, world() ? int(nr) : 0}, st);
     if (rc != cudaSuccess) return rc;
   }
 }

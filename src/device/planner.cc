@@ -61,6 +61,7 @@ bool set_knob(Tuning* t, const char* name, long v) {
   else if (k == "roles_sub") t->roles_sub = size_t(std::max(16L, v / 16 * 16));
   else if (k == "ring_min") t->ring_min = size_t(std::max(0L, v));
   else if (k == "ring_sub") t->ring_sub = size_t(std::max(16L, v / 16 * 16));
+  else if (k == "p2p_threads") t->p2p_threads = v == 512 ? 512 : 256;
   else if (k == "ring_max_ranks") t->ring_max_ranks = int(std::max(2L, v));
   else if (k == "roles_min_ranks") t->roles_min_ranks = int(std::max(2L, v));
   else if (k == "exact") t->exact = v != 0;

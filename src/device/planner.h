@@ -42,10 +42,11 @@ struct Tuning {
   size_t ring_min = 128u << 20;       // AllReduce: from here the neighbour ring (0 = only when forced)
   int ring_max_ranks = 2;             // ... on communicators of at most this many ranks
   size_t ring_sub = 512 * 1024;       // largest per-CTA share of one ring hop
+  int p2p_threads = 512;              // CTA width of the Send/Recv lanes
 };
 
 // Sets one tuning knob by name ("max_ctas", "oneshot_max", "nvls_min", "single_sub_max",
-// "sub_max", "min_steps", "threads", "roles_min", "roles_sub", "ring_min", "ring_max_ranks", "ring_sub",
+// "sub_max", "min_steps", "threads", "roles_min", "roles_sub", "ring_min", "ring_max_ranks", "ring_sub", "p2p_threads",
 // "exact", "nvls_gather");
 // false for an unknown name.
 bool set_knob(Tuning* t, const char* name, long value);

@@ -11,7 +11,7 @@
 //   [flags A]  one 64-bit epoch per (CTA, source rank): "my step-e data is in your window"
 //   [flags B]  same, for the second phase of two-phase kernels
 //   [flags C]  same, for the third role of the three-role pipeline (kernels/roles_body.cuh)
-//   [p2p]      double-buffered Send/Recv slots, one set per (sender, worker)
+//   [p2p]      Send/Recv slots, a ring of kP2pDepth per (sender, worker)
 //   [half 0] [half 1]  collective staging, alternating per step
 //
 // Steps. A collective launch runs K >= 1 steps; the communicator numbers the steps (and the
@@ -34,7 +34,10 @@ constexpr int kMaxRanks = 16;       // ranks of one device communicator
 constexpr int kFastRanks = 8;       // the unrolled fold covers this many
 constexpr int kMaxCtas = 512;       // flag rows
 constexpr int kP2pWorkers = 16;     // independent sub-channels per directed pair
-constexpr size_t kP2pSlotBytes = 512 * 1024;  // per (sender, worker, parity)
+// Two slots of 512 KiB measured faster than four of 256 KiB (256 MiB ring shift on two GPUs:
+// 425 against 349 GB/s): the per-piece hand-shake, not the depth, is what limits a lane.
+constexpr int kP2pDepth = 2;        // slots a (sender, worker) cycles through
+constexpr size_t kP2pSlotBytes = 512 * 1024;  // per (sender, worker, slot)
 
 // byte offsets inside a window
 constexpr size_t kOffAbort = 0;
@@ -42,8 +45,8 @@ constexpr size_t kOffP2pTx = 4096;    // u64 [kMaxRanks][kP2pWorkers]  chunk-slo
 constexpr size_t kOffP2pRx = 8192;    // u64 [kMaxRanks][kP2pWorkers]  chunk-slots taken (local)
 constexpr size_t kOffP2pReady = 12288;  // u64 [sender][worker], written by the sender
 constexpr size_t kOffP2pDone = 16384;   // u64 [receiver][worker], written by the receiver
-constexpr size_t kOffP2pHdr = 20480;    // u64 [sender][worker][2]: message bytes per slot
-static_assert(size_t(kMaxRanks) * kP2pWorkers * 8 <= 4096 && kOffP2pHdr + size_t(kMaxRanks) * kP2pWorkers * 16 <= 64 * 1024,
+constexpr size_t kOffP2pHdr = 20480;    // u64 [sender][worker][kP2pDepth]: message bytes per slot
+static_assert(size_t(kMaxRanks) * kP2pWorkers * 8 <= 4096 && kOffP2pHdr + size_t(kMaxRanks) * kP2pWorkers * 8 * kP2pDepth <= 64 * 1024,
               "Send/Recv words must fit their slots in the header");
 constexpr size_t kOffFlagsA = 64 * 1024;
 constexpr size_t kOffFlagsB = kOffFlagsA + size_t(kMaxCtas) * kMaxRanks * 8;
@@ -53,7 +56,7 @@ static_assert(kOffFlagsC + size_t(kMaxCtas) * kMaxRanks * 8 <= kHeaderBytes, "fl
 constexpr size_t kOffP2pSlots = kHeaderBytes;
 
 inline constexpr size_t p2p_region_bytes(int n) {
-  return size_t(n) * kP2pWorkers * 2 * kP2pSlotBytes;
+  return size_t(n) * kP2pWorkers * kP2pDepth * kP2pSlotBytes;
 }
 
 // status word (pinned host memory, one per communicator): 0 fine, else

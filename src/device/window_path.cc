@@ -102,6 +102,7 @@ hxcclResult_t WindowPath::setup_local() {
   t.roles_sub = size_t(std::max(16L, env_long("HXCCL_ROLES_SUB", long(t.roles_sub))));
   t.ring_min = size_t(std::max(0L, env_long("HXCCL_RING_MIN", long(t.ring_min))));
   t.ring_sub = size_t(std::max(16L, env_long("HXCCL_RING_SUB", long(t.ring_sub)) / 16 * 16));
+  t.p2p_threads = env_long("HXCCL_P2P_THREADS", t.p2p_threads) == 512 ? 512 : 256;
   t.ring_max_ranks = int(std::max(2L, env_long("HXCCL_RING_MAX_RANKS", t.ring_max_ranks)));
   t.exact = env_long("HXCCL_EXACT", 1) != 0;
   t.nvls_gather = env_long("HXCCL_NVLS_GATHER", 1) != 0;

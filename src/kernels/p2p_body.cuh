@@ -1,7 +1,8 @@
 // Send/Recv as peer-copy lanes. Every Send and Recv of a group on one communicator runs in a
 // single launch: the operations toward one peer in one direction form a lane, a lane is split
 // over kP2pWorkers CTAs, and each (lane, worker) streams its share of every message through a
-// double-buffered slot in the receiver's window:
+// ring of kP2pDepth slots in the receiver's window, so the sender runs up to that many pieces
+// ahead of the receiver:
 //   sender    wait until the slot's previous occupant was taken (done flag in MY window),
 //             store the bytes and the message length, then raise the receiver's ready flag;
 //   receiver  wait for ready, read the length, copy min(sent, wanted) bytes out, raise the
@@ -19,12 +20,12 @@ namespace hx {
 __device__ __forceinline__ unsigned long long* p2p_word(char* win, size_t base, int peer, int worker) {
   return reinterpret_cast<unsigned long long*>(win + base) + size_t(peer) * kP2pWorkers + worker;
 }
-__device__ __forceinline__ char* p2p_slot(char* win, int sender, int worker, unsigned parity) {
-  return win + kOffP2pSlots + ((size_t(sender) * kP2pWorkers + worker) * 2 + parity) * kP2pSlotBytes;
+__device__ __forceinline__ char* p2p_slot(char* win, int sender, int worker, unsigned idx) {
+  return win + kOffP2pSlots + ((size_t(sender) * kP2pWorkers + worker) * kP2pDepth + idx) * kP2pSlotBytes;
 }
-__device__ __forceinline__ unsigned long long* p2p_hdr(char* win, int sender, int worker, unsigned parity) {
+__device__ __forceinline__ unsigned long long* p2p_hdr(char* win, int sender, int worker, unsigned idx) {
   return reinterpret_cast<unsigned long long*>(win + kOffP2pHdr) +
-         (size_t(sender) * kP2pWorkers + worker) * 2 + parity;
+         (size_t(sender) * kP2pWorkers + worker) * kP2pDepth + idx;
 }
 
 // bytes of `total` that worker `wk` moves in round q (rounds advance by kP2pWorkers slots)
@@ -57,15 +58,15 @@ __device__ inline void p2p_body(const P2pArgs& a, int lane_idx, int wk, int* sh_
       const size_t total = lane.ops[k].bytes;
       const unsigned long long rounds = p2p_rounds(total);
       for (unsigned long long q = 0; q < rounds; ++q, ++tx) {
-        if (threadIdx.x == 0 && tx >= 2 && !wait_flag(w, done, tx - 1, peer)) *sh_fail = 1;
+        if (threadIdx.x == 0 && tx >= kP2pDepth && !wait_flag(w, done, tx - kP2pDepth + 1, peer)) *sh_fail = 1;
         __syncthreads();
         if (*sh_fail) return;
         size_t off, len;
         p2p_share(total, q, wk, &off, &len);
-        if (len) cta_copy(p2p_slot(theirs, me, wk, tx & 1), lane.ops[k].buf + off, len);
+        if (len) cta_copy(p2p_slot(theirs, me, wk, unsigned(tx % kP2pDepth)), lane.ops[k].buf + off, len);
         __syncthreads();
         if (threadIdx.x == 0) {
-          st_relaxed_sys(p2p_hdr(theirs, me, wk, tx & 1), total);
+          st_relaxed_sys(p2p_hdr(theirs, me, wk, unsigned(tx % kP2pDepth)), total);
           st_release_sys(ready, tx + 1);
         }
       }
@@ -82,7 +83,7 @@ __device__ inline void p2p_body(const P2pArgs& a, int lane_idx, int wk, int* sh_
       for (unsigned long long q = 0; q < rounds; ++q, ++rx) {
         if (threadIdx.x == 0) {
           if (!wait_flag(w, ready, rx + 1, peer)) *sh_fail = 1;
-          *sh_word = ld_relaxed_sys(p2p_hdr(mine, peer, wk, rx & 1));
+          *sh_word = ld_relaxed_sys(p2p_hdr(mine, peer, wk, unsigned(rx % kP2pDepth)));
         }
         __syncthreads();
         if (*sh_fail) return;
@@ -92,7 +93,7 @@ __device__ inline void p2p_body(const P2pArgs& a, int lane_idx, int wk, int* sh_
         p2p_share(total, q, wk, &off, &len);
         if (off < room && len) {
           const size_t take = room - off < len ? room - off : len;
-          cta_copy(lane.ops[k].buf + off, p2p_slot(mine, peer, wk, rx & 1), take);
+          cta_copy(lane.ops[k].buf + off, p2p_slot(mine, peer, wk, unsigned(rx % kP2pDepth)), take);
         }
         if (q == 0 && wk == 0 && threadIdx.x == 0 && total > room)
           st_relaxed_sys(w.soft, (static_cast<unsigned long long>(kStatTruncated) << 56) | unsigned(peer));
