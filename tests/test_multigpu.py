@@ -73,13 +73,16 @@ def test_allreduce_exact_with_small_chunks():
         for op in (L.SUM, L.AVG):
             for count, variant in (((2 << 20) // L.DTYPE_SIZE[dt] + 3, 0), ((2 << 20) // L.DTYPE_SIZE[dt] + 3, 6)):
                 cases.append((dt, op, count, variant, 100 + len(cases)))
-    res = run_ranks(n, _allreduce_body, cases, gpus=True, timeout=120, env={"HXCCL_IPC_CHUNK": "4096"},
+    cases.append((L.FLOAT32, L.SUM, (5 << 20) // 4 + 1, 0, 99))  # above HXCCL_RING_MIN: the tuner picks the ring
+    res = run_ranks(n, _allreduce_body, cases, gpus=True, timeout=120,
+                    env={"HXCCL_IPC_CHUNK": "4096", "HXCCL_RING_MIN": str(4 << 20)},
                     rank_env={1: {"HXCCL_IPC_CHUNK": "65536"}})
     for k, (dt, op, count, variant, seed) in enumerate(cases):
         want = oracle.allreduce(inputs_for(n, count, dt, seed, tame=True), dt, op)
         for r in range(n):
             got = res[r][1][k][0].view(oracle.raw_dtype(dt))
             assert np.array_equal(got, want[r]), (dt, op, count, variant, r)
+            assert res[r][1][k][2] == (6 if variant == 6 or count * L.DTYPE_SIZE[dt] >= (4 << 20) else 2)
     assert all(r[2] == 0 for r in res)
 
 
