@@ -83,3 +83,35 @@ def test_traffic_counters(n):
         else:
             assert res[r]["rd"] == (total * levels, levels)
         assert res[r]["tiny"][1] > 0
+
+
+def _plumbing_body(comm, rank, n):
+    """The CPU plumbing configuration of the baseline: fp32, 1,048,576 elements of U(-1,1)
+    from seed 1234+rank, sum and avg, ring at full size and recursive doubling at 16 KB."""
+    x = np.random.default_rng(1234 + rank).uniform(-1.0, 1.0, 1 << 20).astype(np.float32)
+    out = {}
+    for algo, count in (("ring", 1 << 20), ("rd", 4096)):
+        os.environ["HXCCL_ALGO"] = algo
+        for name, op in (("sum", L.SUM), ("avg", L.AVG)):
+            y = np.zeros(count, dtype=np.float32)
+            comm.reset_stats()
+            comm.all_reduce(x[:count], y, op=op)
+            out[algo, name] = (y, comm.stats())
+    os.environ.pop("HXCCL_ALGO")
+    return out
+
+
+def test_cpu_plumbing_config_against_fp64_sum():
+    n = 2
+    res = run_ranks(n, _plumbing_body, timeout=120)
+    xs = [np.random.default_rng(1234 + r).uniform(-1.0, 1.0, 1 << 20).astype(np.float32) for r in range(n)]
+    for algo, count in (("ring", 1 << 20), ("rd", 4096)):
+        ref = sum(x[:count].astype(np.float64) for x in xs)
+        for r in range(n):
+            got_sum, stats = res[r][algo, "sum"]
+            got_avg, _ = res[r][algo, "avg"]
+            assert np.abs(got_sum.astype(np.float64) - ref).max() <= 2.5e-7  # one fp32 rounding of a value below 2
+            assert np.abs(got_avg.astype(np.float64) - ref / n).max() <= 2.5e-7
+            assert np.array_equal(got_sum, res[0][algo, "sum"][0])  # every rank holds the same bits
+            # with two ranks both schedules move the whole vector once: two halves (ring) or one piece (rd)
+            assert stats == ((count * 4, 2) if algo == "ring" else (count * 4, 1)), (algo, stats)
