@@ -62,6 +62,16 @@ void hxcclRingBlock(size_t count, int n, int i, size_t* off, size_t* len);
 hxcclResult_t hxcclTestNarrowConvert(hxcclDataType_t dt, unsigned long long* mismatches,
                                      unsigned int* first_bad_bits);
 
+/* Plans one launch without a device: kind 0 generic exchange (amount = largest block of a pair),
+ * 1 two-shot / NVLS AllReduce (amount = message bytes), 2 the same as three-role pipeline,
+ * 3 neighbour ring (amount = largest ring block), for `nranks` ranks whose staging halves hold
+ * `half_bytes` each, with the default tuning except `max_ctas` (0 keeps it) and one optional
+ * knob (`knob` may be NULL). shape = {ctas, threads, steps, epochs, sub_bytes}. Returns
+ * hxcclSuccess when the shape fits the window layout the kernels assume and covers `amount`,
+ * hxcclInternalError otherwise (`why`, when given, receives the reason). */
+hxcclResult_t hxcclTestPlan(int kind, size_t amount, int nranks, size_t half_bytes, int max_ctas,
+                            const char* knob, long knob_value, size_t shape[5], char* why, size_t why_len);
+
 /* ---- fault injection (host side only) ---------------------------------------------------------- */
 /* The (after+1)-th host-path send from now fails with hxcclSystemError; after < 0 disarms. */
 hxcclResult_t hxcclTestFailSends(hxcclComm_t comm, long after);

@@ -11,6 +11,17 @@ Engine::~Engine() {
   if (dev_args_) cudaFree(dev_args_);
 }
 
+// Host-side check of every launch shape against the window layout (planner.h); a violation is
+// a bug in the planner, reported instead of launched.
+#define HX_CHECK_PLAN(KIND, G, AMOUNT)                                                   \
+  do {                                                                                   \
+    const std::string why_ = check_geometry(KIND, G, AMOUNT, n(), views[0].half_bytes);  \
+    if (!why_.empty()) {                                                                 \
+      error = "launch plan rejected: " + why_;                                           \
+      return cudaErrorInvalidValue;                                                      \
+    }                                                                                    \
+  } while (0)
+
 LaunchShape Engine::shape(const Geometry& g) const {
   return LaunchShape{g.ctas, g.threads, world() ? int(views.size()) : 0};
 }
@@ -50,6 +61,7 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
     // the recursive-doubling order costs n log n combines per element: give a CTA less of it
     const Geometry g = plan_xchg(bytes, n(), views[0].half_bytes, tune,
                                  order == kOrderDoubling ? 2 * 1024 : 16 * 1024);
+    HX_CHECK_PLAN(kPlanXchg, g, bytes);
     std::vector<XchgArgs> args(views.size());
     for (size_t r = 0; r < views.size(); ++r)
       build_allreduce_oneshot(&args[r], views[r], epoch, g, b[r].send, b[r].recv, count, dt, plan, order);
@@ -60,6 +72,7 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
   if (var == kVarRing) {
     const size_t es = dtype_size(dt);
     const Geometry g = plan_ring((count + n() - 1) / n() * es, n(), views[0].half_bytes, tune);
+    HX_CHECK_PLAN(kPlanRing, g, (count + n() - 1) / n() * es);
     std::vector<TwoShotArgs> args(views.size());
     for (size_t r = 0; r < views.size(); ++r)
       build_allreduce_twoshot(&args[r], views[r], epoch, g, b[r].send, b[r].recv, count, dt, plan, order, false);
@@ -73,6 +86,7 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
                      (var == kVarNvls ? n() > 2 : n() >= tune.roles_min_ranks);
   const Geometry g = roles ? plan_roles(bytes, n(), views[0].half_bytes, tune)
                            : plan_sliced(bytes, n(), views[0].half_bytes, tune);
+  HX_CHECK_PLAN(roles ? kPlanRoles : kPlanSliced, g, bytes);
   if (var == kVarNvls) {
     std::vector<NvlsArgs> args(1);
     build_allreduce_nvls(&args[0], views[0], epoch, g, b[0].send, b[0].recv, count, dt, plan);
@@ -97,6 +111,7 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
 cudaError_t Engine::reducescatter(const RankBufs* b, size_t per, int dt, const OpPlan& plan,
                                   cudaStream_t st) {
   const Geometry g = plan_xchg(per * dtype_size(dt), n(), views[0].half_bytes, tune);
+  HX_CHECK_PLAN(kPlanXchg, g, per * dtype_size(dt));
   std::vector<XchgArgs> args(views.size());
   for (size_t r = 0; r < views.size(); ++r)
     build_reducescatter(&args[r], views[r], epoch, g, b[r].send, b[r].recv, per, dt, plan);
@@ -110,6 +125,7 @@ cudaError_t Engine::reducescatter(const RankBufs* b, size_t per, int dt, const O
 cudaError_t Engine::reduce(const RankBufs* b, size_t count, int dt, const OpPlan& plan, int root,
                            cudaStream_t st) {
   const Geometry g = plan_xchg(count * dtype_size(dt), n(), views[0].half_bytes, tune);
+  HX_CHECK_PLAN(kPlanXchg, g, count * dtype_size(dt));
   std::vector<XchgArgs> args(views.size());
   for (size_t r = 0; r < views.size(); ++r)
     build_reduce(&args[r], views[r], epoch, g, b[r].send, b[r].recv, count, dt, plan, root);
@@ -122,6 +138,7 @@ cudaError_t Engine::reduce(const RankBufs* b, size_t count, int dt, const OpPlan
 
 #define HX_COPY_COLLECTIVE(MAXPAIR, BUILD)                                  \
   const Geometry g = plan_xchg(MAXPAIR, n(), views[0].half_bytes, tune);    \
+  HX_CHECK_PLAN(kPlanXchg, g, MAXPAIR);                                     \
   std::vector<XchgArgs> args(views.size());                                 \
   for (size_t r = 0; r < views.size(); ++r) { BUILD; }                      \
   epoch += g.epochs;                                                         \

@@ -1,9 +1,12 @@
 // Extension entry points (include/hxccl_ext.h) other than the single-GPU world.
 #include <cuda_runtime.h>
 
+#include <cstdio>
 #include <cstring>
+#include <string>
 
 #include "core/comm.h"
+#include "device/planner.h"
 #include "device/window_path.h"
 #include "hxccl_ext.h"
 #include "kernels/launch.h"
@@ -120,6 +123,34 @@ hxcclResult_t hxcclTestSeverPeer(hxcclComm_t c, int peer) {
   if (!c || peer < 0 || peer >= c->nranks) return hxcclInvalidArgument;
   c->chan->fabric().sever(c->chan->members()[peer]);
   return hxcclSuccess;
+}
+
+hxcclResult_t hxcclTestPlan(int kind, size_t amount, int nranks, size_t half_bytes, int max_ctas,
+                            const char* knob, long knob_value, size_t shape[5], char* why, size_t why_len) {
+  using namespace hx;
+  if (nranks < 1 || nranks > kMaxRanks || !shape) return hxcclInvalidArgument;
+  Tuning t;
+  if (max_ctas > 0) t.max_ctas = max_ctas;
+  if (knob && *knob && !set_knob(&t, knob, knob_value)) return hxcclInvalidArgument;
+  Geometry g;
+  switch (kind) {
+    case kPlanXchg: g = plan_xchg(amount, nranks, half_bytes, t); break;
+    case kPlanSliced: g = plan_sliced(amount, nranks, half_bytes, t); break;
+    case kPlanRoles: g = plan_roles(amount, nranks, half_bytes, t); break;
+    case kPlanRing:
+      if (nranks < 2) return hxcclInvalidArgument;
+      g = plan_ring(amount, nranks, half_bytes, t);
+      break;
+    default: return hxcclInvalidArgument;
+  }
+  shape[0] = size_t(g.ctas);
+  shape[1] = size_t(g.threads);
+  shape[2] = size_t(g.steps);
+  shape[3] = size_t(g.epochs);
+  shape[4] = g.sub_bytes;
+  const std::string bad = check_geometry(kind, g, amount, nranks, half_bytes);
+  if (why && why_len) std::snprintf(why, why_len, "%s", bad.c_str());
+  return bad.empty() ? hxcclSuccess : hxcclInternalError;
 }
 
 }  // extern "C"

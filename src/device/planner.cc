@@ -42,9 +42,10 @@ void split_steps(Geometry* g, size_t per_cta_total, size_t fit_single, size_t fi
   }
   size_t sub = std::min(std::max(round_up(want / std::max(2, t.min_steps), 16), size_t(4096)), t.sub_max);
   sub = std::max<size_t>(16, std::min(sub, fit_ring));
-  g->sub_bytes = sub;
   g->steps = int(ceil_div(want, sub));
   if (g->steps == 1 && want > fit_single) g->steps = 2;  // cannot happen with sane windows
+  // equal steps: no short last step when the window, not the tuning, set the size
+  g->sub_bytes = std::max<size_t>(16, std::min(sub, round_up(ceil_div(want, size_t(g->steps)), 16)));
 }
 }  // namespace
 
@@ -127,6 +128,37 @@ Geometry plan_ring(size_t max_block, int n, size_t half_bytes, const Tuning& t) 
   g.epochs = g.steps * int(hops) + 2;
   g.threads = t.threads ? t.threads : threads_for(g.sub_bytes);
   return g;
+}
+
+std::string check_geometry(int kind, const Geometry& g, size_t amount, int n, size_t half_bytes) {
+  auto num = [](size_t v) { return std::to_string(v); };
+  if (g.ctas < 1 || g.ctas > kMaxCtas) return "grid of " + num(size_t(g.ctas)) + " CTAs does not fit the flag rows";
+  if (g.threads != 256 && g.threads != 512) return "CTA width " + num(size_t(g.threads));
+  if (g.steps < 1 || g.sub_bytes < 16 || g.sub_bytes % 16) return "step of " + num(g.sub_bytes) + " bytes";
+  if (n < 1 || n > kMaxRanks) return "rank count " + num(size_t(n));
+  const size_t ctas = size_t(g.ctas), steps = size_t(g.steps), ranks = size_t(n);
+  if (kind == kPlanXchg) {
+    const size_t buf = buffer_bytes(half_bytes, g.steps), stride = round_down(buf / ranks, 256);
+    if (g.epochs != (g.steps == 1 ? 1 : g.steps + 2)) return "epoch count";
+    if (ctas * g.sub_bytes > stride || ranks * stride > buf) return "a source's slots overrun its share of the buffer";
+    if (steps * ctas * g.sub_bytes < amount) return "steps do not cover the block";
+  } else if (kind == kPlanSliced || kind == kPlanRoles) {
+    const bool roles = kind == kPlanRoles;
+    if (roles && (g.ctas % 3 || g.epochs != g.steps + 1)) return "role pipeline shape";
+    if (!roles && g.epochs != (g.steps == 1 ? 1 : g.steps + 2)) return "epoch count";
+    const size_t buf = roles ? buffer_bytes(half_bytes, 2) : buffer_bytes(half_bytes, g.steps);
+    const size_t second = round_down(buf / 2, 256), slice = (roles ? ctas / 3 : ctas) * g.sub_bytes;
+    if (ranks * slice > second || second + ranks * slice > buf) return "slices overrun a half of the buffer";
+    if (steps * ranks * slice < amount) return "steps do not cover the message";
+  } else if (kind == kPlanRing) {
+    const size_t hops = size_t(2 * n - 2);
+    if (n < 2 || g.epochs != g.steps * int(hops) + 2) return "ring shape";
+    if (hops * ctas * g.sub_bytes > 2 * half_bytes) return "ring slots overrun the staging area";
+    if (steps * ctas * g.sub_bytes < amount) return "rounds do not cover a block";
+  } else {
+    return "unknown plan kind";
+  }
+  return std::string();
 }
 
 FoldSpec make_fold(const OpPlan& plan, int kind) {

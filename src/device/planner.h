@@ -5,6 +5,7 @@
 #pragma once
 #include <cstddef>
 #include <cstdint>
+#include <string>
 
 #include "core/devpath.h"
 #include "core/schedule.h"
@@ -61,6 +62,13 @@ Geometry plan_roles(size_t bytes, int n, size_t half_bytes, const Tuning& t);
 // neighbour ring over blocks of at most `max_block` bytes: steps = rounds,
 // epochs = rounds * (2n - 2) + 2
 Geometry plan_ring(size_t max_block, int n, size_t half_bytes, const Tuning& t);
+
+// Checks a launch shape against the window layout the kernels assume: every slot a CTA writes
+// lies inside its staging buffer, the steps cover the whole message, the grid fits the flag rows.
+// Returns an empty string when all holds, else what does not. `amount` is what the matching
+// plan_* function was given. Run before every launch (host arithmetic only).
+enum : int { kPlanXchg = 0, kPlanSliced = 1, kPlanRoles = 2, kPlanRing = 3 };
+std::string check_geometry(int kind, const Geometry& g, size_t amount, int n, size_t half_bytes);
 
 FoldSpec make_fold(const OpPlan& plan, int kind);
 

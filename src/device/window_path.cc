@@ -106,6 +106,26 @@ hxcclResult_t WindowPath::setup_local() {
   t.ring_max_ranks = int(std::max(2L, env_long("HXCCL_RING_MAX_RANKS", t.ring_max_ranks)));
   t.exact = env_long("HXCCL_EXACT", 1) != 0;
   t.nvls_gather = env_long("HXCCL_NVLS_GATHER", 1) != 0;
+  // HXCCL_TUNE_FILE: one "name value" or "name=value" per line, '#' starts a comment; the names
+  // are those of hxcclCommTuneKnob. Applied after the variables above, so a file wins.
+  if (const char* path = std::getenv("HXCCL_TUNE_FILE")) {
+    std::ifstream in(path);
+    if (!in) return fail(hxcclInvalidArgument, std::string("cannot read HXCCL_TUNE_FILE ") + path);
+    std::string line;
+    while (std::getline(in, line)) {
+      const size_t hash = line.find('#');
+      if (hash != std::string::npos) line.erase(hash);
+      for (char& ch : line)
+        if (ch == '=' || ch == '\t' || ch == '\r') ch = ' ';
+      char name[64];
+      long value = 0;
+      const int got = std::sscanf(line.c_str(), " %63s %ld", name, &value);
+      if (got <= 0) continue;  // blank
+      if (got != 2 || !set_knob(&t, name, value))
+        return fail(hxcclInvalidArgument, std::string("HXCCL_TUNE_FILE: cannot use the line for '") + name + "'");
+    }
+    t.max_ctas = std::min(t.max_ctas, max_resident_ctas(t.threads ? t.threads : 512));
+  }
   if (const char* v = std::getenv("HXCCL_VARIANT")) {
     if (!std::strcmp(v, "oneshot")) eng_.forced_variant = kVarOneShot;
     if (!std::strcmp(v, "twoshot")) eng_.forced_variant = kVarTwoShot;
@@ -448,7 +468,16 @@ hxcclResult_t WindowPath::allreduce(const void* send, void* recv, size_t count, 
                                     const OpPlan& plan, int order, void* stream) {
   if (count == 0) return hxcclSuccess;
   RankBufs b{send, recv};
-  return done(eng_.allreduce(&b, count, dt, plan, order, enter(stream)), "AllReduce launch");
+  const cudaError_t e = eng_.allreduce(&b, count, dt, plan, order, enter(stream));
+  // HXCCL_DEBUG=2 (or more): one line per AllReduce on rank 0 with what the tuner chose
+  static const int level = [] { const char* v = std::getenv("HXCCL_DEBUG"); return v ? std::atoi(v) : 0; }();
+  if (level >= 2 && rank_ == 0) {
+    static const char* const names[] = {"auto", "one-shot", "two-shot", "nvls", "two-shot roles", "nvls roles", "ring"};
+    const int v = eng_.last_variant;
+    std::fprintf(stderr, "hxccl: AllReduce %zu bytes, dtype %d, order %s -> %s\n", count * dtype_size(dt), dt,
+                 order == kOrderRing ? "ring" : "doubling", v >= 0 && v <= 6 ? names[v] : "?");
+  }
+  return done(e, "AllReduce launch");
 }
 hxcclResult_t WindowPath::allgather(const void* send, void* recv, size_t block, void* stream) {
   if (block == 0) return hxcclSuccess;

@@ -1,0 +1,64 @@
+"""Launch shapes of the device path, checked on the CPU: for every collective plan, message
+size, rank count, window size and grid limit, each CTA's slots must lie inside its staging
+buffer, the steps must cover the message and the epochs must match what the kernels consume.
+The same check runs before every real launch (src/device/planner.h: check_geometry)."""
+import ctypes as C
+
+import pytest
+
+from hxccl_b200 import _lib as L
+
+KINDS = {"xchg": 0, "sliced": 1, "roles": 2, "ring": 3}
+
+
+def plan(kind, amount, n, half, max_ctas=0, knob=None, value=0):
+    lib = L.lib()
+    lib.hxcclTestPlan.argtypes = [C.c_int, C.c_size_t, C.c_int, C.c_size_t, C.c_int, C.c_char_p, C.c_long,
+                                  C.POINTER(C.c_size_t), C.c_char_p, C.c_size_t]
+    shape = (C.c_size_t * 5)()
+    why = C.create_string_buffer(256)
+    rc = lib.hxcclTestPlan(KINDS[kind], amount, n, half, max_ctas, knob.encode() if knob else None, value, shape, why, 256)
+    return rc, list(shape), why.value.decode()
+
+
+SIZES = [1, 15, 16, 17, 4099, 65536, 262144, 262145, (1 << 20) + 16, 3 << 20, (64 << 20) + 48, 256 << 20, 1 << 30, (1 << 30) + 4]
+
+
+@pytest.mark.parametrize("kind", list(KINDS))
+def test_every_plan_fits_its_window(kind):
+    bad = []
+    for n in (1, 2, 3, 4, 8, 16):
+        if kind == "ring" and n < 2:
+            continue
+        for half in (3 << 20, 61 << 20, 253 << 20):
+            for max_ctas in (0, 1, 8, 48, 512):
+                for amount in SIZES:
+                    rc, shape, why = plan(kind, amount, n, half, max_ctas)
+                    if rc != 0:
+                        bad.append((n, half, max_ctas, amount, shape, why))
+    assert not bad, bad[:5]
+
+
+def test_knobs_keep_plans_inside_the_window():
+    for knob, values in (("sub_max", (16, 4096, 1 << 20)), ("single_sub_max", (16, 1 << 22)), ("min_steps", (2, 64)),
+                         ("roles_sub", (16, 4096, 1 << 22)), ("ring_sub", (16, 4096, 1 << 22)), ("threads", (256, 512))):
+        for v in values:
+            for kind in KINDS:
+                for n in (2, 8):
+                    for amount in (4099, 3 << 20, 256 << 20):
+                        rc, shape, why = plan(kind, amount, n, 61 << 20, 0, knob, v)
+                        assert rc == 0, (knob, v, kind, n, amount, shape, why)
+
+
+def test_shapes_of_the_measured_defaults():
+    # 256 MiB on two ranks: the ring runs 128 CTAs in two rounds of 512 KiB hops
+    rc, (ctas, threads, steps, epochs, sub), _ = plan("ring", 128 << 20, 2, 253 << 20)
+    assert rc == 0 and (ctas, threads, steps, epochs, sub) == (128, 512, 2, 2 * 2 + 2, 512 << 10)
+    # 256 MiB two-shot on four ranks: pipelined steps of at most 128 KiB per CTA and slice (a quarter
+    # of the staging area holds a little less than four ranks x 128 CTAs x 128 KiB x two phases)
+    rc, (ctas, threads, steps, epochs, sub), _ = plan("sliced", 256 << 20, 4, 253 << 20)
+    assert rc == 0 and ctas == 128 and steps == 5 and epochs == 7 and sub == (512 << 10) // 5 // 16 * 16 + 16
+    # 64 MiB on eight ranks fits one step
+    rc, (ctas, threads, steps, epochs, sub), _ = plan("sliced", 64 << 20, 8, 253 << 20)
+    assert rc == 0 and (steps, epochs, sub) == (1, 1, 64 << 10)
+    assert plan("ring", 1024, 1, 1 << 20)[0] == L.INVALID_ARGUMENT
