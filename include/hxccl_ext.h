@@ -65,7 +65,7 @@ hxcclResult_t hxcclTestNarrowConvert(hxcclDataType_t dt, unsigned long long* mis
 /* Plans one launch without a device: kind 0 generic exchange (amount = largest block of a pair),
  * 1 two-shot / NVLS AllReduce (amount = message bytes), 2 the same as three-role pipeline,
  * 3 neighbour ring (amount = largest ring block), for `nranks` ranks whose staging halves hold
- * `half_bytes` each, with the default tuning except `max_ctas` (0 keeps it) and one optional
+ * `half_bytes` each, with the default tuning, then HXCCL_TUNE_FILE when set, then `max_ctas` (0 keeps it) and one optional
  * knob (`knob` may be NULL). shape = {ctas, threads, steps, epochs, sub_bytes}. Returns
  * hxcclSuccess when the shape fits the window layout the kernels assume and covers `amount`,
  * hxcclInternalError otherwise (`why`, when given, receives the reason). */

@@ -2,6 +2,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
@@ -130,6 +131,13 @@ hxcclResult_t hxcclTestPlan(int kind, size_t amount, int nranks, size_t half_byt
   using namespace hx;
   if (nranks < 1 || nranks > kMaxRanks || !shape) return hxcclInvalidArgument;
   Tuning t;
+  if (const char* path = std::getenv("HXCCL_TUNE_FILE")) {
+    std::string bad_line;
+    if (!load_tune_file(&t, path, &bad_line)) {
+      if (why && why_len) std::snprintf(why, why_len, "%s", bad_line.c_str());
+      return hxcclInvalidArgument;
+    }
+  }
   if (max_ctas > 0) t.max_ctas = max_ctas;
   if (knob && *knob && !set_knob(&t, knob, knob_value)) return hxcclInvalidArgument;
   Geometry g;

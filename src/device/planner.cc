@@ -1,7 +1,9 @@
 #include "device/planner.h"
 
 #include <algorithm>
+#include <cstdio>
 #include <cstring>
+#include <fstream>
 #include <string>
 
 #include "device/nvls_modes.h"
@@ -68,6 +70,30 @@ bool set_knob(Tuning* t, const char* name, long v) {
   else if (k == "exact") t->exact = v != 0;
   else if (k == "nvls_gather") t->nvls_gather = v != 0;
   else return false;
+  return true;
+}
+
+bool load_tune_file(Tuning* t, const char* path, std::string* why) {
+  std::ifstream in(path);
+  if (!in) {
+    *why = std::string("cannot read HXCCL_TUNE_FILE ") + path;
+    return false;
+  }
+  std::string line;
+  while (std::getline(in, line)) {
+    const size_t hash = line.find('#');
+    if (hash != std::string::npos) line.erase(hash);
+    for (char& ch : line)
+      if (ch == '=' || ch == '\t' || ch == '\r') ch = ' ';
+    char name[64];
+    long value = 0;
+    const int got = std::sscanf(line.c_str(), " %63s %ld", name, &value);
+    if (got <= 0) continue;  // blank
+    if (got != 2 || !set_knob(t, name, value)) {
+      *why = std::string("HXCCL_TUNE_FILE: cannot use the line for '") + name + "'";
+      return false;
+    }
+  }
   return true;
 }
 

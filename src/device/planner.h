@@ -51,6 +51,9 @@ struct Tuning {
 // "exact", "nvls_gather");
 // false for an unknown name.
 bool set_knob(Tuning* t, const char* name, long value);
+// Applies a file of knob settings (HXCCL_TUNE_FILE): one "name value" or "name=value" per line,
+// '#' starts a comment. False, with the reason in *why, for an unreadable file or a bad line.
+bool load_tune_file(Tuning* t, const char* path, std::string* why);
 
 // generic exchange where the largest block of any pair is `max_pair` bytes
 Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t, size_t cta_bytes = 16 * 1024);

@@ -106,24 +106,9 @@ hxcclResult_t WindowPath::setup_local() {
   t.ring_max_ranks = int(std::max(2L, env_long("HXCCL_RING_MAX_RANKS", t.ring_max_ranks)));
   t.exact = env_long("HXCCL_EXACT", 1) != 0;
   t.nvls_gather = env_long("HXCCL_NVLS_GATHER", 1) != 0;
-  // HXCCL_TUNE_FILE: one "name value" or "name=value" per line, '#' starts a comment; the names
-  // are those of hxcclCommTuneKnob. Applied after the variables above, so a file wins.
-  if (const char* path = std::getenv("HXCCL_TUNE_FILE")) {
-    std::ifstream in(path);
-    if (!in) return fail(hxcclInvalidArgument, std::string("cannot read HXCCL_TUNE_FILE ") + path);
-    std::string line;
-    while (std::getline(in, line)) {
-      const size_t hash = line.find('#');
-      if (hash != std::string::npos) line.erase(hash);
-      for (char& ch : line)
-        if (ch == '=' || ch == '\t' || ch == '\r') ch = ' ';
-      char name[64];
-      long value = 0;
-      const int got = std::sscanf(line.c_str(), " %63s %ld", name, &value);
-      if (got <= 0) continue;  // blank
-      if (got != 2 || !set_knob(&t, name, value))
-        return fail(hxcclInvalidArgument, std::string("HXCCL_TUNE_FILE: cannot use the line for '") + name + "'");
-    }
+  if (const char* path = std::getenv("HXCCL_TUNE_FILE")) {  // applied last, so a file wins
+    std::string why;
+    if (!load_tune_file(&t, path, &why)) return fail(hxcclInvalidArgument, why);
     t.max_ctas = std::min(t.max_ctas, max_resident_ctas(t.threads ? t.threads : 512));
   }
   if (const char* v = std::getenv("HXCCL_VARIANT")) {

@@ -62,3 +62,18 @@ def test_shapes_of_the_measured_defaults():
     rc, (ctas, threads, steps, epochs, sub), _ = plan("sliced", 64 << 20, 8, 253 << 20)
     assert rc == 0 and (steps, epochs, sub) == (1, 1, 64 << 10)
     assert plan("ring", 1024, 1, 1 << 20)[0] == L.INVALID_ARGUMENT
+
+
+def test_tune_file(tmp_path, monkeypatch):
+    good = tmp_path / "tune.txt"
+    good.write_text("# settings measured on some node\nmax_ctas = 8\nsub_max 4096   # small steps\n\nmin_steps=2\n")
+    monkeypatch.setenv("HXCCL_TUNE_FILE", str(good))
+    rc, (ctas, threads, steps, epochs, sub), why = plan("sliced", 64 << 20, 2, 253 << 20)
+    assert rc == 0 and ctas == 8 and sub == 4096 and steps == (64 << 20) // 2 // 8 // 4096 and epochs == steps + 2
+    bad = tmp_path / "bad.txt"
+    bad.write_text("max_ctas 8\nno_such_knob 3\n")
+    monkeypatch.setenv("HXCCL_TUNE_FILE", str(bad))
+    rc, _, why = plan("sliced", 1 << 20, 2, 253 << 20)
+    assert rc == L.INVALID_ARGUMENT and "no_such_knob" in why
+    monkeypatch.setenv("HXCCL_TUNE_FILE", str(tmp_path / "missing.txt"))
+    assert plan("sliced", 1 << 20, 2, 253 << 20)[0] == L.INVALID_ARGUMENT
