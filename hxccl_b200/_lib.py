@@ -44,13 +44,18 @@ def lib() -> C.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not _LIB_PATH.exists():
-        if os.environ.get("HXCCL_NO_AUTOBUILD"):
-            raise OSError(f"{_LIB_PATH} is missing; run `python -m hxccl_b200.build`")
+    override = os.environ.get("HXCCL_LIBRARY")  # e.g. the sanitizer build (python -m hxccl_b200.build --sanitize)
+    if override:
+        path = Path(override)
+    else:
+        path = _LIB_PATH
+    if not path.exists():
+        if override or os.environ.get("HXCCL_NO_AUTOBUILD"):
+            raise OSError(f"{path} is missing; run `python -m hxccl_b200.build`")
         from . import build  # noqa: PLC0415
 
         build.build_lib()
-    L = C.CDLL(str(_LIB_PATH), mode=C.RTLD_GLOBAL)
+    L = C.CDLL(str(path), mode=C.RTLD_GLOBAL)
     vp, sz, i, u64p = C.c_void_p, C.c_size_t, C.c_int, C.POINTER(C.c_uint64)
     szp = C.POINTER(C.c_size_t)
     sig = {

@@ -3,6 +3,17 @@ request, the torch.distributed backend extension.
 
     python -m hxccl_b200.build            # library
     python -m hxccl_b200.build --torch    # library + torch backend
+    python -m hxccl_b200.build --sanitize # build/libhxccl_san.so: host code under ASan + UBSan
+
+The sanitizer build compiles every host source (.cc) with -fsanitize=address,undefined and links
+it with the ordinary kernel objects. Run the CPU tests against it with
+
+    HXCCL_LIBRARY=build/libhxccl_san.so LD_PRELOAD=$(g++ -print-file-name=libasan.so) \
+        ASAN_OPTIONS=detect_leaks=0 python -m pytest tests -q -m "not gpu" --deselect tests/test_torch_backend.py
+
+(the interpreter itself is not instrumented, hence the preload and no leak report; the torch
+backend test is left out because libtorch throws C++ exceptions before the preloaded ASan has
+found the real __cxa_throw, which ends the process with an ASan CHECK that is not about this code).
 
 The CUDA sources are compiled for sm_100a only (-gencode arch=compute_100a,code=sm_100a);
 nvcc cross-compiles, so no GPU is needed to build. Objects land in build/ (ignored by git),
@@ -40,14 +51,19 @@ def _newest_header() -> float:
     return max(p.stat().st_mtime for p in hdrs)
 
 
-def _compile(src: Path, hdr_time: float, verbose: bool) -> Path:
-    obj = OBJ / (str(src.relative_to(SRC)).replace("/", "_") + ".o")
+SANFLAGS = ["-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-g", "-O1"]
+
+
+def _compile(src: Path, hdr_time: float, verbose: bool, sanitize: bool = False) -> Path:
+    sanitize = sanitize and src.suffix != ".cu"
+    obj = OBJ / (str(src.relative_to(SRC)).replace("/", "_") + (".san.o" if sanitize else ".o"))
     if obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, hdr_time):
         return obj
     if src.suffix == ".cu":
         cmd = [NVCC, *NVCCFLAGS, *INCLUDES, "-c", str(src), "-o", str(obj)]
     else:
-        cmd = [os.environ.get("CXX", "g++"), *CXXFLAGS, *INCLUDES, "-c", str(src), "-o", str(obj)]
+        cmd = [os.environ.get("CXX", "g++"), *CXXFLAGS, *(SANFLAGS if sanitize else []), *INCLUDES, "-c", str(src),
+               "-o", str(obj)]
     if verbose:
         print(" ".join(cmd), flush=True)
     res = subprocess.run(cmd, capture_output=True, text=True)
@@ -75,6 +91,25 @@ def build_lib(verbose: bool = False, jobs: int | None = None) -> Path:
     if res.returncode != 0:
         raise RuntimeError(f"linking libhxccl.so failed:\n{res.stdout}\n{res.stderr}")
     return LIB
+
+
+def build_sanitized(verbose: bool = False, jobs: int | None = None) -> Path:
+    """Links build/libhxccl_san.so: host sources under ASan + UBSan, kernels as in the normal build."""
+    build_lib(verbose, jobs)  # the kernel objects
+    sources = sorted(SRC.rglob("*.cc")) + sorted(SRC.rglob("*.cu"))
+    hdr_time = _newest_header()
+    with ThreadPoolExecutor(max_workers=jobs or max(1, (os.cpu_count() or 2))) as pool:
+        objs = list(pool.map(lambda s: _compile(s, hdr_time, verbose, sanitize=True), sources))
+    out = ROOT / "build" / "libhxccl_san.so"
+    cmd = [NVCC, "-shared", "-cudart", "static", "-o", str(out), *map(str, objs),
+           "-Xcompiler", "-pthread", "-Xcompiler", "-fsanitize=address", "-Xcompiler", "-fsanitize=undefined",
+           "-ldl", "-lrt"]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"linking libhxccl_san.so failed:\n{res.stdout}\n{res.stderr}")
+    return out
 
 
 def build_perf(verbose: bool = False) -> Path:
@@ -126,6 +161,7 @@ def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--torch", action="store_true", help="also build the torch.distributed backend")
     ap.add_argument("--perf", action="store_true", help="also build bench/hx_perf")
+    ap.add_argument("--sanitize", action="store_true", help="also build build/libhxccl_san.so (ASan + UBSan)")
     ap.add_argument("-v", "--verbose", action="store_true")
     ap.add_argument("-j", "--jobs", type=int, default=None)
     args = ap.parse_args()
@@ -134,6 +170,8 @@ def main() -> None:
         print(build_torch_ext(args.verbose))
     if args.perf:
         print(build_perf(args.verbose))
+    if args.sanitize:
+        print(build_sanitized(args.verbose, args.jobs))
 
 
 if __name__ == "__main__":
