@@ -88,6 +88,18 @@ def reference_unavailable(reason: str) -> None:
     print(json.dumps({"impl": "reference", "unavailable": reason}))
 
 
+# The reference's published device AllReduce (fp32 sum, 256 MiB) as bus bandwidth: 43028 us with
+# two ranks and 110449 us with four, all ranks sharing one RTX 3060 Ti (its README, device table).
+# Nothing is published for one or eight ranks, for other sizes of this benchmark, or for B200.
+PUBLISHED_BUSBW_256MIB = {2: 268435456 / 43028e-6 / 1e9 * 1.0, 4: 268435456 / 110449e-6 / 1e9 * 1.5}
+
+
+def vs_published(value: float, world: int, nbytes: int, dtype: str):
+    ref = PUBLISHED_BUSBW_256MIB.get(world) if (nbytes == 268435456 and dtype == "float32") else None
+    return round(value / ref, 2) if ref else None
+
+
+
 def main() -> int:
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -182,9 +194,12 @@ def main() -> int:
         allreduce(src, dst)
     barrier()
     l0 = launches_of()
-    # in place on `dst`, the form torch.distributed offers, so that every arm does the same work
+    # in place on `dst`, the form torch.distributed offers, so that every arm does the same work.
+    # With one rank an in-place AllReduce is no work at all (in this library and in the reference),
+    # so the single-GPU run is out of place: the whole message is read and written once.
     dst.copy_(src)
-    ms = timed(lambda: allreduce(dst, dst), args.steps, 0)
+    step = (lambda: allreduce(src, dst)) if world == 1 else (lambda: allreduce(dst, dst))
+    ms = timed(step, args.steps, 0)
     launches = launches_of() - l0
     factor = 2.0 * (world - 1) / world if world > 1 else 1.0
     algbw = nbytes / (ms * 1e-3) / 1e9
@@ -233,7 +248,8 @@ def main() -> int:
         for sz in (8, 1024, 64 << 10, 1 << 20, 16 << 20, 64 << 20):
             n_el = max(1, sz // es)
             a, b = src[:n_el], dst[:n_el]
-            t = timed(lambda: allreduce(b, b), 50 if sz <= (1 << 20) else 20, 5)
+            t = timed((lambda: allreduce(a, b)) if world == 1 else (lambda: allreduce(b, b)),
+                      50 if sz <= (1 << 20) else 20, 5)
             sweep.append({"bytes": n_el * es, "us": round(t * 1e3, 2),
                           "busbw_GBps": round(n_el * es / (t * 1e-3) / 1e9 * factor, 2)})
 
@@ -250,13 +266,14 @@ def main() -> int:
         line = {
             "metric": "allreduce_busbw_GBps", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.dtype,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": vs_published(value, world, nbytes, args.dtype),
+            "dtype": args.dtype,
             "data": "synthetic U(-1,1), seed 1234+rank", "impl": args.impl,
-            "config": {"model": "AllReduce sum, in place", "global_batch": nbytes * world, "seq_len": count,
+            "config": {"model": "AllReduce sum, in place" if world > 1 else "AllReduce sum, out of place (one rank)", "global_batch": nbytes * world, "seq_len": count,
                        "parallelism": f"{world} ranks, one per GPU", "bytes_per_rank": nbytes,
                        "l2_policy": "message larger than L2 (126 MB): no flush needed",
                        "exact_order": bool(args.exact), "device_path": variant,
-                       "note": ("one GPU: value is algorithm bandwidth of the local AllReduce (bus factor is 0)"
+                       "note": ("one GPU: value is the algorithm bandwidth of the local out-of-place AllReduce (bus factor is 0)"
                                 if world == 1 else "value = algbw * 2(N-1)/N (nccl-tests bus bandwidth)")},
             "algbw_GBps": round(algbw, 2),
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "ms_per_step": round(e2e_ms, 4),

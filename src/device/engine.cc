@@ -49,6 +49,14 @@ const Args* Engine::stage(const std::vector<Args>& args, cudaStream_t st, cudaEr
 cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpPlan& plan,
                               int order, cudaStream_t st) {
   const size_t bytes = count * dtype_size(dt);
+  // One rank, nothing to scale or divide: the result is the input (the reference's path does a
+  // plain copy then too, src/algo_ring.cc:17-18). In place that is no work at all.
+  if (!world() && n() == 1 && !plan.premul && !(plan.postdiv && plan.divisor != 1)) {
+    last_variant = kVarAuto;
+    if (b[0].send == b[0].recv) return cudaSuccess;
+    ++launches;
+    return launch_copy(b[0].recv, b[0].send, bytes, st);
+  }
   int var = choose_variant(bytes, dt, plan, n(), tune, forced_variant);
   // recursive doubling gives every rank its own operand order; only the variant in which each
   // rank folds for itself can replay that

@@ -1,5 +1,7 @@
 // Type-independent kernels (byte exchange, Send/Recv lanes, NVLS) and the run-time dispatch
 // from hxcclDataType_t to the per-type launchers.
+#include <algorithm>
+
 #include "kernels/inst.cuh"
 #include "kernels/nvls_body.cuh"
 #include "kernels/p2p_body.cuh"
@@ -36,6 +38,19 @@ template <typename T, int kMode>
 __global__ void __launch_bounds__(512) k_nvls_roles(const __grid_constant__ NvlsArgs a) {
   __shared__ FoldShared sh;
   nvls_roles_body<T, kMode>(a, blockIdx.x, gridDim.x, sh);
+}
+
+// Every CTA copies one contiguous share with eight 16-byte loads in flight per thread.
+__global__ void __launch_bounds__(512) k_copy(char* dst, const char* src, size_t bytes, size_t share) {
+  const size_t lo = size_t(blockIdx.x) * share;
+  if (lo < bytes) cta_copy(dst + lo, src + lo, min_sz(share, bytes - lo));
+}
+cudaError_t launch_copy(void* dst, const void* src, size_t bytes, cudaStream_t st) {
+  if (bytes == 0) return cudaSuccess;
+  const int grid = int(std::min<size_t>(size_t(max_resident_ctas(512)) * 2, (bytes + 65535) / 65536));
+  const size_t share = ((bytes + grid - 1) / grid + 15) & ~size_t(15);
+  k_copy<<<grid, 512, 0, st>>>(static_cast<char*>(dst), static_cast<const char*>(src), bytes, share);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_xchg_copy(const XchgArgs* args, LaunchShape s, cudaStream_t st) {

@@ -27,6 +27,9 @@ cudaError_t launch_ring(int dt, const TwoShotArgs* args, LaunchShape s, cudaStre
 cudaError_t launch_nvls(const NvlsArgs* args, LaunchShape s, cudaStream_t st, bool roles = false);
 cudaError_t launch_p2p(const P2pArgs* args, LaunchShape s, cudaStream_t st);
 
+// dst[0, bytes) = src[0, bytes) at memory speed (the single-rank collectives)
+cudaError_t launch_copy(void* dst, const void* src, size_t bytes, cudaStream_t st);
+
 // standalone elementwise kernels (dst op= src, dst = src*scalar, buf /= divisor)
 cudaError_t launch_reduce(void* dst, const void* src, size_t count, int dt, int op, cudaStream_t st);
 cudaError_t launch_scale(void* dst, const void* src, size_t count, int dt, const void* scalar_host,

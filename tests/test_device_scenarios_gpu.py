@@ -145,3 +145,34 @@ def test_truncation_in_one_communicator_leaves_the_other_working():
         assert (a0, a1) == (10 + rnd, 10 + rnd)  # what fitted did arrive
         assert (b0, b1) == (20 + rnd, 20 + rnd)
     assert receiver[3] == (0, 3.0, 0) and sender[3] == (0, 3.0, 0)
+
+
+def _single_rank_body(comm, rank, n):
+    """One rank: out of place is one copy launch, in place is no launch at all, and neither changes
+    a bit (no arithmetic runs, so NaN payloads stay as they are)."""
+    out = []
+    for count in (1, 7, 4099, (3 << 20) + 5):
+        t = torch.randint(0, 255, (count,), dtype=torch.uint8, device="cuda")
+        o = torch.zeros_like(t)
+        before = comm.device_info()["launches"]
+        comm.all_reduce(t, o, op=L.SUM, count=count, dtype=L.UINT8)
+        mid = comm.device_info()["launches"]
+        keep = t.clone()
+        comm.all_reduce(t, t, op=L.MAX, count=count, dtype=L.UINT8)
+        torch.cuda.synchronize()
+        out.append((bool(torch.equal(o, t)), bool(torch.equal(t, keep)), mid - before, comm.device_info()["launches"] - mid))
+    i = torch.arange(-5, 5, dtype=torch.int32, device="cuda")
+    o = torch.zeros_like(i)
+    comm.all_reduce(i, o, op=L.AVG)
+    f = torch.tensor([1.5, float("nan"), -0.0], device="cuda")
+    g = torch.zeros_like(f)
+    comm.all_reduce(f, g, op=L.AVG)  # scaled by 1.0 through the general kernel
+    torch.cuda.synchronize()
+    return out, bool(torch.equal(i, o)), g.cpu().numpy().view(np.uint32).tolist(), comm.async_error()
+
+
+def test_single_rank_allreduce_is_a_copy_or_nothing():
+    (out, int_ok, fbits, err), = run_ranks(1, _single_rank_body, gpus=True, timeout=60)
+    assert all(o == (True, True, 1, 0) for o in out), out
+    assert int_ok and err == 0
+    assert fbits[0] == 0x3FC00000 and (fbits[1] & 0x7FC00000) == 0x7FC00000 and fbits[2] == 0x80000000
