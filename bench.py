@@ -231,17 +231,6 @@ def main() -> int:
                 "note": "HXCCL_EXACT=0: float sums combined by the switch, order unspecified"}
         comm.tune(variant=0, exact=True)
 
-    # ---- extras: the same step through the neighbour-ring kernel (bit-exact like the headline) --
-    ring = None
-    if comm is not None and world > 1 and args.exact:
-        comm.tune(variant=6, exact=True)
-        dst.copy_(src)
-        ring_ms = timed(lambda: allreduce(dst, dst), args.steps, 3)
-        ring = {"value": round(nbytes / (ring_ms * 1e-3) / 1e9 * factor, 2), "unit": "GB/s",
-                "ms_per_step": round(ring_ms, 4), "variant": comm.device_info()["variant"],
-                "note": "HXCCL_VARIANT=ring: reduce-scatter and all-gather around the ring, same bits"}
-        comm.tune(variant=0, exact=True)
-
     # ---- extras: latency and a short sweep ------------------------------------------------------
     sweep = []
     if not args.no_sweep:
@@ -252,6 +241,21 @@ def main() -> int:
                       50 if sz <= (1 << 20) else 20, 5)
             sweep.append({"bytes": n_el * es, "us": round(t * 1e3, 2),
                           "busbw_GBps": round(n_el * es / (t * 1e-3) / 1e9 * factor, 2)})
+
+    # ---- extras: the same step through the neighbour-ring kernel (bit-exact like the headline).
+    # Last of all measurements and guarded: whatever happens here cannot cost the figures above.
+    ring = None
+    if comm is not None and world > 1 and args.exact:
+        try:
+            comm.tune(variant=6, exact=True)
+            dst.copy_(src)
+            ring_ms = timed(lambda: allreduce(dst, dst), args.steps, 3)
+            ring = {"value": round(nbytes / (ring_ms * 1e-3) / 1e9 * factor, 2), "unit": "GB/s",
+                    "ms_per_step": round(ring_ms, 4), "variant": comm.device_info()["variant"],
+                    "note": "HXCCL_VARIANT=ring: reduce-scatter and all-gather around the ring, same bits"}
+            comm.tune(variant=0, exact=True)
+        except Exception as e:  # noqa: BLE001
+            ring = {"error": str(e)[:200]}
 
     clocks = sampler.stop() if sampler else None
     if comm is not None:
