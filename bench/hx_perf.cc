@@ -87,7 +87,7 @@ int run_rank(const Options& o, int rank, const hxcclUniqueId& id) {
   const hxcclRedOp_t red = parse_red(o.red);
   const bool gathers = o.op == "allgather" || o.op == "gather";
   const bool scatters = o.op == "reducescatter" || o.op == "alltoall" || o.op == "scatter";
-  const size_t cap = o.max_bytes * (gathers || scatters ? 1 : 1) + 256;
+  const size_t cap = o.max_bytes + 256;  // `bytes` is the larger side of every collective here
   char *send = nullptr, *recv = nullptr;
   if (o.host) {
     send = static_cast<char*>(std::malloc(cap));
