@@ -27,3 +27,21 @@ def test_plot_curves_and_phases(tmp_path):
         doc = xml.dom.minidom.parse(str(out))
         assert doc.documentElement.tagName == "svg"
         assert len(doc.getElementsByTagName(tag)) >= least
+
+
+def test_torch_allreduce_bench_on_cpu():
+    """bench/torch_allreduce.py as two CPU ranks: one JSON line per backend and size."""
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", str(port),
+                          os.path.join(ROOT, "bench", "torch_allreduce.py"), "--device", "cpu",
+                          "--backends", "hxccl,gloo", "--sizes", "4K,256K", "--iters", "3", "--warmup", "1"],
+                         capture_output=True, text=True, timeout=240)
+    assert res.returncode == 0, res.stderr[-2000:]
+    rows = [json.loads(line) for line in res.stdout.splitlines() if line.startswith("{")]
+    assert [(r["backend"], r["bytes"]) for r in rows] == [("hxccl", 4096), ("hxccl", 262144), ("gloo", 4096), ("gloo", 262144)]
+    assert all(r["us"] > 0 and r["ranks"] == 2 for r in rows)
