@@ -45,3 +45,17 @@ def test_torch_allreduce_bench_on_cpu():
     rows = [json.loads(line) for line in res.stdout.splitlines() if line.startswith("{")]
     assert [(r["backend"], r["bytes"]) for r in rows] == [("hxccl", 4096), ("hxccl", 262144), ("gloo", 4096), ("gloo", 262144)]
     assert all(r["us"] > 0 and r["ranks"] == 2 for r in rows)
+
+
+def test_c_example_builds_as_c99_and_runs(tmp_path):
+    """The public headers are plain C; examples/allreduce.c runs three ranks over the socket bootstrap."""
+    from hxccl_b200 import _lib
+
+    _lib.lib()  # builds the library when it is missing
+    libdir = os.path.join(ROOT, "hxccl_b200", "lib")
+    exe = tmp_path / "allreduce"
+    subprocess.run(["gcc", "-std=c99", "-D_POSIX_C_SOURCE=200809L", "-Wall", "-Wextra", "-pedantic", "-Werror",
+                    "-I" + os.path.join(ROOT, "include"), os.path.join(ROOT, "examples", "allreduce.c"),
+                    "-L" + libdir, "-lhxccl", "-Wl,-rpath," + libdir, "-o", str(exe)], check=True, timeout=120)
+    res = subprocess.run([str(exe), "3"], capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0 and "3 ranks: average 2, ring shift ok" in res.stdout, (res.stdout, res.stderr)
