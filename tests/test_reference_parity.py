@@ -1,0 +1,166 @@
+"""Bit-for-bit parity with the reference library itself, on host buffers and without a GPU: the
+unmodified reference (built by baseline/build_ref.py into baseline/_ref/libhxccl_ref.so) and
+this library run the same collectives on the same random bytes as real multi-process jobs over
+their socket bootstraps, and every result byte must agree. This pins the element rules
+(src/elem.h, src/fp.h, src/reduce.cc of the reference) AND the reduction orders of its
+algorithms (src/algo_ring.cc, src/algo_rd.cc, src/algo_rooted.cc) at once.
+
+Skipped where the reference build or the CUDA stub driver library is absent (the reference's
+CUDA build links libcuda; without a GPU the toolkit's stub stands in and its host path never
+calls it)."""
+import ctypes as C
+import multiprocessing as mp
+import os
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from hxccl_b200 import _lib as L
+from hxccl_b200.ops import oracle
+from hxccl_b200.utils import run_ranks
+
+ROOT = Path(__file__).resolve().parent.parent
+REF = ROOT / "baseline" / "_ref" / "libhxccl_ref.so"
+STUB = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "lib64" / "stubs" / "libcuda.so"
+
+pytestmark = pytest.mark.skipif(not REF.exists(), reason="reference build absent (python baseline/build_ref.py)")
+
+
+class RefId(C.Structure):
+    _fields_ = [("internal", C.c_char * 128)]
+
+
+def _load_reference():
+    try:
+        C.CDLL("libcuda.so.1", mode=C.RTLD_GLOBAL)
+    except OSError:
+        C.CDLL(str(STUB), mode=C.RTLD_GLOBAL)  # no driver on this machine: the toolkit's stub
+    lib = C.CDLL(str(REF))
+    vp = C.c_void_p
+    lib.hxcclCommInitRank.argtypes = [C.POINTER(vp), C.c_int, RefId, C.c_int]
+    lib.hxcclAllReduce.argtypes = [vp, vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
+    lib.hxcclReduceScatter.argtypes = [vp, vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
+    lib.hxcclReduce.argtypes = [vp, vp, C.c_size_t, C.c_int, C.c_int, C.c_int, vp, vp]
+    lib.hxcclCommDestroy.argtypes = [vp]
+    return lib
+
+
+def inputs_for(n, count, dt, seed):
+    es = L.DTYPE_SIZE[dt]
+    return [np.random.default_rng(seed * 1000 + r).integers(0, 256, count * es, dtype=np.uint8) for r in range(n)]
+
+
+def _ref_child(rank, n, cases, id_q, out_q):
+    try:
+        os.environ["HXCCL_DEVICE"] = "0"
+        lib = _load_reference()
+        uid = RefId()
+        if rank == 0:
+            assert lib.hxcclGetUniqueId(C.byref(uid)) == 0
+            for _ in range(n - 1):
+                id_q.put(bytes(uid))
+        else:
+            uid = RefId.from_buffer_copy(id_q.get(timeout=60))
+        comm = C.c_void_p()
+        assert lib.hxcclCommInitRank(C.byref(comm), n, uid, rank) == 0
+        res = []
+        for (coll, dt, op, count, seed) in cases:
+            es = L.DTYPE_SIZE[dt]
+            if coll == "allreduce":
+                x = inputs_for(n, count, dt, seed)[rank].copy()
+                rc = lib.hxcclAllReduce(x.ctypes.data, x.ctypes.data, count, dt, op, comm, None)
+                res.append((rc, x))
+            elif coll == "reducescatter":
+                x = inputs_for(n, count * n, dt, seed)[rank].copy()
+                y = np.zeros(count * es, dtype=np.uint8)
+                rc = lib.hxcclReduceScatter(x.ctypes.data, y.ctypes.data, count, dt, op, comm, None)
+                res.append((rc, y))
+            else:
+                x = inputs_for(n, count, dt, seed)[rank].copy()
+                y = np.zeros(count * es, dtype=np.uint8)
+                rc = lib.hxcclReduce(x.ctypes.data, y.ctypes.data, count, dt, op, n - 1, comm, None)
+                res.append((rc, y if rank == n - 1 else None))
+        lib.hxcclCommDestroy(comm)
+        out_q.put((rank, "ok", res))
+    except BaseException as e:  # noqa: BLE001
+        out_q.put((rank, "err", repr(e)))
+
+
+def run_reference(n, cases):
+    ctx = mp.get_context("spawn")
+    id_q, out_q = ctx.Queue(), ctx.Queue()
+    procs = [ctx.Process(target=_ref_child, args=(r, n, cases, id_q, out_q)) for r in range(n)]
+    for p in procs:
+        p.start()
+    got = {}
+    try:
+        for _ in range(n):
+            rank, state, payload = out_q.get(timeout=180)
+            assert state == "ok", payload
+            got[rank] = payload
+    finally:
+        for p in procs:
+            p.join(10)
+            if p.is_alive():
+                p.kill()
+    return [got[r] for r in range(n)]
+
+
+def _ours_body(comm, rank, n, cases):
+    res = []
+    for (coll, dt, op, count, seed) in cases:
+        es = L.DTYPE_SIZE[dt]
+        if coll == "allreduce":
+            x = inputs_for(n, count, dt, seed)[rank].copy()
+            rc = comm.all_reduce(x, x, op=op, count=count, dtype=dt, check=False)
+            res.append((rc, x))
+        elif coll == "reducescatter":
+            x = inputs_for(n, count * n, dt, seed)[rank].copy()
+            y = np.zeros(count * es, dtype=np.uint8)
+            rc = comm.reduce_scatter(x, y, op=op, count=count, dtype=dt, check=False)
+            res.append((rc, y))
+        else:
+            x = inputs_for(n, count, dt, seed)[rank].copy()
+            y = np.zeros(count * es, dtype=np.uint8)
+            rc = comm.reduce(x, y, root=n - 1, op=op, count=count, dtype=dt, check=False)
+            res.append((rc, y if rank == n - 1 else None))
+    return res
+
+
+def make_cases():
+    cases = []
+    for dt in range(12):
+        es = L.DTYPE_SIZE[dt]
+        for op in (L.SUM, L.PROD, L.MAX, L.MIN, L.AVG):
+            # 7 and 1000 elements take recursive doubling (< 64 KiB), the last count the ring
+            for count in (7, 1000, (64 << 10) // es + 13):
+                cases.append(("allreduce", dt, op, count, len(cases)))
+        cases.append(("reducescatter", dt, L.SUM, 501, len(cases)))
+        cases.append(("reducescatter", dt, L.AVG, 33, len(cases)))
+        cases.append(("reduce", dt, L.SUM, 777, len(cases)))                    # tree toward the root
+        cases.append(("reduce", dt, L.PROD, (512 << 10) // es + 5, len(cases)))  # chain in 512 KiB pieces
+    return cases
+
+
+@pytest.mark.parametrize("n", [2, 3, 4, 5, 8])
+def test_host_collectives_equal_the_reference_bit_for_bit(n):
+    if not STUB.exists():
+        try:
+            C.CDLL("libcuda.so.1")
+        except OSError:
+            pytest.skip("neither a CUDA driver nor the toolkit's stub library is here")
+    cases = make_cases()
+    ref = run_reference(n, cases)
+    ours = run_ranks(n, _ours_body, cases, timeout=180)
+    for k, (coll, dt, op, count, seed) in enumerate(cases):
+        for r in range(n):
+            rc_ref, out_ref = ref[r][k]
+            rc_ours, out_ours = ours[r][k]
+            assert rc_ref == 0 and rc_ours == 0, (n, coll, dt, op, count, r, rc_ref, rc_ours)
+            if out_ref is None:
+                continue
+            assert np.array_equal(out_ref, out_ours), (n, coll, dt, op, count, r)
+        if coll == "allreduce":  # and the in-process oracle the GPU tests rely on says the same
+            want = oracle.allreduce([x.view(oracle.raw_dtype(dt)) for x in inputs_for(n, count, dt, seed)], dt, op)
+            assert np.array_equal(ref[0][k][1], want[0].view(np.uint8)), (n, dt, op, count)
