@@ -1,7 +1,8 @@
 """Bit-for-bit parity with the reference library itself, on host buffers and without a GPU: the
 unmodified reference (built by baseline/build_ref.py into baseline/_ref/libhxccl_ref.so) and
 this library run the same collectives on the same random bytes as real multi-process jobs over
-their socket bootstraps, and every result byte must agree. This pins the element rules
+their socket bootstraps; every result byte and every traffic counter (bytes and messages each
+rank sent) must agree. This pins the element rules
 (src/elem.h, src/fp.h, src/reduce.cc of the reference) AND the reduction orders of its
 algorithms (src/algo_ring.cc, src/algo_rd.cc, src/algo_rooted.cc) at once.
 
@@ -42,8 +43,19 @@ def _load_reference():
     lib.hxcclAllReduce.argtypes = [vp, vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
     lib.hxcclReduceScatter.argtypes = [vp, vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
     lib.hxcclReduce.argtypes = [vp, vp, C.c_size_t, C.c_int, C.c_int, C.c_int, vp, vp]
+    lib.hxcclAllGather.argtypes = [vp, vp, C.c_size_t, C.c_int, vp, vp]
+    lib.hxcclBroadcast.argtypes = [vp, vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
+    lib.hxcclAlltoAll.argtypes = [vp, vp, C.c_size_t, C.c_int, vp, vp]
     lib.hxcclCommDestroy.argtypes = [vp]
+    lib.hxcclCommResetStats.argtypes = [vp]
+    lib.hxcclCommGetStats.argtypes = [vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
     return lib
+
+
+def _ref_stats(lib, comm):
+    b, m = C.c_uint64(), C.c_uint64()
+    assert lib.hxcclCommGetStats(comm, C.byref(b), C.byref(m)) == 0
+    return (b.value, m.value)
 
 
 def inputs_for(n, count, dt, seed):
@@ -67,6 +79,7 @@ def _ref_child(rank, n, cases, id_q, out_q):
         res = []
         for (coll, dt, op, count, seed) in cases:
             es = L.DTYPE_SIZE[dt]
+            lib.hxcclCommResetStats(comm)
             if coll == "allreduce":
                 x = inputs_for(n, count, dt, seed)[rank].copy()
                 rc = lib.hxcclAllReduce(x.ctypes.data, x.ctypes.data, count, dt, op, comm, None)
@@ -76,11 +89,27 @@ def _ref_child(rank, n, cases, id_q, out_q):
                 y = np.zeros(count * es, dtype=np.uint8)
                 rc = lib.hxcclReduceScatter(x.ctypes.data, y.ctypes.data, count, dt, op, comm, None)
                 res.append((rc, y))
+            elif coll == "allgather":
+                x = inputs_for(n, count, dt, seed)[rank].copy()
+                y = np.zeros(count * es * n, dtype=np.uint8)
+                rc = lib.hxcclAllGather(x.ctypes.data, y.ctypes.data, count, dt, comm, None)
+                res.append((rc, y))
+            elif coll == "broadcast":
+                x = inputs_for(n, count, dt, seed)[rank].copy()
+                y = np.zeros(count * es, dtype=np.uint8)
+                rc = lib.hxcclBroadcast(x.ctypes.data, y.ctypes.data, count, dt, 1 % n, comm, None)
+                res.append((rc, y))
+            elif coll == "alltoall":
+                x = inputs_for(n, count * n, dt, seed)[rank].copy()
+                y = np.zeros(count * es * n, dtype=np.uint8)
+                rc = lib.hxcclAlltoAll(x.ctypes.data, y.ctypes.data, count, dt, comm, None)
+                res.append((rc, y))
             else:
                 x = inputs_for(n, count, dt, seed)[rank].copy()
                 y = np.zeros(count * es, dtype=np.uint8)
                 rc = lib.hxcclReduce(x.ctypes.data, y.ctypes.data, count, dt, op, n - 1, comm, None)
                 res.append((rc, y if rank == n - 1 else None))
+            res[-1] = res[-1] + (_ref_stats(lib, comm),)
         lib.hxcclCommDestroy(comm)
         out_q.put((rank, "ok", res))
     except BaseException as e:  # noqa: BLE001
@@ -111,6 +140,7 @@ def _ours_body(comm, rank, n, cases):
     res = []
     for (coll, dt, op, count, seed) in cases:
         es = L.DTYPE_SIZE[dt]
+        comm.reset_stats()
         if coll == "allreduce":
             x = inputs_for(n, count, dt, seed)[rank].copy()
             rc = comm.all_reduce(x, x, op=op, count=count, dtype=dt, check=False)
@@ -120,11 +150,27 @@ def _ours_body(comm, rank, n, cases):
             y = np.zeros(count * es, dtype=np.uint8)
             rc = comm.reduce_scatter(x, y, op=op, count=count, dtype=dt, check=False)
             res.append((rc, y))
+        elif coll == "allgather":
+            x = inputs_for(n, count, dt, seed)[rank].copy()
+            y = np.zeros(count * es * n, dtype=np.uint8)
+            rc = comm.all_gather(x, y, count=count, dtype=dt, check=False)
+            res.append((rc, y))
+        elif coll == "broadcast":
+            x = inputs_for(n, count, dt, seed)[rank].copy()
+            y = np.zeros(count * es, dtype=np.uint8)
+            rc = comm.broadcast(x, y, root=1 % n, count=count, dtype=dt, check=False)
+            res.append((rc, y))
+        elif coll == "alltoall":
+            x = inputs_for(n, count * n, dt, seed)[rank].copy()
+            y = np.zeros(count * es * n, dtype=np.uint8)
+            rc = comm.all_to_all(x, y, count=count, dtype=dt, check=False)
+            res.append((rc, y))
         else:
             x = inputs_for(n, count, dt, seed)[rank].copy()
             y = np.zeros(count * es, dtype=np.uint8)
             rc = comm.reduce(x, y, root=n - 1, op=op, count=count, dtype=dt, check=False)
             res.append((rc, y if rank == n - 1 else None))
+        res[-1] = res[-1] + (tuple(comm.stats()),)
     return res
 
 
@@ -140,6 +186,11 @@ def make_cases():
         cases.append(("reducescatter", dt, L.AVG, 33, len(cases)))
         cases.append(("reduce", dt, L.SUM, 777, len(cases)))                    # tree toward the root
         cases.append(("reduce", dt, L.PROD, (512 << 10) // es + 5, len(cases)))  # chain in 512 KiB pieces
+    for dt, count in ((L.UINT8, 300), (L.FLOAT64, 41)):
+        cases.append(("allgather", dt, 0, count, len(cases)))
+        cases.append(("alltoall", dt, 0, count, len(cases)))
+        cases.append(("broadcast", dt, 0, count, len(cases)))                        # binomial tree
+    cases.append(("broadcast", L.INT32, 0, (1600 << 10) // 4 + 3, len(cases)))      # chain in 512 KiB pieces
     return cases
 
 
@@ -155,9 +206,10 @@ def test_host_collectives_equal_the_reference_bit_for_bit(n):
     ours = run_ranks(n, _ours_body, cases, timeout=180)
     for k, (coll, dt, op, count, seed) in enumerate(cases):
         for r in range(n):
-            rc_ref, out_ref = ref[r][k]
-            rc_ours, out_ours = ours[r][k]
+            rc_ref, out_ref, stats_ref = ref[r][k]
+            rc_ours, out_ours, stats_ours = ours[r][k]
             assert rc_ref == 0 and rc_ours == 0, (n, coll, dt, op, count, r, rc_ref, rc_ours)
+            assert stats_ref == stats_ours, (n, coll, dt, op, count, r, stats_ref, stats_ours)  # same schedule
             if out_ref is None:
                 continue
             assert np.array_equal(out_ref, out_ours), (n, coll, dt, op, count, r)
