@@ -46,6 +46,7 @@ def _load_reference():
     lib.hxcclAllGather.argtypes = [vp, vp, C.c_size_t, C.c_int, vp, vp]
     lib.hxcclBroadcast.argtypes = [vp, vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
     lib.hxcclAlltoAll.argtypes = [vp, vp, C.c_size_t, C.c_int, vp, vp]
+    lib.hxcclRedOpCreatePreMulSum.argtypes = [C.POINTER(C.c_int), vp, C.c_int, C.c_int, vp]
     lib.hxcclCommDestroy.argtypes = [vp]
     lib.hxcclCommResetStats.argtypes = [vp]
     lib.hxcclCommGetStats.argtypes = [vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
@@ -89,6 +90,13 @@ def _ref_child(rank, n, cases, id_q, out_q):
                 y = np.zeros(count * es, dtype=np.uint8)
                 rc = lib.hxcclReduceScatter(x.ctypes.data, y.ctypes.data, count, dt, op, comm, None)
                 res.append((rc, y))
+            elif coll == "premul":  # `op` carries the scalar's bits
+                k = np.array([op], dtype=np.uint64).view(np.uint8)[:es].copy()
+                handle = C.c_int()
+                assert lib.hxcclRedOpCreatePreMulSum(C.byref(handle), k.ctypes.data, dt, L.SCALAR_HOST_IMMEDIATE, comm) == 0
+                x = inputs_for(n, count, dt, seed)[rank].copy()
+                rc = lib.hxcclAllReduce(x.ctypes.data, x.ctypes.data, count, dt, handle.value, comm, None)
+                res.append((rc, x))
             elif coll == "allgather":
                 x = inputs_for(n, count, dt, seed)[rank].copy()
                 y = np.zeros(count * es * n, dtype=np.uint8)
@@ -150,6 +158,12 @@ def _ours_body(comm, rank, n, cases):
             y = np.zeros(count * es, dtype=np.uint8)
             rc = comm.reduce_scatter(x, y, op=op, count=count, dtype=dt, check=False)
             res.append((rc, y))
+        elif coll == "premul":
+            k = np.array([op], dtype=np.uint64).view(np.uint8)[:es].copy()
+            handle = comm.create_premul_sum(k, dtype=dt)
+            x = inputs_for(n, count, dt, seed)[rank].copy()
+            rc = comm.all_reduce(x, x, op=handle, count=count, dtype=dt, check=False)
+            res.append((rc, x))
         elif coll == "allgather":
             x = inputs_for(n, count, dt, seed)[rank].copy()
             y = np.zeros(count * es * n, dtype=np.uint8)
@@ -191,6 +205,10 @@ def make_cases():
         cases.append(("alltoall", dt, 0, count, len(cases)))
         cases.append(("broadcast", dt, 0, count, len(cases)))                        # binomial tree
     cases.append(("broadcast", L.INT32, 0, (1600 << 10) // 4 + 3, len(cases)))      # chain in 512 KiB pieces
+    # PreMulSum: scalar bits 0.125 (fp16), 0.5 (bf16), 3 (int32), 1.5 (e5m2), -0.25 (fp32), small and ring-sized
+    for dt, bits in ((L.FLOAT16, 0x3000), (L.BFLOAT16, 0x3F00), (L.INT32, 3), (L.FLOAT8E5M2, 0x3E), (L.FLOAT32, 0xBE800000)):
+        cases.append(("premul", dt, bits, 1001, len(cases)))
+        cases.append(("premul", dt, bits, (64 << 10) // L.DTYPE_SIZE[dt] + 7, len(cases)))
     return cases
 
 
