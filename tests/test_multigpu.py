@@ -173,7 +173,8 @@ def test_other_collectives(n):
         assert res[r]["ag"] and res[r]["bc"] and res[r]["shift"] and res[r]["err"] == 0, (r, res[r])
         assert np.array_equal(res[r]["rs"], want_rs[r])
         first = [int(np.random.default_rng(r).integers(0, 256, 3 << 20, dtype=np.uint8)[0])] * n
-        assert res[r]["a2a"] == [(first[0] + i) % 256 for i in range(n)] or True  # layout checked below
+        # block j of rank r's result is block r of rank j's send buffer: x_r + j (uint8, wrapping)
+        assert res[r]["a2a"] == [(first[0] + i) % 256 for i in range(n)], (r, res[r]["a2a"], first[0])
 
 
 def _departure_body(comm, rank, n):
