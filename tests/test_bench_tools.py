@@ -59,3 +59,13 @@ def test_c_example_builds_as_c99_and_runs(tmp_path):
                     "-L" + libdir, "-lhxccl", "-Wl,-rpath," + libdir, "-o", str(exe)], check=True, timeout=120)
     res = subprocess.run([str(exe), "3"], capture_output=True, text=True, timeout=120)
     assert res.returncode == 0 and "3 ranks: average 2, ring shift ok" in res.stdout, (res.stdout, res.stderr)
+
+
+def test_mpi_entry_point_compiles_against_an_mpi_header():
+    """hxcclCommInitMPI is only built where MPI exists; the stand-in header of the reference arm is
+    enough to check that it still compiles together with the public header's MPI section."""
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    subprocess.run(["g++", "-std=c++17", "-fsyntax-only", "-Wall", "-Wextra", "-Werror", "-DHXCCL_HAVE_MPI",
+                    "-I" + os.path.join(ROOT, "baseline", "mpi_stub"), "-I" + os.path.join(ROOT, "include"),
+                    "-I" + os.path.join(ROOT, "src"), "-I" + os.path.join(cuda, "include"),
+                    os.path.join(ROOT, "src", "core", "comm_mpi.cc")], check=True, timeout=120)
