@@ -33,6 +33,7 @@ def main() -> int:
     ap.add_argument("--exact", type=int, default=1)
     ap.add_argument("--max-ctas", type=int, default=48, help="grid bound of the hxccl kernels during training")
     ap.add_argument("--check", action="store_true", help="print the loss of every step")
+    ap.add_argument("--compress", action="store_true", help="hxccl: average the buckets in bfloat16 (half the bytes)")
     args = ap.parse_args()
 
     import torch
@@ -61,9 +62,9 @@ def main() -> int:
     model = GPT2(cfg).cuda()
     ddp = DDP(model, device_ids=[local], bucket_cap_mb=25, gradient_as_bucket_view=True)
     if args.backend == "hxccl":
-        from hxccl_b200.parallel import fused_average_hook
+        from hxccl_b200.parallel import bf16_compress_average_hook, fused_average_hook
 
-        ddp.register_comm_hook(None, fused_average_hook)
+        ddp.register_comm_hook(None, bf16_compress_average_hook if args.compress else fused_average_hook)
     opt = torch.optim.AdamW(ddp.parameters(), lr=3e-4, fused=True)
     g = torch.Generator(device="cuda").manual_seed(1000 + rank)
 

@@ -85,3 +85,58 @@ def test_backend_matches_gloo(world):
         if p.is_alive():
             p.kill()
     assert all(m == "ok" for _, m in got), got
+
+
+def _ddp_worker(rank, world, port, q):
+    """Two steps of SGD on a small CPU model under DDP with each hook; every rank must end with the
+    weights of a single process that saw the whole batch (exactly for the fp32 hook up to summation
+    order, within bfloat16 rounding for the compressing one)."""
+    try:
+        import hxccl_b200.parallel as hp
+
+        hp.register()
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("hxccl", rank=rank, world_size=world)
+        torch.manual_seed(0)
+        data, target = torch.randn(world * 8, 16), torch.randn(world * 8, 4)
+
+        def make():
+            torch.manual_seed(1)
+            return torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.Tanh(), torch.nn.Linear(32, 4))
+
+        def train(model, x, y):
+            opt = torch.optim.SGD(model.parameters(), lr=0.1)
+            for _ in range(2):
+                opt.zero_grad()
+                torch.nn.functional.mse_loss(model(x), y).backward()
+                opt.step()
+            return torch.cat([p.detach().flatten() for p in model.parameters()])
+
+        want = train(make(), data, target)  # the whole batch in one process
+        mine = slice(rank * 8, rank * 8 + 8)
+        for compress, tol in ((False, 1e-5), (True, 2e-2)):
+            got = train(hp.wrap(make(), compress=compress, bucket_cap_mb=1), data[mine], target[mine])
+            assert torch.allclose(got, want, rtol=tol, atol=tol), (compress, (got - want).abs().max())
+            same = [torch.empty_like(got) for _ in range(world)]
+            dist.all_gather(same, got)
+            assert all(torch.equal(s, same[0]) for s in same)  # replicas stay identical
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except BaseException as e:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, f"{e!r}\n{traceback.format_exc()}"))
+
+
+def test_ddp_hooks_on_cpu():
+    world, ctx = 2, mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_ddp_worker, args=(r, world, 29671, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=180) for _ in range(world)]
+    for p in procs:
+        p.join(10)
+        if p.is_alive():
+            p.kill()
+    assert all(m == "ok" for _, m in got), got
