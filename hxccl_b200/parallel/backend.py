@@ -47,6 +47,9 @@ def register() -> None:
         return
     import torch.distributed as dist  # noqa: PLC0415
 
+    from ..utils.env import fill_env_from_openmpi  # noqa: PLC0415
+
+    fill_env_from_openmpi()  # under mpirun: RANK / WORLD_SIZE / LOCAL_RANK from Open MPI's variables
     ext = extension()
     dist.Backend.register_backend("hxccl", ext.create_backend, devices=["cuda", "cpu"])
     _registered = True

@@ -69,3 +69,17 @@ def test_mpi_entry_point_compiles_against_an_mpi_header():
                     "-I" + os.path.join(ROOT, "baseline", "mpi_stub"), "-I" + os.path.join(ROOT, "include"),
                     "-I" + os.path.join(ROOT, "src"), "-I" + os.path.join(cuda, "include"),
                     os.path.join(ROOT, "src", "core", "comm_mpi.cc")], check=True, timeout=120)
+
+
+def test_launch_environment_from_openmpi(monkeypatch):
+    from hxccl_b200.utils.env import fill_env_from_openmpi
+
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+        monkeypatch.delenv(k, raising=False)
+    monkeypatch.setenv("OMPI_COMM_WORLD_RANK", "3")
+    monkeypatch.setenv("OMPI_COMM_WORLD_SIZE", "8")
+    monkeypatch.setenv("OMPI_COMM_WORLD_LOCAL_RANK", "1")
+    monkeypatch.setenv("MASTER_PORT", "12345")  # what the user set stays
+    fill_env_from_openmpi()
+    assert (os.environ["RANK"], os.environ["WORLD_SIZE"], os.environ["LOCAL_RANK"]) == ("3", "8", "1")
+    assert os.environ["MASTER_ADDR"] == "127.0.0.1" and os.environ["MASTER_PORT"] == "12345"
