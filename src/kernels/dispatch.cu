@@ -166,8 +166,8 @@ cudaError_t launch_nvls(const NvlsArgs* args, LaunchShape s, cudaStream_t st, bo
 
 int max_resident_ctas(int threads) {
   // The collective kernels differ in register use from type to type; every one of them fits
-  // one 512-thread CTA per SM (__launch_bounds__(512)), so that is what is promised.
-  // (at most 128 registers per thread), hence two CTAs of 256 threads.
+  // one 512-thread CTA per SM (__launch_bounds__(512) caps them at 128 registers per thread),
+  // hence also two CTAs of 256 threads. That is what is promised, whatever the type.
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 1;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
