@@ -83,3 +83,23 @@ def test_launch_environment_from_openmpi(monkeypatch):
     fill_env_from_openmpi()
     assert (os.environ["RANK"], os.environ["WORLD_SIZE"], os.environ["LOCAL_RANK"]) == ("3", "8", "1")
     assert os.environ["MASTER_ADDR"] == "127.0.0.1" and os.environ["MASTER_PORT"] == "12345"
+
+
+def test_measurement_session_on_host_buffers(tmp_path):
+    """bench/measure.py in host mode (no GPU): one table per (collective, rank count), a session record,
+    and tables the plotting tool can read."""
+    out = tmp_path / "res"
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "bench", "measure.py"), "--out", str(out), "--ranks", "2,3",
+                          "--modes", "host", "--ops", "allreduce,sendrecv", "--min-bytes", "1024", "--max-bytes", "65536",
+                          "--factor", "8", "--iters", "3"], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout + res.stderr
+    session = json.loads((out / "session.json").read_text())
+    assert [r["file"] for r in session["runs"]] == ["allreduce_np2_host.txt", "sendrecv_np2_host.txt",
+                                                    "allreduce_np3_host.txt", "sendrecv_np3_host.txt"]
+    assert all(r["rc"] == 0 for r in session["runs"])
+    table = (out / "allreduce_np3_host.txt").read_text()
+    assert "# hx_perf  op=allreduce" in table and "ranks=3" in table and table.count("\n") >= 5
+    svg = tmp_path / "c.svg"
+    subprocess.run([sys.executable, os.path.join(ROOT, "bench", "plot.py"), "curves", str(out / "allreduce_np2_host.txt"),
+                    str(out / "allreduce_np3_host.txt"), "-o", str(svg)], check=True, timeout=60)
+    assert len(xml.dom.minidom.parse(str(svg)).getElementsByTagName("path")) == 2
