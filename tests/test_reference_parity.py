@@ -46,6 +46,10 @@ def _load_reference():
     lib.hxcclAllGather.argtypes = [vp, vp, C.c_size_t, C.c_int, vp, vp]
     lib.hxcclBroadcast.argtypes = [vp, vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
     lib.hxcclAlltoAll.argtypes = [vp, vp, C.c_size_t, C.c_int, vp, vp]
+    lib.hxcclGather.argtypes = [vp, vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
+    lib.hxcclScatter.argtypes = [vp, vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
+    lib.hxcclSend.argtypes = [vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
+    lib.hxcclRecv.argtypes = [vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
     lib.hxcclRedOpCreatePreMulSum.argtypes = [C.POINTER(C.c_int), vp, C.c_int, C.c_int, vp]
     lib.hxcclCommDestroy.argtypes = [vp]
     lib.hxcclCommResetStats.argtypes = [vp]
@@ -89,6 +93,24 @@ def _ref_child(rank, n, cases, id_q, out_q):
                 x = inputs_for(n, count * n, dt, seed)[rank].copy()
                 y = np.zeros(count * es, dtype=np.uint8)
                 rc = lib.hxcclReduceScatter(x.ctypes.data, y.ctypes.data, count, dt, op, comm, None)
+                res.append((rc, y))
+            elif coll == "gather":
+                x = inputs_for(n, count, dt, seed)[rank].copy()
+                y = np.zeros(count * es * n, dtype=np.uint8)
+                rc = lib.hxcclGather(x.ctypes.data, y.ctypes.data if rank == 0 else None, count, dt, 0, comm, None)
+                res.append((rc, y if rank == 0 else None))
+            elif coll == "scatter":
+                x = inputs_for(n, count * n, dt, seed)[0].copy()
+                y = np.zeros(count * es, dtype=np.uint8)
+                rc = lib.hxcclScatter(x.ctypes.data if rank == 0 else None, y.ctypes.data, count, dt, 0, comm, None)
+                res.append((rc, y))
+            elif coll == "shift":  # ring shift: Send and Recv in one group
+                x = inputs_for(n, count, dt, seed)[rank].copy()
+                y = np.zeros(count * es, dtype=np.uint8)
+                lib.hxcclGroupStart()
+                lib.hxcclSend(x.ctypes.data, count, dt, (rank + 1) % n, comm, None)
+                lib.hxcclRecv(y.ctypes.data, count, dt, (rank + n - 1) % n, comm, None)
+                rc = lib.hxcclGroupEnd()
                 res.append((rc, y))
             elif coll == "premul":  # `op` carries the scalar's bits
                 k = np.array([op], dtype=np.uint64).view(np.uint8)[:es].copy()
@@ -158,6 +180,26 @@ def _ours_body(comm, rank, n, cases):
             y = np.zeros(count * es, dtype=np.uint8)
             rc = comm.reduce_scatter(x, y, op=op, count=count, dtype=dt, check=False)
             res.append((rc, y))
+        elif coll == "gather":
+            x = inputs_for(n, count, dt, seed)[rank].copy()
+            y = np.zeros(count * es * n, dtype=np.uint8)
+            rc = comm.gather(x, y if rank == 0 else None, root=0, count=count, dtype=dt, check=False)
+            res.append((rc, y if rank == 0 else None))
+        elif coll == "scatter":
+            x = inputs_for(n, count * n, dt, seed)[0].copy()
+            y = np.zeros(count * es, dtype=np.uint8)
+            rc = comm.scatter(x if rank == 0 else None, y, root=0, count=count, dtype=dt, check=False)
+            res.append((rc, y))
+        elif coll == "shift":
+            import hxccl_b200 as hx  # noqa: PLC0415
+
+            x = inputs_for(n, count, dt, seed)[rank].copy()
+            y = np.zeros(count * es, dtype=np.uint8)
+            hx.group_start()
+            comm.send(x, (rank + 1) % n, count=count, dtype=dt)
+            comm.recv(y, (rank + n - 1) % n, count=count, dtype=dt)
+            rc = hx.group_end()
+            res.append((rc, y))
         elif coll == "premul":
             k = np.array([op], dtype=np.uint64).view(np.uint8)[:es].copy()
             handle = comm.create_premul_sum(k, dtype=dt)
@@ -204,6 +246,9 @@ def make_cases():
         cases.append(("allgather", dt, 0, count, len(cases)))
         cases.append(("alltoall", dt, 0, count, len(cases)))
         cases.append(("broadcast", dt, 0, count, len(cases)))                        # binomial tree
+        cases.append(("gather", dt, 0, count, len(cases)))
+        cases.append(("scatter", dt, 0, count, len(cases)))
+        cases.append(("shift", dt, 0, count, len(cases)))
     cases.append(("broadcast", L.INT32, 0, (1600 << 10) // 4 + 3, len(cases)))      # chain in 512 KiB pieces
     # PreMulSum: scalar bits 0.125 (fp16), 0.5 (bf16), 3 (int32), 1.5 (e5m2), -0.25 (fp32), small and ring-sized
     for dt, bits in ((L.FLOAT16, 0x3000), (L.BFLOAT16, 0x3F00), (L.INT32, 3), (L.FLOAT8E5M2, 0x3E), (L.FLOAT32, 0xBE800000)):
