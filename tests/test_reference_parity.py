@@ -46,6 +46,8 @@ def _load_reference():
     lib.hxcclAllGather.argtypes = [vp, vp, C.c_size_t, C.c_int, vp, vp]
     lib.hxcclBroadcast.argtypes = [vp, vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
     lib.hxcclAlltoAll.argtypes = [vp, vp, C.c_size_t, C.c_int, vp, vp]
+    szp = C.POINTER(C.c_size_t)
+    lib.hxcclAllToAllv.argtypes = [vp, szp, szp, vp, szp, szp, C.c_int, vp, vp]
     lib.hxcclGather.argtypes = [vp, vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
     lib.hxcclScatter.argtypes = [vp, vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
     lib.hxcclSend.argtypes = [vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
@@ -66,6 +68,16 @@ def _ref_stats(lib, comm):
 def inputs_for(n, count, dt, seed):
     es = L.DTYPE_SIZE[dt]
     return [np.random.default_rng(seed * 1000 + r).integers(0, 256, count * es, dtype=np.uint8) for r in range(n)]
+
+
+def v_layout(n, rank, mean, seed):
+    """Uneven AlltoAllv counts: rank i sends counts[i][j] elements to rank j, blocks packed with a gap of
+    one element between them on both sides."""
+    counts = np.random.default_rng(seed).integers(0, 2 * mean + 1, (n, n))
+    scounts, rcounts = [int(c) for c in counts[rank]], [int(c) for c in counts[:, rank]]
+    sdispls = [int(sum(scounts[:j]) + j) for j in range(n)]
+    rdispls = [int(sum(rcounts[:j]) + j) for j in range(n)]
+    return scounts, sdispls, rcounts, rdispls, sum(scounts) + n, sum(rcounts) + n
 
 
 def _ref_child(rank, n, cases, id_q, out_q):
@@ -93,6 +105,13 @@ def _ref_child(rank, n, cases, id_q, out_q):
                 x = inputs_for(n, count * n, dt, seed)[rank].copy()
                 y = np.zeros(count * es, dtype=np.uint8)
                 rc = lib.hxcclReduceScatter(x.ctypes.data, y.ctypes.data, count, dt, op, comm, None)
+                res.append((rc, y))
+            elif coll == "alltoallv":
+                sc, sd, rcn, rd, stot, rtot = v_layout(n, rank, count, seed)
+                x = inputs_for(n, stot, dt, seed)[rank].copy()
+                y = np.zeros(rtot * es, dtype=np.uint8)
+                arr = lambda v: (C.c_size_t * n)(*v)  # noqa: E731
+                rc = lib.hxcclAllToAllv(x.ctypes.data, arr(sc), arr(sd), y.ctypes.data, arr(rcn), arr(rd), dt, comm, None)
                 res.append((rc, y))
             elif coll == "gather":
                 x = inputs_for(n, count, dt, seed)[rank].copy()
@@ -180,6 +199,12 @@ def _ours_body(comm, rank, n, cases):
             y = np.zeros(count * es, dtype=np.uint8)
             rc = comm.reduce_scatter(x, y, op=op, count=count, dtype=dt, check=False)
             res.append((rc, y))
+        elif coll == "alltoallv":
+            sc, sd, rcn, rd, stot, rtot = v_layout(n, rank, count, seed)
+            x = inputs_for(n, stot, dt, seed)[rank].copy()
+            y = np.zeros(rtot * es, dtype=np.uint8)
+            rc = comm.all_to_allv(x, sc, sd, y, rcn, rd, dtype=dt, check=False)
+            res.append((rc, y))
         elif coll == "gather":
             x = inputs_for(n, count, dt, seed)[rank].copy()
             y = np.zeros(count * es * n, dtype=np.uint8)
@@ -246,6 +271,7 @@ def make_cases():
         cases.append(("allgather", dt, 0, count, len(cases)))
         cases.append(("alltoall", dt, 0, count, len(cases)))
         cases.append(("broadcast", dt, 0, count, len(cases)))                        # binomial tree
+        cases.append(("alltoallv", dt, 0, count, len(cases)))                        # uneven counts, gaps
         cases.append(("gather", dt, 0, count, len(cases)))
         cases.append(("scatter", dt, 0, count, len(cases)))
         cases.append(("shift", dt, 0, count, len(cases)))
