@@ -305,3 +305,86 @@ def test_host_collectives_equal_the_reference_bit_for_bit(n):
         if coll == "allreduce":  # and the in-process oracle the GPU tests rely on says the same
             want = oracle.allreduce([x.view(oracle.raw_dtype(dt)) for x in inputs_for(n, count, dt, seed)], dt, op)
             assert np.array_equal(ref[0][k][1], want[0].view(np.uint8)), (n, dt, op, count)
+
+
+def _invalid_calls(lib, comm, n):
+    """A battery of calls that must be refused, the same way by both libraries. `lib` is a ctypes
+    handle of either library (the public names and argument lists are identical)."""
+    x = np.ones(16, dtype=np.float32)
+    y = np.zeros(16, dtype=np.float32)
+    p, q, none = x.ctypes.data, y.ctypes.data, None
+    out = [
+        ("allreduce null comm", lib.hxcclAllReduce(p, q, 16, L.FLOAT32, L.SUM, None, None)),
+        ("allreduce bad dtype", lib.hxcclAllReduce(p, q, 16, 99, L.SUM, comm, None)),
+        ("allreduce bad op", lib.hxcclAllReduce(p, q, 16, L.FLOAT32, 99, comm, None)),
+        ("allreduce null send", lib.hxcclAllReduce(none, q, 16, L.FLOAT32, L.SUM, comm, None)),
+        ("allreduce null recv", lib.hxcclAllReduce(p, none, 16, L.FLOAT32, L.SUM, comm, None)),
+        ("allreduce size overflow", lib.hxcclAllReduce(p, q, 1 << 62, L.FLOAT64, L.SUM, comm, None)),
+        ("allreduce zero count null buffers", lib.hxcclAllReduce(none, none, 0, L.FLOAT32, L.SUM, comm, None)),
+        ("broadcast root too large", lib.hxcclBroadcast(p, q, 16, L.FLOAT32, n, comm, None)),
+        ("broadcast negative root", lib.hxcclBroadcast(p, q, 16, L.FLOAT32, -1, comm, None)),
+        ("reduce bad root", lib.hxcclReduce(p, q, 16, L.FLOAT32, L.SUM, n + 3, comm, None)),
+        ("gather bad root", lib.hxcclGather(p, q, 4, L.FLOAT32, -2, comm, None)),
+        ("send bad peer", lib.hxcclSend(p, 16, L.FLOAT32, n, comm, None)),
+        ("recv bad peer", lib.hxcclRecv(q, 16, L.FLOAT32, -1, comm, None)),
+        ("group end without start", lib.hxcclGroupEnd()),
+        ("avg on a valid call", lib.hxcclAllReduce(p, q, 16, L.FLOAT32, L.AVG, comm, None)),
+    ]
+    lib.hxcclGetErrorString.restype = C.c_char_p
+    lib.hxcclGetErrorString.argtypes = [C.c_int]
+    strings = [lib.hxcclGetErrorString(code).decode() for code in range(-1, 11)]
+    version = C.c_int()
+    lib.hxcclGetVersion(C.byref(version))
+    return out, strings, version.value, y.tolist()
+
+
+def _ref_invalid_child(rank, n, id_q, out_q):
+    try:
+        lib = _load_reference()
+        uid = RefId()
+        if rank == 0:
+            lib.hxcclGetUniqueId(C.byref(uid))
+            for _ in range(n - 1):
+                id_q.put(bytes(uid))
+        else:
+            uid = RefId.from_buffer_copy(id_q.get(timeout=60))
+        comm = C.c_void_p()
+        assert lib.hxcclCommInitRank(C.byref(comm), n, uid, rank) == 0
+        res = _invalid_calls(lib, comm, n)
+        lib.hxcclCommDestroy(comm)
+        out_q.put((rank, "ok", res))
+    except BaseException as e:  # noqa: BLE001
+        out_q.put((rank, "err", repr(e)))
+
+
+def _ours_invalid_body(comm, rank, n):
+    return _invalid_calls(L.lib(), C.c_void_p(comm.handle), n)
+
+
+def test_refusals_and_error_strings_equal_the_reference():
+    n = 2
+    ctx = mp.get_context("spawn")
+    id_q, out_q = ctx.Queue(), ctx.Queue()
+    procs = [ctx.Process(target=_ref_invalid_child, args=(r, n, id_q, out_q)) for r in range(n)]
+    for p in procs:
+        p.start()
+    ref = {}
+    try:
+        for _ in range(n):
+            rank, state, payload = out_q.get(timeout=120)
+            assert state == "ok", payload
+            ref[rank] = payload
+    finally:
+        for p in procs:
+            p.join(10)
+            if p.is_alive():
+                p.kill()
+    ours = run_ranks(n, _ours_invalid_body, timeout=120)
+    for r in range(n):
+        assert ours[r][0] == ref[r][0], [(a, b) for a, b in zip(ours[r][0], ref[r][0]) if a != b]
+        # hxcclGetErrorString, codes -1..10: the same words, except that hxcclSystemError (2) reads
+        # "system (network) error" here and "system (MPI) error" there: this library has no MPI transport
+        assert [s for i, s in enumerate(ours[r][1]) if i != 3] == [s for i, s in enumerate(ref[r][1]) if i != 3]
+        assert ours[r][1][3] == "system (network) error" and ref[r][1][3] == "system (MPI) error"
+        assert ours[r][2] == ref[r][2] == 200   # hxcclGetVersion
+        assert ours[r][3] == ref[r][3] == [1.0] * 16  # the one valid call (Avg of ones)
