@@ -388,3 +388,130 @@ def test_refusals_and_error_strings_equal_the_reference():
         assert ours[r][1][3] == "system (network) error" and ref[r][1][3] == "system (MPI) error"
         assert ours[r][2] == ref[r][2] == 200   # hxcclGetVersion
         assert ours[r][3] == ref[r][3] == [1.0] * 16  # the one valid call (Avg of ones)
+
+
+def _lifecycle_calls(lib, comm, rank, n):
+    """Communicator and operator lifecycle through the C API, written once for both libraries:
+    returns every observable (codes, sizes, ranks, handle values, results)."""
+    vp = C.c_void_p
+    lib.hxcclCommSplit.argtypes = [vp, C.c_int, C.c_int, C.POINTER(vp), C.POINTER(L.Config)]
+    lib.hxcclCommShrink.argtypes = [vp, C.POINTER(C.c_int), C.c_int, C.POINTER(vp), C.POINTER(L.Config), C.c_int]
+    lib.hxcclCommCount.argtypes = [vp, C.POINTER(C.c_int)]
+    lib.hxcclCommUserRank.argtypes = [vp, C.POINTER(C.c_int)]
+    lib.hxcclCommGetAsyncError.argtypes = [vp, C.POINTER(C.c_int)]
+    lib.hxcclCommFinalize.argtypes = [vp]
+    lib.hxcclCommAbort.argtypes = [vp]
+    lib.hxcclRedOpDestroy.argtypes = [C.c_int, vp]
+    out = []
+
+    def shape(c):
+        cnt, rk = C.c_int(-1), C.c_int(-1)
+        return (lib.hxcclCommCount(c, C.byref(cnt)), cnt.value, lib.hxcclCommUserRank(c, C.byref(rk)), rk.value)
+
+    out.append(("world", shape(comm)))
+    # split by parity with the order reversed inside each half
+    half = vp()
+    out.append(("split", lib.hxcclCommSplit(comm, rank % 2, -rank, C.byref(half), None), shape(half)))
+    x = np.full(5, float(rank), dtype=np.float64)
+    out.append(("split sum", lib.hxcclAllReduce(x.ctypes.data, x.ctypes.data, 5, L.FLOAT64, L.SUM, half, None), x.tolist()))
+    # no colour on rank 0: no communicator there
+    none = vp(123)
+    out.append(("nocolor", lib.hxcclCommSplit(comm, L.SPLIT_NOCOLOR if rank == 0 else 7, 0, C.byref(none), None),
+                none.value is None if rank == 0 else shape(none)))
+    # configuration checks
+    cfg = L.Config.initializer()
+    cfg.blocking = 0
+    bad = vp()
+    out.append(("config blocking 0", lib.hxcclCommSplit(comm, 0, 0, C.byref(bad), C.byref(cfg))))
+    cfg = L.Config.initializer()
+    cfg.magic = 1
+    out.append(("config magic", lib.hxcclCommSplit(comm, 0, 0, C.byref(bad), C.byref(cfg))))
+    # shrink: argument errors, then the survivors without the last rank
+    two = (C.c_int * 2)(n - 1, n - 1)
+    out.append(("shrink duplicate", lib.hxcclCommShrink(comm, two, 2, C.byref(bad), None, 0)))
+    me = (C.c_int * 1)(rank)
+    out.append(("shrink self", lib.hxcclCommShrink(comm, me, 1, C.byref(bad), None, 0)))
+    last = (C.c_int * 1)(n - 1)
+    out.append(("shrink flags", lib.hxcclCommShrink(comm, last, 1, C.byref(bad), None, 1)))
+    if rank != n - 1:
+        small = vp()
+        out.append(("shrink", lib.hxcclCommShrink(comm, last, 1, C.byref(small), None, 0), shape(small)))
+        y = np.ones(3, dtype=np.int32)
+        out.append(("shrink sum", lib.hxcclAllReduce(y.ctypes.data, y.ctypes.data, 3, L.INT32, L.SUM, small, None), y.tolist()))
+        lib.hxcclCommDestroy(small)
+    # operators: handle values, wrong type, destroyed, reuse of the slot, foreign communicator
+    k = np.array([0.25], dtype=np.float32)
+    op1, op2 = C.c_int(), C.c_int()
+    out.append(("premul create", lib.hxcclRedOpCreatePreMulSum(C.byref(op1), k.ctypes.data, L.FLOAT32, L.SCALAR_HOST_IMMEDIATE, comm),
+                op1.value))
+    out.append(("premul second", lib.hxcclRedOpCreatePreMulSum(C.byref(op2), k.ctypes.data, L.FLOAT32, L.SCALAR_HOST_IMMEDIATE, comm),
+                op2.value))
+    f = np.full(4, 8.0, dtype=np.float32)
+    out.append(("premul use", lib.hxcclAllReduce(f.ctypes.data, f.ctypes.data, 4, L.FLOAT32, op1.value, comm, None), f.tolist()))
+    d = np.ones(4, dtype=np.float64)
+    out.append(("premul wrong type", lib.hxcclAllReduce(d.ctypes.data, d.ctypes.data, 4, L.FLOAT64, op1.value, comm, None)))
+    out.append(("premul foreign comm", lib.hxcclAllReduce(f.ctypes.data, f.ctypes.data, 4, L.FLOAT32, op1.value, half, None)))
+    out.append(("premul destroy", lib.hxcclRedOpDestroy(op1.value, comm)))
+    out.append(("premul destroyed use", lib.hxcclAllReduce(f.ctypes.data, f.ctypes.data, 4, L.FLOAT32, op1.value, comm, None)))
+    out.append(("premul destroy twice", lib.hxcclRedOpDestroy(op1.value, comm)))
+    op3 = C.c_int()
+    out.append(("premul slot reuse", lib.hxcclRedOpCreatePreMulSum(C.byref(op3), k.ctypes.data, L.FLOAT32, L.SCALAR_HOST_IMMEDIATE, comm),
+                op3.value == op1.value))
+    out.append(("destroy builtin", lib.hxcclRedOpDestroy(L.SUM, comm)))
+    # finalize: later calls are usage errors; abort of a child is local
+    err = C.c_int(-1)
+    out.append(("async error", lib.hxcclCommGetAsyncError(comm, C.byref(err)), err.value))
+    out.append(("finalize", lib.hxcclCommFinalize(half)))
+    out.append(("after finalize", lib.hxcclAllReduce(x.ctypes.data, x.ctypes.data, 5, L.FLOAT64, L.SUM, half, None)))
+    out.append(("destroy finalized", lib.hxcclCommDestroy(half)))
+    if rank != 0:
+        out.append(("abort", lib.hxcclCommAbort(none)))
+    return out
+
+
+def _ref_lifecycle_child(rank, n, id_q, out_q):
+    try:
+        lib = _load_reference()
+        uid = RefId()
+        if rank == 0:
+            lib.hxcclGetUniqueId(C.byref(uid))
+            for _ in range(n - 1):
+                id_q.put(bytes(uid))
+        else:
+            uid = RefId.from_buffer_copy(id_q.get(timeout=60))
+        comm = C.c_void_p()
+        assert lib.hxcclCommInitRank(C.byref(comm), n, uid, rank) == 0
+        res = _lifecycle_calls(lib, comm, rank, n)
+        lib.hxcclCommDestroy(comm)
+        out_q.put((rank, "ok", res))
+    except BaseException as e:  # noqa: BLE001
+        import traceback
+
+        out_q.put((rank, "err", repr(e) + traceback.format_exc()))
+
+
+def _ours_lifecycle_body(comm, rank, n):
+    return _lifecycle_calls(L.lib(), C.c_void_p(comm.handle), rank, n)
+
+
+@pytest.mark.parametrize("n", [2, 5])
+def test_lifecycle_observables_equal_the_reference(n):
+    ctx = mp.get_context("spawn")
+    id_q, out_q = ctx.Queue(), ctx.Queue()
+    procs = [ctx.Process(target=_ref_lifecycle_child, args=(r, n, id_q, out_q)) for r in range(n)]
+    for p in procs:
+        p.start()
+    ref = {}
+    try:
+        for _ in range(n):
+            rank, state, payload = out_q.get(timeout=120)
+            assert state == "ok", payload
+            ref[rank] = payload
+    finally:
+        for p in procs:
+            p.join(10)
+            if p.is_alive():
+                p.kill()
+    ours = run_ranks(n, _ours_lifecycle_body, timeout=120)
+    for r in range(n):
+        assert ours[r] == ref[r], (r, [(a, b) for a, b in zip(ours[r], ref[r]) if a != b])
