@@ -515,3 +515,98 @@ def test_lifecycle_observables_equal_the_reference(n):
     ours = run_ranks(n, _ours_lifecycle_body, timeout=120)
     for r in range(n):
         assert ours[r] == ref[r], (r, [(a, b) for a, b in zip(ours[r], ref[r]) if a != b])
+
+
+def _group_calls(lib, comm, rank, n):
+    """Send/Recv and groups through the C API, once for both libraries (two ranks)."""
+    lib.hxcclGetLastError.restype = C.c_char_p
+    lib.hxcclGetLastError.argtypes = [C.c_void_p]
+    out, other = [], 1 - rank
+    # crossed exchange in one group (two blocking calls would deadlock)
+    a = np.arange(100000, dtype=np.float32) + rank
+    b = np.zeros_like(a)
+    codes = [lib.hxcclGroupStart(), lib.hxcclSend(a.ctypes.data, a.size, L.FLOAT32, other, comm, None),
+             lib.hxcclRecv(b.ctypes.data, b.size, L.FLOAT32, other, comm, None), lib.hxcclGroupEnd()]
+    out.append(("crossed", codes, float(b[0]), float(b[-1])))
+    # two messages to the same peer keep their order; nested groups; a collective in the same group
+    s1, s2 = np.full(3, 10 + rank, dtype=np.int32), np.full(3, 20 + rank, dtype=np.int32)
+    r1, r2 = np.zeros(3, dtype=np.int32), np.zeros(3, dtype=np.int32)
+    red = np.ones(4, dtype=np.int64)
+    codes = [lib.hxcclGroupStart(), lib.hxcclGroupStart(),
+             lib.hxcclSend(s1.ctypes.data, 3, L.INT32, other, comm, None),
+             lib.hxcclSend(s2.ctypes.data, 3, L.INT32, other, comm, None),
+             lib.hxcclGroupEnd(),
+             lib.hxcclAllReduce(red.ctypes.data, red.ctypes.data, 4, L.INT64, L.SUM, comm, None),
+             lib.hxcclRecv(r1.ctypes.data, 3, L.INT32, other, comm, None),
+             lib.hxcclRecv(r2.ctypes.data, 3, L.INT32, other, comm, None),
+             lib.hxcclGroupEnd()]
+    out.append(("ordered", codes, r1.tolist(), r2.tolist(), red.tolist()))
+    # a refused call inside a group is skipped, the rest of the group runs
+    t = np.full(2, 5.0 + rank, dtype=np.float64)
+    u = np.zeros(2, dtype=np.float64)
+    codes = [lib.hxcclGroupStart(), lib.hxcclSend(t.ctypes.data, 2, L.FLOAT64, 9, comm, None),
+             lib.hxcclSend(t.ctypes.data, 2, L.FLOAT64, other, comm, None),
+             lib.hxcclRecv(u.ctypes.data, 2, L.FLOAT64, other, comm, None), lib.hxcclGroupEnd()]
+    out.append(("refused inside", codes, u.tolist()))
+    # truncation: eight elements into room for five; only the receiver fails, the head arrives
+    big, room = np.arange(8, dtype=np.int32), np.full(5, -1, dtype=np.int32)
+    if rank == 1:
+        rc = lib.hxcclSend(big.ctypes.data, 8, L.INT32, 0, comm, None)
+        out.append(("truncated send", rc))
+    else:
+        rc = lib.hxcclRecv(room.ctypes.data, 5, L.INT32, 1, comm, None)
+        out.append(("truncated recv", rc, room.tolist(), b"truncated" in lib.hxcclGetLastError(comm)))
+    # the communicator still works afterwards
+    z = np.full(3, rank + 1.0, dtype=np.float32)
+    out.append(("after", lib.hxcclAllReduce(z.ctypes.data, z.ctypes.data, 3, L.FLOAT32, L.MAX, comm, None), z.tolist()))
+    err = C.c_int(-1)
+    lib.hxcclCommGetAsyncError.argtypes = [C.c_void_p, C.POINTER(C.c_int)]
+    out.append(("async", lib.hxcclCommGetAsyncError(comm, C.byref(err)), err.value))
+    return out
+
+
+def _ref_group_child(rank, n, id_q, out_q):
+    try:
+        lib = _load_reference()
+        uid = RefId()
+        if rank == 0:
+            lib.hxcclGetUniqueId(C.byref(uid))
+            id_q.put(bytes(uid))
+        else:
+            uid = RefId.from_buffer_copy(id_q.get(timeout=60))
+        comm = C.c_void_p()
+        assert lib.hxcclCommInitRank(C.byref(comm), n, uid, rank) == 0
+        res = _group_calls(lib, comm, rank, n)
+        lib.hxcclCommDestroy(comm)
+        out_q.put((rank, "ok", res))
+    except BaseException as e:  # noqa: BLE001
+        import traceback
+
+        out_q.put((rank, "err", repr(e) + traceback.format_exc()))
+
+
+def _ours_group_body(comm, rank, n):
+    return _group_calls(L.lib(), C.c_void_p(comm.handle), rank, n)
+
+
+def test_send_recv_and_groups_equal_the_reference():
+    n = 2
+    ctx = mp.get_context("spawn")
+    id_q, out_q = ctx.Queue(), ctx.Queue()
+    procs = [ctx.Process(target=_ref_group_child, args=(r, n, id_q, out_q)) for r in range(n)]
+    for p in procs:
+        p.start()
+    ref = {}
+    try:
+        for _ in range(n):
+            rank, state, payload = out_q.get(timeout=120)
+            assert state == "ok", payload
+            ref[rank] = payload
+    finally:
+        for p in procs:
+            p.join(10)
+            if p.is_alive():
+                p.kill()
+    ours = run_ranks(n, _ours_group_body, timeout=120)
+    for r in range(n):
+        assert ours[r] == ref[r], (r, [(a, b) for a, b in zip(ours[r], ref[r]) if a != b])
