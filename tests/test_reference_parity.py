@@ -330,6 +330,22 @@ def _invalid_calls(lib, comm, n):
         ("group end without start", lib.hxcclGroupEnd()),
         ("avg on a valid call", lib.hxcclAllReduce(p, q, 16, L.FLOAT32, L.AVG, comm, None)),
     ]
+    # AllToAllv with a bad argument on ONE rank only: the ranks agree, everybody refuses, nothing moves
+    rk = C.c_int(-1)
+    lib.hxcclCommUserRank.argtypes = [C.c_void_p, C.POINTER(C.c_int)]
+    lib.hxcclCommUserRank(comm, C.byref(rk))
+    ones, disp = (C.c_size_t * n)(*([2] * n)), (C.c_size_t * n)(*[2 * j for j in range(n)])
+    src, dst = np.ones(2 * n, dtype=np.float32), np.zeros(2 * n, dtype=np.float32)
+    lib.hxcclCommResetStats.argtypes = [C.c_void_p]
+    lib.hxcclCommGetStats.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
+    lib.hxcclCommResetStats(comm)
+    rc = lib.hxcclAllToAllv(src.ctypes.data, None if rk.value == 1 else ones, disp, dst.ctypes.data, ones, disp,
+                            L.FLOAT32, comm, None)
+    sent, msgs = C.c_uint64(), C.c_uint64()
+    lib.hxcclCommGetStats(comm, C.byref(sent), C.byref(msgs))
+    out.append(("alltoallv one bad rank", rc, sent.value, msgs.value, dst.tolist()))
+    rc = lib.hxcclAllToAllv(src.ctypes.data, ones, disp, dst.ctypes.data, ones, disp, L.FLOAT32, comm, None)
+    out.append(("alltoallv good", rc, dst.tolist()))
     lib.hxcclGetErrorString.restype = C.c_char_p
     lib.hxcclGetErrorString.argtypes = [C.c_int]
     strings = [lib.hxcclGetErrorString(code).decode() for code in range(-1, 11)]
@@ -610,3 +626,60 @@ def test_send_recv_and_groups_equal_the_reference():
     ours = run_ranks(n, _ours_group_body, timeout=120)
     for r in range(n):
         assert ours[r] == ref[r], (r, [(a, b) for a, b in zip(ours[r], ref[r]) if a != b])
+
+
+def _bootstrap_calls(lib, uid_struct, rank, n):
+    """hxcclCommInitRank with bad arguments and with every rank claiming to be rank 0."""
+    vp = C.c_void_p
+    comm = vp()
+    out = [("nranks 0", lib.hxcclCommInitRank(C.byref(comm), 0, uid_struct, 0)),
+           ("rank too large", lib.hxcclCommInitRank(C.byref(comm), n, uid_struct, n)),
+           ("negative rank", lib.hxcclCommInitRank(C.byref(comm), n, uid_struct, -1)),
+           ("null comm", lib.hxcclCommInitRank(None, n, uid_struct, rank))]
+    out.append(("duplicate ranks", lib.hxcclCommInitRank(C.byref(comm), n, uid_struct, 0)))
+    return out
+
+
+def _ref_bootstrap_child(rank, n, id_q, out_q):
+    try:
+        lib = _load_reference()
+        uid = RefId()
+        if rank == 0:
+            lib.hxcclGetUniqueId(C.byref(uid))
+            for _ in range(n - 1):
+                id_q.put(bytes(uid))
+        else:
+            uid = RefId.from_buffer_copy(id_q.get(timeout=60))
+        out_q.put((rank, "ok", _bootstrap_calls(lib, uid, rank, n)))
+    except BaseException as e:  # noqa: BLE001
+        out_q.put((rank, "err", repr(e)))
+
+
+def _ours_bootstrap_body(uid, rank, n):
+    from hxccl_b200._lib import UniqueId  # noqa: PLC0415
+
+    return _bootstrap_calls(L.lib(), UniqueId.from_buffer_copy(uid), rank, n)
+
+
+def test_bootstrap_refusals_equal_the_reference():
+    n = 3
+    ctx = mp.get_context("spawn")
+    id_q, out_q = ctx.Queue(), ctx.Queue()
+    procs = [ctx.Process(target=_ref_bootstrap_child, args=(r, n, id_q, out_q)) for r in range(n)]
+    for p in procs:
+        p.start()
+    ref = {}
+    try:
+        for _ in range(n):
+            rank, state, payload = out_q.get(timeout=120)
+            assert state == "ok", payload
+            ref[rank] = payload
+    finally:
+        for p in procs:
+            p.join(10)
+            if p.is_alive():
+                p.kill()
+    ours = run_ranks(n, _ours_bootstrap_body, make_comm=False, timeout=120)
+    for r in range(n):
+        assert ours[r] == ref[r], (r, ours[r], ref[r])
+    assert ref[0][-1] == ("duplicate ranks", L.INVALID_USAGE)
