@@ -34,7 +34,7 @@ def unavailable(rank: int, why: str) -> int:
     return 0
 
 
-def run(args, rank: int, world: int, local: int) -> int:
+def run(args, rank: int, world: int, local: int, config_of=None) -> int:
     if not LIB.exists():
         return unavailable(rank, "baseline/_ref/libhxccl_ref.so is missing: the reference has no setup.py/pyproject "
                                  "(pip install refuses it) and baseline/build_ref.py was not run where its sources are")
@@ -132,16 +132,16 @@ def run(args, rank: int, world: int, local: int) -> int:
     lib.hxcclCommDestroy(comm)
     if world > 1:
         dist.destroy_process_group()
+    config = config_of(world, nbytes, count) if config_of else {"bytes_per_rank": nbytes}
     if rank == 0:
         print(json.dumps({
             "metric": "allreduce_busbw_GBps", "value": round(algbw * factor, 3), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": vs_published(algbw * factor, world, nbytes, args.dtype), "dtype": args.dtype, "data": "synthetic U(-1,1), seed 1234+rank",
             "impl": "reference",
-            "config": {"model": "AllReduce sum, in place" if world > 1 else "AllReduce sum, out of place (one rank)", "global_batch": nbytes * world, "seq_len": count,
-                       "parallelism": f"{world} ranks, one per GPU", "bytes_per_rank": nbytes,
-                       "note": "unmodified reference sources (MPI stand-in header at compile time, socket bootstrap, "
-                               "CUDA IPC staging path); its calls block, events bracket completed work"},
+            "config": config,
+            "impl_note": "unmodified reference sources (MPI stand-in header at compile time, socket bootstrap, "
+                         "CUDA IPC staging path); its calls block, events bracket completed work",
             "algbw_GBps": round(algbw, 3),
             "e2e": {"value": round(nbytes / (e2e_ms * 1e-3) / 1e9 * factor, 3), "unit": "GB/s",
                     "ms_per_step": round(e2e_ms, 4), "h2d_bytes_per_step": nbytes,

@@ -11,8 +11,12 @@ prints one JSON line. `value` is the bus bandwidth in GB/s by the nccl-tests con
 algbw * 2(N-1)/N; with one GPU that factor is zero, so there `value` is the algorithm bandwidth
 of the local AllReduce (a copy) and `config.note` says so. The `e2e` figure repeats the
 measurement through the public Python API with the input copied from pinned host memory and a
-slice of the result read back every step. `--impl reference` runs the unmodified reference
-library instead when it could be built (see baseline/README.md), else reports why not.
+slice of the result read back every step. Before anything is timed the full-size result is
+checked: bit for bit against a replay of the reduction order on rank 0 (`verified`), and by
+tolerance against an fp64 sum for the in-switch `fast_mode`. The `nccl` block repeats a short
+size sweep with torch's NCCL backend in the same process, next to this library's `sweep`.
+`--impl reference` runs the unmodified reference library (built by baseline/build_ref.py from
+its sources) instead when that build is present, else reports why not.
 """
 from __future__ import annotations
 
@@ -38,6 +42,7 @@ def parse_args():
     ap.add_argument("--impl", default="hxccl", choices=["hxccl", "reference", "nccl"])
     ap.add_argument("--exact", type=int, default=1, help="1: bit-exact reduction order; 0: NVLS fast mode")
     ap.add_argument("--no-sweep", action="store_true", help="skip the small size sweep in the extras")
+    ap.add_argument("--no-nccl", action="store_true", help="skip the NCCL comparison in the extras")
     return ap.parse_args()
 
 
@@ -94,6 +99,15 @@ def reference_unavailable(reason: str) -> None:
 PUBLISHED_BUSBW_256MIB = {2: 268435456 / 43028e-6 / 1e9 * 1.0, 4: 268435456 / 110449e-6 / 1e9 * 1.5}
 
 
+def bench_config(world: int, nbytes: int, count: int) -> dict:
+    """The workload, in the same words for every arm."""
+    return {"model": "AllReduce sum, in place" if world > 1 else "AllReduce sum, out of place (one rank)",
+            "global_batch": nbytes * world, "seq_len": count,
+            "parallelism": f"{world} ranks, one per GPU", "bytes_per_rank": nbytes,
+            "note": ("one GPU: value is the algorithm bandwidth of the local out-of-place AllReduce (bus factor is 0)"
+                     if world == 1 else "value = algbw * 2(N-1)/N (nccl-tests bus bandwidth)")}
+
+
 def vs_published(value: float, world: int, nbytes: int, dtype: str):
     ref = PUBLISHED_BUSBW_256MIB.get(world) if (nbytes == 268435456 and dtype == "float32") else None
     return round(value / ref, 2) if ref else None
@@ -114,7 +128,7 @@ def main() -> int:
             if rank == 0:
                 reference_unavailable(f"reference arm could not be loaded: {e!r}"[:200])
             return 0
-        return ref_arm.run(args, rank, world, local)
+        return ref_arm.run(args, rank, world, local, bench_config)
 
     import torch  # noqa: PLC0415
     import torch.distributed as dist  # noqa: PLC0415
@@ -188,6 +202,51 @@ def main() -> int:
         barrier()
         return max_over_ranks(e0.elapsed_time(e1) / steps)
 
+    # ---- correctness of the full-size result, before any timing ------------------------------
+    def replay_on_rank0():
+        """The reference's ring order (block c starts at rank c, then c+1, c+2, ... each added as
+        the left operand) replayed with plain tensor adds from the regenerated inputs of all
+        ranks; fp32 / bf16 adds round once per hop exactly as the kernels do. Also an fp64 sum."""
+        xs = []
+        for r in range(world):
+            gr = torch.Generator(device="cuda").manual_seed(1234 + r)
+            xs.append(torch.rand(count, generator=gr, device="cuda", dtype=torch.float32).mul_(2).sub_(1).to(tdt))
+        exact = torch.empty_like(xs[0])
+        wide = torch.zeros(count, dtype=torch.float64, device="cuda")
+        base, extra = divmod(count, world)
+        for c in range(world):
+            lo = c * base + min(c, extra)
+            hi = lo + base + (1 if c < extra else 0)
+            acc = xs[c][lo:hi].clone()
+            for k in range(1, world):
+                acc = xs[(c + k) % world][lo:hi] + acc
+            exact[lo:hi] = acc
+        for x in xs:
+            wide += x.double()
+        return exact, wide
+
+    def check_result(expect_exact: bool):
+        """Runs one out-of-place AllReduce of the full message and compares rank 0's result."""
+        dst.zero_()
+        allreduce(src, dst)
+        torch.cuda.synchronize()
+        out = None
+        if rank == 0:
+            exact, wide = replay_on_rank0()
+            if expect_exact:
+                same = bool(torch.equal(dst, exact))
+                out = True if same else {"max_abs_diff": float((dst.double() - exact.double()).abs().max())}
+            else:
+                err = float((dst.double() - wide).abs().max())
+                tol = world * (2.0 ** -22 if tdt == torch.float32 else 2.0 ** -7) * 4
+                out = {"max_abs_err_vs_fp64": err, "tolerance": tol, "ok": err <= tol}
+            del exact, wide
+        barrier()
+        return out
+
+    verified = check_result(True) if (comm is not None and nbytes >= (64 << 10)) else None
+    variant_checked = comm.device_info()["variant"] if comm is not None else None
+
     # ---- headline: kernel-only -------------------------------------------------------------
     sampler = ClockSampler(local) if rank == 0 else None
     for _ in range(max(args.warmup, 3)):
@@ -201,6 +260,7 @@ def main() -> int:
     step = (lambda: allreduce(src, dst)) if world == 1 else (lambda: allreduce(dst, dst))
     ms = timed(step, args.steps, 0)
     launches = launches_of() - l0
+    headline_path = comm.device_info() if comm is not None else {"kind": "nccl"}
     factor = 2.0 * (world - 1) / world if world > 1 else 1.0
     algbw = nbytes / (ms * 1e-3) / 1e9
     value = algbw * factor
@@ -224,23 +284,34 @@ def main() -> int:
     fast = None
     if comm is not None and world > 2 and args.exact and "nvls" in info["kind"]:
         comm.tune(variant=0, exact=False)
+        fast_check = check_result(False)
         dst.copy_(src)
         fast_ms = timed(lambda: allreduce(dst, dst), args.steps, 3)
         fast = {"value": round(nbytes / (fast_ms * 1e-3) / 1e9 * factor, 2), "unit": "GB/s",
-                "ms_per_step": round(fast_ms, 4), "variant": comm.device_info()["variant"],
+                "ms_per_step": round(fast_ms, 4), "variant": comm.device_info()["variant"], "checked": fast_check,
                 "note": "HXCCL_EXACT=0: float sums combined by the switch, order unspecified"}
         comm.tune(variant=0, exact=True)
 
     # ---- extras: latency and a short sweep ------------------------------------------------------
-    sweep = []
-    if not args.no_sweep:
-        for sz in (8, 1024, 64 << 10, 1 << 20, 16 << 20, 64 << 20):
+    # In place like the headline. A sum in place grows by a factor of N per call, so the values
+    # are reset before each size and the calls per size are bounded to keep them finite.
+    sweep_sizes = (8, 1024, 64 << 10, 1 << 20, 16 << 20, 64 << 20)
+    sweep_warmup = 5
+    most_calls = int(120 / max(1.0, __import__("math").log2(max(world, 2))))
+
+    def sweep_with(fn) -> list:
+        rows = []
+        for sz in sweep_sizes:
             n_el = max(1, sz // es)
             a, b = src[:n_el], dst[:n_el]
-            t = timed((lambda: allreduce(a, b)) if world == 1 else (lambda: allreduce(b, b)),
-                      50 if sz <= (1 << 20) else 20, 5)
-            sweep.append({"bytes": n_el * es, "us": round(t * 1e3, 2),
-                          "busbw_GBps": round(n_el * es / (t * 1e-3) / 1e9 * factor, 2)})
+            b.copy_(a)
+            steps = min(50 if sz <= (1 << 20) else 20, most_calls - sweep_warmup)
+            t = timed((lambda: fn(a, b)) if world == 1 else (lambda: fn(b, b)), steps, sweep_warmup)
+            rows.append({"bytes": n_el * es, "us": round(t * 1e3, 2),
+                         "busbw_GBps": round(n_el * es / (t * 1e-3) / 1e9 * factor, 2)})
+        return rows
+
+    sweep = sweep_with(allreduce) if not args.no_sweep else []
 
     # ---- extras: the same step through the neighbour-ring kernel (bit-exact like the headline).
     # Last of all measurements and guarded: whatever happens here cannot cost the figures above.
@@ -248,10 +319,11 @@ def main() -> int:
     if comm is not None and world > 1 and args.exact:
         try:
             comm.tune(variant=6, exact=True)
+            ring_check = check_result(True)
             dst.copy_(src)
             ring_ms = timed(lambda: allreduce(dst, dst), args.steps, 3)
             ring = {"value": round(nbytes / (ring_ms * 1e-3) / 1e9 * factor, 2), "unit": "GB/s",
-                    "ms_per_step": round(ring_ms, 4), "variant": comm.device_info()["variant"],
+                    "ms_per_step": round(ring_ms, 4), "variant": comm.device_info()["variant"], "verified": ring_check,
                     "note": "HXCCL_VARIANT=ring: reduce-scatter and all-gather around the ring, same bits"}
             comm.tune(variant=0, exact=True)
         except Exception as e:  # noqa: BLE001
@@ -259,11 +331,30 @@ def main() -> int:
 
     clocks = sampler.stop() if sampler else None
     if comm is not None:
-        variant = comm.device_info()
         err = comm.async_error()
         comm.destroy()
     else:
-        variant, err = {"kind": "nccl"}, 0
+        err = 0
+
+    # ---- extras: torch's NCCL backend on the same sizes, same process, same timing -------------
+    nccl = None
+    if args.impl == "hxccl" and world > 1 and not args.no_sweep and not args.no_nccl:
+        try:
+            os.environ.setdefault("MASTER_PORT", "29533")
+            pg = dist.new_group(backend="nccl")
+
+            def nccl_allreduce(a, b):
+                dist.all_reduce(b, group=pg)
+
+            rows = sweep_with(nccl_allreduce)
+            dst.copy_(src)
+            big_ms = timed(lambda: nccl_allreduce(dst, dst), args.steps, 3)
+            rows.append({"bytes": nbytes, "us": round(big_ms * 1e3, 2),
+                         "busbw_GBps": round(nbytes / (big_ms * 1e-3) / 1e9 * factor, 2)})
+            nccl = {"version": ".".join(map(str, torch.cuda.nccl.version())), "sweep": rows,
+                    "note": "torch.distributed all_reduce, NCCL backend, in place, fp32 sum"}
+        except Exception as e:  # noqa: BLE001
+            nccl = {"error": str(e)[:200]}
     if world > 1:
         dist.destroy_process_group()
     if rank == 0:
@@ -273,16 +364,14 @@ def main() -> int:
             "higher_is_better": True, "scaling": "weak", "vs_baseline": vs_published(value, world, nbytes, args.dtype),
             "dtype": args.dtype,
             "data": "synthetic U(-1,1), seed 1234+rank", "impl": args.impl,
-            "config": {"model": "AllReduce sum, in place" if world > 1 else "AllReduce sum, out of place (one rank)", "global_batch": nbytes * world, "seq_len": count,
-                       "parallelism": f"{world} ranks, one per GPU", "bytes_per_rank": nbytes,
-                       "l2_policy": "message larger than L2 (126 MB): no flush needed",
-                       "exact_order": bool(args.exact), "device_path": variant,
-                       "note": ("one GPU: value is the algorithm bandwidth of the local out-of-place AllReduce (bus factor is 0)"
-                                if world == 1 else "value = algbw * 2(N-1)/N (nccl-tests bus bandwidth)")},
+            "config": bench_config(world, nbytes, count),
+            "l2_policy": "message larger than L2 (126 MB): no flush needed",
+            "exact_order": bool(args.exact), "device_path": headline_path,
+            "verified": verified, "verified_variant": variant_checked,
             "algbw_GBps": round(algbw, 2),
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "ms_per_step": round(e2e_ms, 4),
                     "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": host_out.numel() * es},
-            "gpu_launches": int(launches), "clocks": clocks, "fast_mode": fast, "ring_mode": ring, "sweep": sweep, "async_error": err,
+            "gpu_launches": int(launches), "clocks": clocks, "fast_mode": fast, "ring_mode": ring, "sweep": sweep, "nccl": nccl, "async_error": err,
         }
         print(json.dumps(line))
     return 0

@@ -72,6 +72,7 @@ def lib() -> C.CDLL:
         "hxcclCommCount": [vp, C.POINTER(i)],
         "hxcclCommUserRank": [vp, C.POINTER(i)],
         "hxcclAllReduce": [vp, vp, sz, i, i, vp, vp],
+        "hxcclAllReduceCast": [vp, vp, sz, i, i, vp, vp],
         "hxcclAllGather": [vp, vp, sz, i, vp, vp],
         "hxcclReduceScatter": [vp, vp, sz, i, i, vp, vp],
         "hxcclBroadcast": [vp, vp, sz, i, i, vp, vp],
@@ -108,6 +109,7 @@ def lib() -> C.CDLL:
         "hxcclWorldDestroy": [vp],
         "hxcclWorldTune": [vp, i, i, i],
         "hxcclWorldAllReduce": [vp, C.POINTER(vp), C.POINTER(vp), sz, i, i, vp, i, vp],
+        "hxcclWorldAllReduceCast": [vp, C.POINTER(vp), C.POINTER(vp), sz, i, i, vp],
         "hxcclWorldReduceScatter": [vp, C.POINTER(vp), C.POINTER(vp), sz, i, i, vp, vp],
         "hxcclWorldReduce": [vp, C.POINTER(vp), C.POINTER(vp), sz, i, i, vp, i, vp],
         "hxcclWorldAllGather": [vp, C.POINTER(vp), C.POINTER(vp), sz, vp],

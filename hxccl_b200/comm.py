@@ -24,17 +24,21 @@ _NP_DT = {np.dtype(np.int8): L.INT8, np.dtype(np.uint8): L.UINT8, np.dtype(np.in
           np.dtype(np.float64): L.FLOAT64}
 
 
-def _torch_dt(t) -> int:
-    import torch  # noqa: PLC0415
+_TORCH_DT: dict = {}  # filled on first use: torch is imported only when tensors show up
 
-    table = {torch.int8: L.INT8, torch.uint8: L.UINT8, torch.int32: L.INT32, torch.int64: L.INT64,
-             torch.float16: L.FLOAT16, torch.float32: L.FLOAT32, torch.float64: L.FLOAT64,
-             torch.bfloat16: L.BFLOAT16, torch.float8_e4m3fn: L.FLOAT8E4M3,
-             torch.float8_e5m2: L.FLOAT8E5M2}
-    for name, code in (("uint32", L.UINT32), ("uint64", L.UINT64)):
-        if hasattr(torch, name):
-            table[getattr(torch, name)] = code
-    return table[t.dtype]
+
+def _torch_dt(t) -> int:
+    if not _TORCH_DT:
+        import torch  # noqa: PLC0415
+
+        _TORCH_DT.update({torch.int8: L.INT8, torch.uint8: L.UINT8, torch.int32: L.INT32, torch.int64: L.INT64,
+                          torch.float16: L.FLOAT16, torch.float32: L.FLOAT32, torch.float64: L.FLOAT64,
+                          torch.bfloat16: L.BFLOAT16, torch.float8_e4m3fn: L.FLOAT8E4M3,
+                          torch.float8_e5m2: L.FLOAT8E5M2})
+        for name, code in (("uint32", L.UINT32), ("uint64", L.UINT64)):
+            if hasattr(torch, name):
+                _TORCH_DT[getattr(torch, name)] = code
+    return _TORCH_DT[t.dtype]
 
 
 def ptr(buf: Any) -> Optional[int]:
@@ -205,6 +209,15 @@ class Communicator:
         return self._ok(L.lib().hxcclAllReduce(ptr(send), ptr(recv), n, dtype_of(send, dtype), op,
                                                self._h, _stream(stream, send, recv)),
                         "hxcclAllReduce", check)
+
+    def all_reduce_cast(self, send, recv=None, wire_dtype: int = L.BFLOAT16, op: int = L.SUM, count=None,
+                        stream=None, check: bool = True) -> int:
+        """AllReduce of fp32 CUDA buffers with fp16 / bf16 on the wire, one kernel
+        (hxcclAllReduceCast): the bits of cast, all_reduce in the wire type, cast back."""
+        recv = send if recv is None else recv
+        n = _numel(send) if count is None else count
+        return self._ok(L.lib().hxcclAllReduceCast(ptr(send), ptr(recv), n, wire_dtype, op, self._h,
+                                                   _stream(stream, send, recv)), "hxcclAllReduceCast", check)
 
     def all_gather(self, send, recv, count=None, dtype=None, stream=None, check=True) -> int:
         n = _numel(send) if count is None else count

@@ -171,6 +171,15 @@ class HxcclBackend : public Backend {
         ok(hxcclAllReduce(t.data_ptr(), t.data_ptr(), t.numel(), to_dt(t.scalar_type()), op, comm_, s), "AllReduce");
     });
   }
+  // fp32 CUDA tensor reduced in place with fp16 / bf16 on the wire, one kernel (hxcclAllReduceCast)
+  c10::intrusive_ptr<Work> allreduce_cast(at::Tensor& t, hxcclDataType_t wire, hxcclRedOp_t op) {
+    check_tensor(t);
+    TORCH_CHECK_VALUE(t.is_cuda() && t.scalar_type() == at::kFloat, "hxccl: allreduce_cast takes an fp32 CUDA tensor");
+    std::vector<at::Tensor> ts{t};
+    return run(OpType::ALLREDUCE, t, ts, ts, [&](hxcclStream_t s) {
+      ok(hxcclAllReduceCast(t.data_ptr(), t.data_ptr(), t.numel(), wire, op, comm_, s), "AllReduceCast");
+    });
+  }
   c10::intrusive_ptr<Work> allreduce_coalesced(std::vector<at::Tensor>& ts,
                                                const AllreduceCoalescedOptions& o) override {
     AllreduceOptions ao;
@@ -403,9 +412,15 @@ std::tuple<std::string, int, unsigned long long> device_info(const c10::intrusiv
   hxcclCommDeviceInfo(h->comm(), kind, sizeof kind, &variant, &launches);
   return {kind, variant, launches};
 }
+c10::intrusive_ptr<Work> allreduce_cast(const c10::intrusive_ptr<Backend>& b, at::Tensor t, bool bf16, bool average) {
+  auto* h = dynamic_cast<HxcclBackend*>(b.get());
+  TORCH_CHECK(h, "not an hxccl backend");
+  return h->allreduce_cast(t, bf16 ? hxcclBfloat16 : hxcclFloat16, average ? hxcclAvg : hxcclSum);
+}
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("allreduce_cast", &allreduce_cast);
   m.def("create_backend", &create_backend);
   m.def("tune", &tune);
   m.def("device_info", &device_info);

@@ -82,6 +82,11 @@ class World:
                                              self._scalar(scalar), order, _stream(stream)),
                  "hxcclWorldAllReduce")
 
+    def all_reduce_cast(self, send, recv, count: int, wire_dt: int, op: int = L.SUM, stream=None) -> None:
+        """fp32 buffers, `wire_dt` (FLOAT16 / BFLOAT16) carried and summed (hxcclAllReduceCast)."""
+        self._ok(L.lib().hxcclWorldAllReduceCast(self._h, _ptrs(send), _ptrs(recv), count, wire_dt, op,
+                                                 _stream(stream)), "hxcclWorldAllReduceCast")
+
     def reduce_scatter(self, send, recv, recvcount: int, dt: int, op: int = L.SUM, scalar=None,
                        stream=None) -> None:
         self._ok(L.lib().hxcclWorldReduceScatter(self._h, _ptrs(send), _ptrs(recv), recvcount, dt, op,

@@ -68,6 +68,12 @@ def tune(variant: int = 0, exact: bool = True, max_ctas: int = 0, group=None) ->
     extension().tune(_backend_of(group), variant, int(exact), max_ctas)
 
 
+def all_reduce_cast(tensor, bf16: bool = True, average: bool = True, group=None):
+    """In-place AllReduce of an fp32 CUDA tensor with bfloat16 (or float16) on the wire, as one
+    kernel (hxcclAllReduceCast). Returns the Work object; the tensor needs at least 32 Ki elements."""
+    return extension().allreduce_cast(_backend_of(group), tensor, bf16, average)
+
+
 def device_info(group=None) -> dict:
     kind, variant, launches = extension().device_info(_backend_of(group))
     return {"kind": kind, "variant": variant, "launches": launches}

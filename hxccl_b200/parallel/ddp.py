@@ -20,14 +20,22 @@ def fused_average_hook(state, bucket):
 
 
 def bf16_compress_average_hook(state, bucket):
-    """Like fused_average_hook with half the bytes on the links: the bucket is cast to bfloat16,
-    averaged in bfloat16 (each rank's contribution is scaled by 1/N and rounded to bfloat16 before
-    the sum, the library's Avg rule) and cast back into the bucket when the collective is done."""
+    """Like fused_average_hook with half the bytes on the links: every gradient is rounded to
+    bfloat16, scaled by 1/N and summed in bfloat16 (the library's Avg rule), and the result is
+    widened back into the fp32 bucket. On the window device path all of that is one kernel
+    (hxcclAllReduceCast: the cast happens as the bucket is read and written); small buckets and
+    the other paths cast with tensor ops around an ordinary bfloat16 AllReduce, with the same bits."""
     import torch  # noqa: PLC0415
     import torch.distributed as dist  # noqa: PLC0415
 
+    from . import backend as hb  # noqa: PLC0415
+
     group = state if state is not None else dist.group.WORLD
     buf = bucket.buffer()
+    if (buf.is_cuda and buf.dtype == torch.float32 and buf.numel() * 2 >= 64 * 1024
+            and dist.get_world_size(group) > 1 and _fused_cast_ok(group)):
+        work = hb.all_reduce_cast(buf, bf16=True, average=True, group=None if state is None else group)
+        return work.get_future().then(lambda fut: fut.value()[0])
     small = buf.to(torch.bfloat16)
     work = dist.all_reduce(small, op=dist.ReduceOp.AVG, group=group, async_op=True)
 
@@ -36,6 +44,22 @@ def bf16_compress_average_hook(state, bucket):
         return buf
 
     return work.get_future().then(widen)
+
+
+_FUSED_OK: dict = {}
+
+
+def _fused_cast_ok(group) -> bool:
+    """Whether the group's communicator runs on the window device path (asked once per group)."""
+    key = id(group)
+    if key not in _FUSED_OK:
+        from . import backend as hb  # noqa: PLC0415
+
+        try:
+            _FUSED_OK[key] = hb.device_info(group).get("kind", "").startswith("window")
+        except Exception:  # noqa: BLE001  (another backend behind this group)
+            _FUSED_OK[key] = False
+    return _FUSED_OK[key]
 
 
 def wrap(module, device=None, bucket_cap_mb: int = 25, process_group=None, compress: bool = False, **kw):

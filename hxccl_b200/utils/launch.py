@@ -5,6 +5,13 @@ communicator and calls `fn(comm, rank, nranks, *args)`. The parent collects the 
 (anything picklable) and re-raises the first failure. With `gpus=True` rank r uses CUDA device
 r % device_count and creates its context before the communicator, so the device path starts.
 This is the stand-in for `mpirun -np N` that the reference's tests use (CMakeLists.txt:47-142).
+
+GPU ranks get two defaults unless the caller's `env` says otherwise: a short device-side wait
+limit (HXCCL_WAIT_LIMIT_MS) and NVSwitch multicast off (HXCCL_NVLS=0; pass `nvls=True` for the
+runs that are about multicast). When one rank fails, the survivors are given longer than that
+wait limit to leave through their bounded waits and destroy their communicator (which unbinds
+the window from the multicast object) before any process is killed: a rank must not be ended
+while its kernels spin or while its memory is bound to a multicast object.
 """
 from __future__ import annotations
 
@@ -55,12 +62,26 @@ def _child(rank: int, n: int, fn: Callable, args: tuple, uid_recv, uid_send: Lis
         out.send(("err", f"rank {rank}: {e!r}\n{traceback.format_exc()}"))
 
 
+GPU_WAIT_LIMIT_MS = 5000  # default device-side wait limit of ranks started with gpus=True
+
+
 def run_ranks(n: int, fn: Callable, *args: Any, env: Optional[Dict[str, str]] = None, gpus: bool = False,
               timeout: float = 120.0, make_comm: bool = True,
-              rank_env: Optional[Dict[int, Dict[str, str]]] = None) -> List[Any]:
+              rank_env: Optional[Dict[int, Dict[str, str]]] = None, nvls: bool = False) -> List[Any]:
     """Returns [fn's result on rank 0, ..., on rank n-1]. `fn` must be importable (module level).
-    `rank_env[r]` adds environment variables for rank r only."""
+    `rank_env[r]` adds environment variables for rank r only. `nvls` leaves NVSwitch multicast
+    on for GPU ranks (default off, see the module text)."""
     ctx = mp.get_context("spawn")
+    env = dict(env or {})
+    if gpus:
+        env.setdefault("HXCCL_WAIT_LIMIT_MS", os.environ.get("HXCCL_WAIT_LIMIT_MS", str(GPU_WAIT_LIMIT_MS)))
+        if not nvls:
+            env.setdefault("HXCCL_NVLS", "0")
+    # how long a survivor may need to notice a dead peer and leave on its own
+    try:
+        grace = (float(env.get("HXCCL_WAIT_LIMIT_MS", 0)) / 1000.0 if gpus else 0.0) + 5.0
+    except ValueError:
+        grace = 10.0
     uid_pipes = [ctx.Pipe(duplex=False) for _ in range(n - 1)]
     outs = [ctx.Pipe(duplex=False) for _ in range(n)]
     procs = []
@@ -78,6 +99,7 @@ def run_ranks(n: int, fn: Callable, *args: Any, env: Optional[Dict[str, str]] = 
 
     deadline = time.monotonic() + timeout
     pending = set(range(n))
+    shortened = False
     while pending:
         for r in sorted(pending):
             if outs[r][0].poll(0.05):
@@ -90,15 +112,19 @@ def run_ranks(n: int, fn: Callable, *args: Any, env: Optional[Dict[str, str]] = 
             elif not procs[r].is_alive() and not outs[r][0].poll(0):
                 errors.append(f"rank {r}: process ended with exit code {procs[r].exitcode} and no result")
                 pending.discard(r)
-        if errors:  # one rank failed: give the others a moment to report, then stop waiting
-            deadline = min(deadline, time.monotonic() + 3.0)
-            errors_seen = True
+        if errors and not shortened:  # one rank failed: the others get the grace period to report
+            deadline = min(deadline, time.monotonic() + grace)
+            shortened = True
         if time.monotonic() > deadline:
             break
     for r in sorted(pending):
         errors.append(f"rank {r}: no result" + ("" if errors else f" within {timeout} s"))
+    # Ranks that reported are on their way out (communicator destroyed in _child); the others
+    # get the grace period once more, in total, before the last resort.
+    give_up = time.monotonic() + (grace if errors else 5.0)
     for p in procs:
-        p.join(0.5 if errors else 5)
+        p.join(max(0.1, give_up - time.monotonic()))
+    for p in procs:
         if p.is_alive():
             p.kill()  # this exact child, by handle
             p.join()

@@ -20,7 +20,7 @@ extern "C" {
 hxcclResult_t hxcclCommDeviceInfo(hxcclComm_t comm, char* kind, size_t kind_len, int* variant,
                                   unsigned long long* launches);
 /* Forces the AllReduce variant of later calls (0 auto, 1 one-shot, 2 two-shot, 3 NVLS,
- * 6 neighbour ring), the
+ * 6 neighbour ring, 7 flag-in-data lines for small messages), the
  * exactness mode (1 = floats match the host path bit for bit) and the largest grid (0 keeps it).
  * Every rank must make the same call. */
 hxcclResult_t hxcclCommTune(hxcclComm_t comm, int variant, int exact, int max_ctas);
@@ -29,6 +29,17 @@ hxcclResult_t hxcclCommTune(hxcclComm_t comm, int variant, int exact, int max_ct
  * "roles_min" (bytes from which AllReduce runs as a three-role pipeline). Same call on every
  * rank. hxcclInvalidArgument for an unknown name. */
 hxcclResult_t hxcclCommTuneKnob(hxcclComm_t comm, const char* name, long value);
+
+/* AllReduce of fp32 device buffers with a 16-bit float type on the wire (hxcclFloat16 or
+ * hxcclBfloat16): every value is rounded to wire_dt, the ranks' values are combined under
+ * wire_dt's rules in the ring order (op as for hxcclAllReduce, hxcclAvg and PreMulSum operators
+ * created for wire_dt included), and the result is widened back to fp32 - bit for bit what
+ * "cast, hxcclAllReduce in wire_dt, cast back" gives, in one kernel and with half the bytes on
+ * the links (a gradient bucket of a data-parallel step). count * 2 must be at least 64 KiB
+ * (the size from which hxcclAllReduce takes the ring order) and the communicator needs two or
+ * more ranks on the window device path; otherwise hxcclInvalidUsage, and nothing was done. */
+hxcclResult_t hxcclAllReduceCast(const void* send, void* recv, size_t count, hxcclDataType_t wire_dt,
+                                 hxcclRedOp_t op, hxcclComm_t comm, hxcclStream_t stream);
 
 /* Phase timers of the collective kernels (communicators created with HXCCL_TRACE=1): 16
  * nanosecond sums per CTA since the previous read (staging in, first flag, first wait,
@@ -64,7 +75,7 @@ hxcclResult_t hxcclTestNarrowConvert(hxcclDataType_t dt, unsigned long long* mis
 
 /* Plans one launch without a device: kind 0 generic exchange (amount = largest block of a pair),
  * 1 two-shot / NVLS AllReduce (amount = message bytes), 2 the same as three-role pipeline,
- * 3 neighbour ring (amount = largest ring block), for `nranks` ranks whose staging halves hold
+ * 3 neighbour ring (amount = largest ring block), 4 the same for ReduceScatter, for `nranks` ranks whose staging halves hold
  * `half_bytes` each, with the default tuning, then HXCCL_TUNE_FILE when set, then `max_ctas` (0 keeps it) and one optional
  * knob (`knob` may be NULL). shape = {ctas, threads, steps, epochs, sub_bytes}. Returns
  * hxcclSuccess when the shape fits the window layout the kernels assume and covers `amount`,
@@ -93,6 +104,10 @@ hxcclResult_t hxcclWorldTuneKnob(hxcclWorld_t world, const char* name, long valu
 hxcclResult_t hxcclWorldAllReduce(hxcclWorld_t world, const void* const* send, void* const* recv,
                                   size_t count, hxcclDataType_t dt, hxcclRedOp_t op,
                                   const void* scalar, int order, hxcclStream_t stream);
+/* hxcclAllReduceCast in the world: send[r] / recv[r] hold fp32, wire_dt travels */
+hxcclResult_t hxcclWorldAllReduceCast(hxcclWorld_t world, const void* const* send, void* const* recv,
+                                      size_t count, hxcclDataType_t wire_dt, hxcclRedOp_t op,
+                                      hxcclStream_t stream);
 hxcclResult_t hxcclWorldReduceScatter(hxcclWorld_t world, const void* const* send,
                                       void* const* recv, size_t recvcount, hxcclDataType_t dt,
                                       hxcclRedOp_t op, const void* scalar, hxcclStream_t stream);

@@ -33,9 +33,9 @@ hxcclResult_t host_done(hxcclComm* c, hxcclResult_t r) {
   return r == hxcclSuccess ? r : comm_fail(c, r, c->wire->error);
 }
 hxcclResult_t dev_done(hxcclComm* c, hxcclResult_t r, Traffic t) {
-  if (r != hxcclSuccess) return comm_fail(c, r, c->dev->error);
-  c->dev_bytes += t.bytes;
-  c->dev_msgs += t.msgs;
+  if (r != hxcclSuccess) return comm_fail(c, r, c->device.path->error);
+  c->device.bytes += t.bytes;
+  c->device.msgs += t.msgs;
   return r;
 }
 HostCtx ctx(hxcclComm* c) { return HostCtx{*c->wire, c->rank, c->nranks}; }
@@ -86,7 +86,7 @@ hxcclResult_t run_alltoallv(hxcclComm* c, Path path, void* stream, const char* s
   TraceRange range("hxccl:alltoall");
   if (path == Path::Device)  // the kernel stages through the windows, so overlap is harmless
     return dev_done(c,
-                    c->dev->alltoallv(send, sb.data(), so.data(), recv, rb.data(), ro.data(),
+                    c->device.path->alltoallv(send, sb.data(), so.data(), recv, rb.data(), ro.data(),
                                       max_pair, stream),
                     traffic_alltoallv(c->rank, c->nranks, sb.data()));
   // in-place or overlapping buffers: the exchange would overwrite blocks not yet sent
@@ -124,7 +124,7 @@ hxcclResult_t hxcclAllReduce(const void* send, void* recv, size_t count, hxcclDa
   return dispatch(c, [=] {
     TraceRange range("hxccl:allreduce");
     if (path == Path::Device)
-      return dev_done(c, c->dev->allreduce(send, recv, count, dt, plan, order, stream),
+      return dev_done(c, c->device.path->allreduce(send, recv, count, dt, plan, order, stream),
                       traffic_allreduce(order, c->rank, c->nranks, count, es));
     std::vector<char> tmp;
     const void* in = host_premul(plan, send, count, dt, tmp);
@@ -133,6 +133,28 @@ hxcclResult_t hxcclAllReduce(const void* send, void* recv, size_t count, hxcclDa
                           : host_allreduce_doubling(ctx(c), in, recv, count, dt, plan.base);
     if (r == hxcclSuccess) host_finish(plan, recv, count, dt);
     return host_done(c, r);
+  });
+}
+
+// An extension (include/hxccl_ext.h): fp32 device buffers, a 16-bit float type on the wire.
+hxcclResult_t hxcclAllReduceCast(const void* send, void* recv, size_t count, hxcclDataType_t wire_dt,
+                                 hxcclRedOp_t op, hxcclComm_t c, hxcclStream_t stream) {
+  if (hxcclResult_t r = check_args(c, send, recv, count, 1, hxcclFloat32)) return r;
+  if (wire_dt != hxcclFloat16 && wire_dt != hxcclBfloat16)
+    return comm_fail(c, hxcclInvalidArgument, "the wire type must be hxcclFloat16 or hxcclBfloat16");
+  OpPlan plan;
+  if (hxcclResult_t r = plan_op(c, op, wire_dt, &plan)) return r;
+  const size_t es = dtype_size(wire_dt);
+  if (choose_order(count * es) != kOrderRing)
+    return comm_fail(c, hxcclInvalidUsage, "the fused cast AllReduce needs a message that takes the ring order");
+  Path path;
+  if (hxcclResult_t r = pick_path(c, send, recv, &path)) return r;
+  if (path != Path::Device) return comm_fail(c, hxcclInvalidUsage, "the fused cast AllReduce is for device buffers");
+  return dispatch(c, [=] {
+    TraceRange range("hxccl:allreduce_cast");
+    const hxcclResult_t r = c->device.path->allreduce_cast(send, recv, count, wire_dt, plan, stream);
+    if (r == hxcclInvalidUsage) return comm_fail(c, r, c->device.path->error);  // not offered here: no failure state
+    return dev_done(c, r, traffic_allreduce(kOrderRing, c->rank, c->nranks, count, es));
   });
 }
 
@@ -147,7 +169,7 @@ hxcclResult_t hxcclAllGather(const void* send, void* recv, size_t sendcount, hxc
   return dispatch(c, [=] {
     TraceRange range("hxccl:allgather");
     if (path == Path::Device)
-      return dev_done(c, c->dev->allgather(send, recv, block, stream),
+      return dev_done(c, c->device.path->allgather(send, recv, block, stream),
                       traffic_ring_blocks(c->nranks, block));
     return host_done(c, host_allgather(ctx(c), send, recv, block));
   });
@@ -167,7 +189,7 @@ hxcclResult_t hxcclReduceScatter(const void* send, void* recv, size_t recvcount,
   return dispatch(c, [=] {
     TraceRange range("hxccl:reducescatter");
     if (path == Path::Device)
-      return dev_done(c, c->dev->reducescatter(send, recv, recvcount, dt, plan, stream),
+      return dev_done(c, c->device.path->reducescatter(send, recv, recvcount, dt, plan, stream),
                       traffic_ring_blocks(c->nranks, block));
     std::vector<char> tmp;
     const void* in = host_premul(plan, send, recvcount * c->nranks, dt, tmp);
@@ -189,7 +211,7 @@ hxcclResult_t hxcclBroadcast(const void* send, void* recv, size_t count, hxcclDa
   return dispatch(c, [=] {
     TraceRange range("hxccl:broadcast");
     if (path == Path::Device)
-      return dev_done(c, c->dev->broadcast(send, recv, bytes, root, stream),
+      return dev_done(c, c->device.path->broadcast(send, recv, bytes, root, stream),
                       traffic_broadcast(c->rank, c->nranks, bytes, root));
     return host_done(c, host_broadcast(ctx(c), send, recv, bytes, root));
   });
@@ -216,7 +238,7 @@ hxcclResult_t hxcclReduce(const void* send, void* recv, size_t count, hxcclDataT
   return dispatch(c, [=] {
     TraceRange range("hxccl:reduce");
     if (path == Path::Device)
-      return dev_done(c, c->dev->reduce(send, recv, count, dt, plan, root, stream),
+      return dev_done(c, c->device.path->reduce(send, recv, count, dt, plan, root, stream),
                       traffic_reduce(c->rank, c->nranks, bytes, root));
     std::vector<char> tmp;
     const void* in = host_premul(plan, send, count, dt, tmp);
@@ -241,7 +263,7 @@ hxcclResult_t hxcclGather(const void* send, void* recv, size_t count, hxcclDataT
   return dispatch(c, [=] {
     TraceRange range("hxccl:gather");
     if (path == Path::Device)
-      return dev_done(c, c->dev->gather(send, recv, block, root, stream),
+      return dev_done(c, c->device.path->gather(send, recv, block, root, stream),
                       traffic_gather(c->rank, c->nranks, block, root));
     return host_done(c, host_gather(ctx(c), send, recv, block, root));
   });
@@ -262,7 +284,7 @@ hxcclResult_t hxcclScatter(const void* send, void* recv, size_t count, hxcclData
   return dispatch(c, [=] {
     TraceRange range("hxccl:scatter");
     if (path == Path::Device)
-      return dev_done(c, c->dev->scatter(send, recv, block, root, stream),
+      return dev_done(c, c->device.path->scatter(send, recv, block, root, stream),
                       traffic_scatter(c->rank, c->nranks, block, root));
     return host_done(c, host_scatter(ctx(c), send, recv, block, root));
   });
@@ -275,7 +297,7 @@ hxcclResult_t hxcclAllToAllv(const void* send, const size_t sc[], const size_t s
                              const size_t rc[], const size_t rd[], hxcclDataType_t dt,
                              hxcclComm_t c, hxcclStream_t stream) {
   if (!c) return hxcclInvalidArgument;
-  if (c->finalized) return comm_fail(c, hxcclInvalidUsage, "communicator was finalized");
+  if (c->closed) return comm_fail(c, hxcclInvalidUsage, "communicator was finalized");
   const size_t es = dtype_size(dt);
   struct Verdict {
     uint64_t status, largest;
@@ -377,34 +399,28 @@ hxcclResult_t hxcclRedOpCreatePreMulSum(hxcclRedOp_t* op, void* scalar, hxcclDat
   if (dtype_size(dt) == 0) return comm_fail(c, hxcclInvalidArgument, "unknown datatype");
   if (residence != hxcclScalarDevice && residence != hxcclScalarHostImmediate)
     return comm_fail(c, hxcclInvalidArgument, "unknown scalar residence");
-  size_t slot = 0;  // lowest free slot, so a destroyed op's handle comes back
-  while (slot < c->user_ops.size() && c->user_ops[slot].live) ++slot;
-  if (slot >> kOpSlotBits)
-    return comm_fail(c, hxcclInternalError, "too many live PreMulSum ops on this communicator");
-  if (slot == c->user_ops.size()) c->user_ops.emplace_back();
-  UserOp& u = c->user_ops[slot];
-  u = UserOp{};
-  u.live = true;
-  u.dt = dt;
-  u.by_pointer = residence == hxcclScalarDevice;
-  if (u.by_pointer) {
-    u.ptr = scalar;
-  } else if (classify(scalar) == MemKind::Device) {
+  if (residence == hxcclScalarHostImmediate && classify(scalar) == MemKind::Device)
     return comm_fail(c, hxcclInvalidArgument,
                      "hxcclScalarHostImmediate needs a scalar in host memory");
-  } else {
-    std::memcpy(u.value, scalar, dtype_size(dt));
-  }
-  *op = static_cast<hxcclRedOp_t>(hxcclNumOps + (c->op_tag << kOpSlotBits) + int(slot));
+  const long slot = c->ops.claim();
+  if (slot < 0)
+    return comm_fail(c, hxcclInternalError, "too many live PreMulSum ops on this communicator");
+  ScalarOp& u = c->ops.at(slot);
+  u.dt = dt;
+  if (residence == hxcclScalarDevice)
+    u.deferred = scalar;
+  else
+    std::memcpy(u.bits, scalar, dtype_size(dt));
+  *op = c->ops.handle(slot);
   return hxcclSuccess;
 }
 
 hxcclResult_t hxcclRedOpDestroy(hxcclRedOp_t op, hxcclComm_t c) {
   if (!c) return hxcclInvalidArgument;
-  const long slot = user_op_slot(c, op);
+  const long slot = c->ops.find(op);
   if (slot < 0)
     return comm_fail(c, hxcclInvalidArgument, "not a live PreMulSum op of this communicator");
-  c->user_ops[slot].live = false;
+  c->ops.release(slot);
   return hxcclSuccess;
 }
 

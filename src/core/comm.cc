@@ -24,7 +24,7 @@ hxcclResult_t make_comm(hxcclComm_t* out, std::shared_ptr<Channel> chan) {
   c->nranks = chan->size();
   c->chan = std::move(chan);
   c->wire = std::make_unique<HostWire>(c->chan);
-  c->op_tag = next_op_tag();
+  c->ops = OpTable(next_op_tag());
   device_eager_start(c);
   *out = c;
   return hxcclSuccess;
@@ -39,10 +39,10 @@ hxcclResult_t check_config(const hxcclConfig_t* cfg) {
 }
 
 void teardown(hxcclComm* c, bool orderly) {
-  if (c->dev) {
-    c->dev->drain();
-    if (orderly && std::strstr(c->dev->kind(), "nvls")) c->chan->barrier();
-    c->dev.reset();
+  if (c->device.path) {
+    c->device.path->drain();
+    if (orderly && std::strstr(c->device.path->kind(), "nvls")) c->chan->barrier();
+    c->device.path.reset();
   }
   c->wire.reset();
   delete c;
@@ -86,7 +86,7 @@ hxcclResult_t hxcclCommSplit(hxcclComm_t comm, int color, int key, hxcclComm_t* 
   if (!comm || !newcomm || (color < 0 && color != HXCCL_SPLIT_NOCOLOR))
     return hxcclInvalidArgument;
   if (hxcclResult_t r = check_config(config)) return comm_fail(comm, r, "unsupported config");
-  const uint64_t seq = comm->derived++;
+  const uint64_t seq = comm->offspring.splits++;
   const int mine[2] = {color, key};
   std::vector<int> all(2 * size_t(comm->nranks));
   if (hxcclResult_t r = comm->chan->allgather(mine, all.data(), sizeof mine))
@@ -132,7 +132,7 @@ hxcclResult_t hxcclCommShrink(hxcclComm_t comm, int* excl, int nexcl, hxcclComm_
   }
   const int me = int(std::find(members.begin(), members.end(), comm->rank) - members.begin());
   return make_comm(newcomm,
-                   comm->chan->child(members, me, mix_id(comm->chan->id(), comm->shrunk[salt]++, salt)));
+                   comm->chan->child(members, me, mix_id(comm->chan->id(), comm->offspring.shrinks[salt]++, salt)));
 }
 
 hxcclResult_t hxcclCommAbort(hxcclComm_t comm) {
@@ -143,18 +143,18 @@ hxcclResult_t hxcclCommAbort(hxcclComm_t comm) {
 
 hxcclResult_t hxcclCommFinalize(hxcclComm_t comm) {
   if (!comm) return hxcclInvalidArgument;
-  if (comm->dev) comm->dev->drain();
-  comm->finalized = true;
+  if (comm->device.path) comm->device.path->drain();
+  comm->closed = true;
   return hxcclSuccess;
 }
 
 hxcclResult_t hxcclCommGetAsyncError(hxcclComm_t comm, hxcclResult_t* err) {
   if (!comm || !err) return hxcclInvalidArgument;
-  if (comm->dev && comm->async_error == hxcclSuccess) {
+  if (comm->device.path && comm->fail.sticky == hxcclSuccess) {
     std::string why;
-    if (hxcclResult_t r = comm->dev->broken(&why)) comm_fail(comm, r, why);
+    if (hxcclResult_t r = comm->device.path->broken(&why)) comm_fail(comm, r, why);
   }
-  *err = comm->async_error;
+  *err = comm->fail.sticky;
   return hxcclSuccess;
 }
 
@@ -191,19 +191,19 @@ const char* hxcclGetErrorString(hxcclResult_t r) {
   }
 }
 
-const char* hxcclGetLastError(hxcclComm_t comm) { return comm ? comm->last_error.c_str() : ""; }
+const char* hxcclGetLastError(hxcclComm_t comm) { return comm ? comm->fail.text.c_str() : ""; }
 
 hxcclResult_t hxcclCommGetStats(hxcclComm_t comm, uint64_t* bytes, uint64_t* msgs) {
   if (!comm || !bytes || !msgs) return hxcclInvalidArgument;
-  *bytes = comm->wire->bytes_sent + comm->dev_bytes;
-  *msgs = comm->wire->msgs_sent + comm->dev_msgs;
+  *bytes = comm->wire->bytes_sent + comm->device.bytes;
+  *msgs = comm->wire->msgs_sent + comm->device.msgs;
   return hxcclSuccess;
 }
 
 hxcclResult_t hxcclCommResetStats(hxcclComm_t comm) {
   if (!comm) return hxcclInvalidArgument;
   comm->wire->bytes_sent = comm->wire->msgs_sent = 0;
-  comm->dev_bytes = comm->dev_msgs = 0;
+  comm->device.bytes = comm->device.msgs = 0;
   return hxcclSuccess;
 }
 

@@ -43,6 +43,12 @@ class DevicePath {
 
   virtual hxcclResult_t allreduce(const void* send, void* recv, size_t count, int dt,
                                   const OpPlan& plan, int order, void* stream) = 0;
+  // fp32 buffers reduced with `wire_dt` (fp16 / bf16) on the wire; paths without a fused
+  // kernel answer hxcclInvalidUsage and the caller casts for itself
+  virtual hxcclResult_t allreduce_cast(const void*, void*, size_t, int /*wire_dt*/, const OpPlan&, void* /*stream*/) {
+    error = "this device path has no fused cast AllReduce";
+    return hxcclInvalidUsage;
+  }
   virtual hxcclResult_t allgather(const void* send, void* recv, size_t block_bytes,
                                   void* stream) = 0;
   virtual hxcclResult_t reducescatter(const void* send, void* recv, size_t per, int dt,

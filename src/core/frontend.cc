@@ -11,25 +11,17 @@ namespace hx {
 
 hxcclResult_t comm_fail(hxcclComm* c, hxcclResult_t r, const std::string& msg) {
   if (c) {
-    c->last_error = msg;
+    c->fail.text = msg;
     if (r == hxcclSystemError || r == hxcclInternalError || r == hxcclRemoteError || r == hxcclTimeout)
-      c->async_error = r;
+      c->fail.sticky = r;
   }
   return r;
-}
-
-long user_op_slot(const hxcclComm* c, hxcclRedOp_t op) {
-  const long v = static_cast<long>(op) - hxcclNumOps;
-  if (v < 0 || (v >> kOpSlotBits) != c->op_tag) return -1;
-  const long slot = v & ((1L << kOpSlotBits) - 1);
-  if (slot >= static_cast<long>(c->user_ops.size()) || !c->user_ops[slot].live) return -1;
-  return slot;
 }
 
 hxcclResult_t check_args(hxcclComm* c, const void* send, const void* recv, size_t count,
                          size_t multiplier, hxcclDataType_t dt) {
   if (!c) return hxcclInvalidArgument;
-  if (c->finalized) return comm_fail(c, hxcclInvalidUsage, "communicator was finalized");
+  if (c->closed) return comm_fail(c, hxcclInvalidUsage, "communicator was finalized");
   const size_t es = dtype_size(dt);
   if (es == 0) return comm_fail(c, hxcclInvalidArgument, "unknown datatype");
   if (count != 0 && count > SIZE_MAX / es / multiplier)
@@ -61,18 +53,18 @@ hxcclResult_t plan_op(hxcclComm* c, hxcclRedOp_t op, hxcclDataType_t dt, OpPlan*
     }
     return hxcclSuccess;
   }
-  const long slot = user_op_slot(c, op);
+  const long slot = c->ops.find(op);
   if (slot < 0) return comm_fail(c, hxcclInvalidArgument, "unknown op for this communicator");
-  const UserOp& u = c->user_ops[slot];
+  const ScalarOp& u = c->ops.at(slot);
   if (u.dt != dt)
     return comm_fail(c, hxcclInvalidArgument, "PreMulSum op was created for another datatype");
   plan->premul = true;
-  if (!u.by_pointer) {
-    std::memcpy(plan->scalar, u.value, dtype_size(dt));
-  } else if (classify(u.ptr) == MemKind::Device) {
-    plan->scalar_dev = u.ptr;  // the kernel loads it, ordered after earlier work on the stream
+  if (!u.deferred) {
+    std::memcpy(plan->scalar, u.bits, dtype_size(dt));
+  } else if (classify(u.deferred) == MemKind::Device) {
+    plan->scalar_dev = u.deferred;  // the kernel loads it, ordered after earlier work on the stream
   } else {
-    std::memcpy(plan->scalar, u.ptr, dtype_size(dt));
+    std::memcpy(plan->scalar, u.deferred, dtype_size(dt));
   }
   return hxcclSuccess;
 }
@@ -88,12 +80,12 @@ void device_eager_start(hxcclComm* c) {
     want = cuda_context_exists() ? 1 : 0;
   int no = want ? 0 : 1;
   if (c->chan->max_int(&no) != hxcclSuccess) {
-    c->dev_error = hxcclSystemError;
-    c->dev_error_msg = "agreement on starting the device path failed: " + c->chan->error;
+    c->device.down = hxcclSystemError;
+    c->device.down_why = "agreement on starting the device path failed: " + c->chan->error;
     return;
   }
   if (no) return;
-  c->dev = start_device_path(c, &c->dev_error, &c->dev_error_msg);
+  c->device.path = start_device_path(c, &c->device.down, &c->device.down_why);
 }
 
 hxcclResult_t pick_path(hxcclComm* c, const void* a, const void* b, Path* out) {
@@ -105,16 +97,16 @@ hxcclResult_t pick_path(hxcclComm* c, const void* a, const void* b, Path* out) {
     *out = Path::Host;
     return hxcclSuccess;
   }
-  if (!c->dev && c->dev_error == hxcclSuccess)
-    c->dev = start_device_path(c, &c->dev_error, &c->dev_error_msg);
-  if (c->dev && c->dev_error == hxcclSuccess) {
+  if (!c->device.path && c->device.down == hxcclSuccess)
+    c->device.path = start_device_path(c, &c->device.down, &c->device.down_why);
+  if (c->device.path && c->device.down == hxcclSuccess) {
     std::string why;
-    if (hxcclResult_t r = c->dev->broken(&why)) {
-      c->dev_error = r;
-      c->dev_error_msg = why;
+    if (hxcclResult_t r = c->device.path->broken(&why)) {
+      c->device.down = r;
+      c->device.down_why = why;
     }
   }
-  if (c->dev_error != hxcclSuccess) return comm_fail(c, c->dev_error, c->dev_error_msg);
+  if (c->device.down != hxcclSuccess) return comm_fail(c, c->device.down, c->device.down_why);
   *out = Path::Device;
   return hxcclSuccess;
 }

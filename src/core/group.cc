@@ -53,11 +53,18 @@ hxcclResult_t run_host_p2p(const std::vector<QueuedP2p>& ops) {
   return first;
 }
 
-// Device Send/Recv: one fused peer-copy launch per communicator.
+// Device Send/Recv: one fused peer-copy launch per communicator. The launches of a group are
+// serialised on a stream and each one waits for its peers' kernels, so every rank must issue
+// them in the same order whatever order its calls named the communicators in (rank 0: Send on
+// c1, Recv on c2; rank 1: Send on c2, Recv on c1 - the crossed case of the reference's
+// tests/repro_two_comm_group.cc). The channel id is the same on every member of a communicator,
+// which makes it a rank-independent sort key.
 hxcclResult_t run_device_p2p(const std::vector<QueuedP2p>& ops) {
   std::vector<hxcclComm*> comms;
   for (const QueuedP2p& q : ops)
     if (std::find(comms.begin(), comms.end(), q.c) == comms.end()) comms.push_back(q.c);
+  std::stable_sort(comms.begin(), comms.end(),
+                   [](const hxcclComm* a, const hxcclComm* b) { return a->chan->id() < b->chan->id(); });
   hxcclResult_t first = hxcclSuccess;
   for (hxcclComm* c : comms) {
     std::vector<P2pOp> mine;
@@ -68,12 +75,12 @@ hxcclResult_t run_device_p2p(const std::vector<QueuedP2p>& ops) {
         mine.push_back(q.op);
         if (!have_stream) stream = q.stream, have_stream = true;
         if (q.op.is_send) {
-          c->dev_bytes += q.op.bytes;
-          ++c->dev_msgs;
+          c->device.bytes += q.op.bytes;
+          ++c->device.msgs;
         }
       }
-    const hxcclResult_t r = c->dev->p2p_batch(mine, stream);
-    if (r != hxcclSuccess && first == hxcclSuccess) first = comm_fail(c, r, c->dev->error);
+    const hxcclResult_t r = c->device.path->p2p_batch(mine, stream);
+    if (r != hxcclSuccess && first == hxcclSuccess) first = comm_fail(c, r, c->device.path->error);
   }
   return first;
 }

@@ -60,11 +60,38 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
   int var = choose_variant(bytes, dt, plan, n(), tune, forced_variant);
   // recursive doubling gives every rank its own operand order; only the variant in which each
   // rank folds for itself can replay that
-  if (order == kOrderDoubling && tune.exact && !is_integer(dt)) var = kVarOneShot;
+  if (order == kOrderDoubling && tune.exact && !is_integer(dt) && var != kVarLL) var = kVarOneShot;
   if (world() && var == kVarNvls) var = kVarTwoShot;
+  if (var == kVarLL) {
+    // A line carries the low 32 bits of the epoch. Zero is what a cleared region holds, and
+    // when the upper half of the epoch moves on, lines of 2^32 steps ago could match again:
+    // then every rank clears its own region (in stream order) and this call takes the ordinary
+    // one-shot kernel, whose all-to-all hand-shake separates the clearing from later lines.
+    if ((epoch >> 32) != ll_era_) {
+      ll_era_ = epoch >> 32;
+      for (const WinView& v : views)
+        if (cudaError_t e = cudaMemsetAsync(v.win[v.rank] + kOffLL, 0, kLLBytes, st)) return e;
+      var = kVarOneShot;
+    } else if (uint32_t(epoch) == 0) {
+      var = kVarOneShot;
+    }
+  }
   last_variant = var;
   cudaError_t rc;
   ++launches;
+  if (var == kVarLL) {
+    const size_t lines = (bytes + 7) / 8;
+    Geometry g;
+    g.threads = 256;
+    g.ctas = int(std::max<size_t>(1, std::min<size_t>(std::min(32, tune.max_ctas), (lines + 255) / 256)));
+    std::vector<LLArgs> args(views.size());
+    for (size_t r = 0; r < views.size(); ++r)
+      build_allreduce_ll(&args[r], views[r], epoch, b[r].send, b[r].recv, count, dt, plan, order,
+                         tune.nvls && tune.ll_mc && !world());
+    epoch += 1;
+    const LLArgs* a = stage(args, st, &rc);
+    return rc != cudaSuccess ? rc : launch_ll(dt, a, shape(g), st);
+  }
   if (var == kVarOneShot) {
     // the recursive-doubling order costs n log n combines per element: give a CTA less of it
     const Geometry g = plan_xchg(bytes, n(), views[0].half_bytes, tune,
@@ -116,8 +143,39 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
   return roles ? launch_twoshot_roles(dt, a, shape(g), st) : launch_twoshot(dt, a, shape(g), st);
 }
 
+cudaError_t Engine::allreduce_cast(const RankBufs* b, size_t count, int wire_dt, const OpPlan& plan,
+                                   cudaStream_t st) {
+  const size_t bytes = count * dtype_size(wire_dt);
+  const Geometry g = plan_sliced(bytes, n(), views[0].half_bytes, tune);
+  HX_CHECK_PLAN(kPlanSliced, g, bytes);
+  std::vector<TwoShotArgs> args(views.size());
+  for (size_t r = 0; r < views.size(); ++r)
+    build_allreduce_twoshot(&args[r], views[r], epoch, g, b[r].send, b[r].recv, count, wire_dt, plan, kOrderRing, false);
+  epoch += g.epochs;
+  ++launches;
+  last_variant = kVarTwoShot;
+  cudaError_t rc;
+  const TwoShotArgs* a = stage(args, st, &rc);
+  return rc != cudaSuccess ? rc : launch_twoshot_cast(wire_dt, a, shape(g), st);
+}
+
 cudaError_t Engine::reducescatter(const RankBufs* b, size_t per, int dt, const OpPlan& plan,
                                   cudaStream_t st) {
+  const size_t block = per * dtype_size(dt);
+  // Large inputs go around the neighbour ring (one sender per receiver through the switch, the
+  // same schedule and therefore the same bits); smaller ones are pushed to their owners at once.
+  if (n() >= 2 && block > 0 && ((tune.rs_ring_min && block * n() >= tune.rs_ring_min) || forced_variant == kVarRing)) {
+    const Geometry g = plan_ring(block, n(), views[0].half_bytes, tune, true);
+    HX_CHECK_PLAN(kPlanRingRs, g, block);
+    std::vector<TwoShotArgs> args(views.size());
+    for (size_t r = 0; r < views.size(); ++r)
+      build_reducescatter_ring(&args[r], views[r], epoch, g, b[r].send, b[r].recv, per, dt, plan);
+    epoch += g.epochs;
+    ++launches;
+    cudaError_t rc;
+    const TwoShotArgs* a = stage(args, st, &rc);
+    return rc != cudaSuccess ? rc : launch_ring(dt, a, shape(g), st);
+  }
   const Geometry g = plan_xchg(per * dtype_size(dt), n(), views[0].half_bytes, tune);
   HX_CHECK_PLAN(kPlanXchg, g, per * dtype_size(dt));
   std::vector<XchgArgs> args(views.size());
@@ -156,10 +214,12 @@ cudaError_t Engine::reduce(const RankBufs* b, size_t count, int dt, const OpPlan
   return rc != cudaSuccess ? rc : launch_xchg_copy(a, shape(g), st);
 
 cudaError_t Engine::allgather(const RankBufs* b, size_t block, cudaStream_t st) {
-  HX_COPY_COLLECTIVE(block, build_allgather(&args[r], views[r], epoch, g, b[r].send, b[r].recv, block))
+  const bool mc = tune.nvls && tune.mc_copy && !world() && block >= tune.mc_copy_min;
+  HX_COPY_COLLECTIVE(block, build_allgather(&args[r], views[r], epoch, g, b[r].send, b[r].recv, block, mc))
 }
 cudaError_t Engine::broadcast(const RankBufs* b, size_t bytes, int root, cudaStream_t st) {
-  HX_COPY_COLLECTIVE(bytes, build_broadcast(&args[r], views[r], epoch, g, b[r].send, b[r].recv, bytes, root))
+  const bool mc = tune.nvls && tune.mc_copy && !world() && bytes >= tune.mc_copy_min;
+  HX_COPY_COLLECTIVE(bytes, build_broadcast(&args[r], views[r], epoch, g, b[r].send, b[r].recv, bytes, root, mc))
 }
 cudaError_t Engine::gather(const RankBufs* b, size_t block, int root, cudaStream_t st) {
   HX_COPY_COLLECTIVE(block, build_gather(&args[r], views[r], epoch, g, b[r].send, b[r].recv, block, root))
@@ -192,14 +252,38 @@ cudaError_t Engine::p2p(const RankP2p* ops, cudaStream_t st) {
     }
     for (size_t k = 0; k < sends.size(); ++k) {
       const size_t nbytes = std::min(sends[k].bytes, recvs[k].bytes);
-      if (nbytes && sends[k].buf != recvs[k].buf)
-        if (cudaError_t e = cudaMemcpyAsync(recvs[k].buf, sends[k].buf, nbytes, cudaMemcpyDeviceToDevice, st))
-          return e;
+      if (nbytes && sends[k].buf != recvs[k].buf) {
+        ++launches;
+        if (cudaError_t e = launch_copy(recvs[k].buf, sends[k].buf, nbytes, st)) return e;
+      }
       if (sends[k].bytes > recvs[k].bytes) {
         error = "message truncated: the receive buffer is smaller than the message";
         return cudaErrorInvalidValue;
       }
     }
+  }
+  // Every CTA of a lane waits for the matching CTA of its peer, so all CTAs of a launch must be
+  // resident at once on every rank. The grid is sized for the most lanes a rank of this
+  // communicator can have (a send and a receive lane per peer), from numbers every rank shares:
+  // when lanes x kP2pWorkers CTAs do not fit, one CTA serves several workers of its lane one
+  // after the other (both ends of a lane walk them in the same order, so the pairing holds).
+  const int sharing = world() ? int(nr) : 1;
+  const int most_lanes = std::max(1, std::min(kMaxLanes, 2 * (n() - 1)));
+  auto workers_per_cta = [&](int width) {
+    const int resident = max_resident_ctas(width) / sharing;
+    int wpc = 1;
+    while (wpc < kP2pWorkers && most_lanes * (kP2pWorkers / wpc) > resident) wpc *= 2;
+    return most_lanes * (kP2pWorkers / wpc) <= resident ? wpc : 0;
+  };
+  int threads = world() ? 256 : tune.p2p_threads;
+  int wpc = workers_per_cta(threads);
+  if (threads == 512 && wpc != 1) {  // narrower CTAs: twice as many are resident
+    const int narrow = workers_per_cta(256);
+    if (narrow && (!wpc || narrow < wpc)) threads = 256, wpc = narrow;
+  }
+  if (!wpc) {
+    error = "Send/Recv lanes of " + std::to_string(n()) + " ranks cannot be co-resident on this device";
+    return cudaErrorInvalidValue;
   }
   for (;;) {  // a lane takes kMaxLaneOps operations per launch; more go into another round
     bool any = false;
@@ -209,6 +293,7 @@ cudaError_t Engine::p2p(const RankP2p* ops, cudaStream_t st) {
       P2pArgs& a = args[r];
       std::memset(&a, 0, sizeof a);
       a.w = views[r];
+      a.workers_per_cta = wpc;
       std::vector<P2pOp> rest;
       for (const P2pOp& o : left[r]) {
         int lane = -1;
@@ -242,7 +327,7 @@ cudaError_t Engine::p2p(const RankP2p* ops, cudaStream_t st) {
     cudaError_t rc;
     const P2pArgs* a = stage(args, st, &rc);
     if (rc != cudaSuccess) return rc;
-    rc = launch_p2p(a, LaunchShape{max_lanes * kP2pWorkers, world() ? 256 : tune.p2p_threads, world() ? int(nr) : 0}, st);
+    rc = launch_p2p(a, LaunchShape{max_lanes * (kP2pWorkers / wpc), threads, world() ? int(nr) : 0}, st);
     if (rc != cudaSuccess) return rc;
   }
 }

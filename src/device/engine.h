@@ -45,6 +45,10 @@ class Engine {
 
   cudaError_t allreduce(const RankBufs* b, size_t count, int dt, const OpPlan& plan, int order,
                         cudaStream_t st);
+  // fp32 buffers, `wire_dt` (fp16 / bf16) carried and summed; ring order only (count * 2 bytes
+  // must be at least the size from which the API takes the ring order)
+  cudaError_t allreduce_cast(const RankBufs* b, size_t count, int wire_dt, const OpPlan& plan,
+                             cudaStream_t st);
   cudaError_t reducescatter(const RankBufs* b, size_t per, int dt, const OpPlan& plan,
                             cudaStream_t st);
   cudaError_t reduce(const RankBufs* b, size_t count, int dt, const OpPlan& plan, int root,
@@ -61,6 +65,7 @@ class Engine {
   template <typename Args>
   const Args* stage(const std::vector<Args>& args, cudaStream_t st, cudaError_t* rc);
   LaunchShape shape(const Geometry& g) const;
+  uint64_t ll_era_ = 0;  // upper half of the epoch the line region was last cleared for
   void* dev_args_ = nullptr;
   size_t dev_args_bytes_ = 0;
 };

@@ -20,12 +20,12 @@ extern "C" {
 hxcclResult_t hxcclCommDeviceInfo(hxcclComm_t c, char* kind, size_t kind_len, int* variant,
                                   unsigned long long* launches) {
   if (!c) return hxcclInvalidArgument;
-  const char* k = c->dev ? c->dev->kind() : "none";
+  const char* k = c->device.path ? c->device.path->kind() : "none";
   if (kind && kind_len) {
     std::strncpy(kind, k, kind_len - 1);
     kind[kind_len - 1] = 0;
   }
-  auto* w = dynamic_cast<WindowPath*>(c->dev.get());
+  auto* w = dynamic_cast<WindowPath*>(c->device.path.get());
   if (variant) *variant = w ? w->engine().last_variant : 0;
   if (launches) *launches = w ? w->engine().launches : 0;
   return hxcclSuccess;
@@ -33,7 +33,7 @@ hxcclResult_t hxcclCommDeviceInfo(hxcclComm_t c, char* kind, size_t kind_len, in
 
 hxcclResult_t hxcclCommTune(hxcclComm_t c, int variant, int exact, int max_ctas) {
   if (!c) return hxcclInvalidArgument;
-  auto* w = dynamic_cast<WindowPath*>(c->dev.get());
+  auto* w = dynamic_cast<WindowPath*>(c->device.path.get());
   if (!w) return hxcclInvalidUsage;
   w->engine().forced_variant = variant;
   w->engine().tune.exact = exact != 0;
@@ -43,13 +43,13 @@ hxcclResult_t hxcclCommTune(hxcclComm_t c, int variant, int exact, int max_ctas)
 
 hxcclResult_t hxcclCommTuneKnob(hxcclComm_t c, const char* name, long value) {
   if (!c) return hxcclInvalidArgument;
-  auto* w = dynamic_cast<WindowPath*>(c->dev.get());
+  auto* w = dynamic_cast<WindowPath*>(c->device.path.get());
   if (!w) return hxcclInvalidUsage;
   return set_knob(&w->engine().tune, name, value) ? hxcclSuccess : hxcclInvalidArgument;
 }
 
 int hxcclCommReadTrace(hxcclComm_t c, unsigned long long* out, int max_ctas) {
-  auto* w = c ? dynamic_cast<WindowPath*>(c->dev.get()) : nullptr;
+  auto* w = c ? dynamic_cast<WindowPath*>(c->device.path.get()) : nullptr;
   return w && out && max_ctas > 0 ? w->read_trace(out, max_ctas) : 0;
 }
 
@@ -146,8 +146,9 @@ hxcclResult_t hxcclTestPlan(int kind, size_t amount, int nranks, size_t half_byt
     case kPlanSliced: g = plan_sliced(amount, nranks, half_bytes, t); break;
     case kPlanRoles: g = plan_roles(amount, nranks, half_bytes, t); break;
     case kPlanRing:
+    case kPlanRingRs:
       if (nranks < 2) return hxcclInvalidArgument;
-      g = plan_ring(amount, nranks, half_bytes, t);
+      g = plan_ring(amount, nranks, half_bytes, t, kind == kPlanRingRs);
       break;
     default: return hxcclInvalidArgument;
   }

@@ -69,6 +69,11 @@ bool set_knob(Tuning* t, const char* name, long v) {
   else if (k == "roles_min_ranks") t->roles_min_ranks = int(std::max(2L, v));
   else if (k == "exact") t->exact = v != 0;
   else if (k == "nvls_gather") t->nvls_gather = v != 0;
+  else if (k == "ll_max") t->ll_max = size_t(std::max(0L, v));
+  else if (k == "ll_mc") t->ll_mc = v != 0;
+  else if (k == "rs_ring_min") t->rs_ring_min = size_t(std::max(0L, v));
+  else if (k == "mc_copy") t->mc_copy = v != 0;
+  else if (k == "mc_copy_min") t->mc_copy_min = size_t(std::max(0L, v));
   else return false;
   return true;
 }
@@ -141,7 +146,7 @@ Geometry plan_roles(size_t bytes, int n, size_t half_bytes, const Tuning& t) {
   return g;
 }
 
-Geometry plan_ring(size_t max_block, int n, size_t half_bytes, const Tuning& t) {
+Geometry plan_ring(size_t max_block, int n, size_t half_bytes, const Tuning& t, bool rs) {
   Geometry g;
   const int cap = std::max(1, std::min(t.max_ctas, kMaxCtas));
   g.ctas = int(std::min<size_t>(cap, std::max<size_t>(1, ceil_div(max_block, 16 * 1024))));
@@ -151,7 +156,7 @@ Geometry plan_ring(size_t max_block, int n, size_t half_bytes, const Tuning& t) 
   const size_t want = std::max<size_t>(16, round_up(ceil_div(max_block, g.ctas), 16));
   g.sub_bytes = std::max<size_t>(16, std::min(want, std::min(round_up(t.ring_sub, 16), fit)));
   g.steps = int(std::max<size_t>(1, ceil_div(want, g.sub_bytes)));
-  g.epochs = g.steps * int(hops) + 2;
+  g.epochs = g.steps * int(rs ? n - 1 : hops) + 2;
   g.threads = t.threads ? t.threads : threads_for(g.sub_bytes);
   return g;
 }
@@ -176,9 +181,9 @@ std::string check_geometry(int kind, const Geometry& g, size_t amount, int n, si
     const size_t second = round_down(buf / 2, 256), slice = (roles ? ctas / 3 : ctas) * g.sub_bytes;
     if (ranks * slice > second || second + ranks * slice > buf) return "slices overrun a half of the buffer";
     if (steps * ranks * slice < amount) return "steps do not cover the message";
-  } else if (kind == kPlanRing) {
+  } else if (kind == kPlanRing || kind == kPlanRingRs) {
     const size_t hops = size_t(2 * n - 2);
-    if (n < 2 || g.epochs != g.steps * int(hops) + 2) return "ring shape";
+    if (n < 2 || g.epochs != g.steps * (kind == kPlanRingRs ? n - 1 : int(hops)) + 2) return "ring shape";
     if (hops * ctas * g.sub_bytes > 2 * half_bytes) return "ring slots overrun the staging area";
     if (steps * ctas * g.sub_bytes < amount) return "rounds do not cover a block";
   } else {
@@ -204,10 +209,13 @@ int choose_variant(size_t bytes, int dt, const OpPlan& plan, int n, const Tuning
                        nvls_mode(dt, plan.base) != kNvNone && (is_integer(dt) || !t.exact);
   if (forced == kVarNvls && nvls_ok) return kVarNvls;
   if (forced == kVarOneShot || forced == kVarTwoShot) return forced;
+  const bool ll_ok = bytes > 0 && bytes <= ll_max_payload(n) && n >= 2;
+  if (forced == kVarLL && ll_ok) return kVarLL;
   if (forced == kVarRing && n >= 2 && bytes > 0) return kVarRing;
   // with two ranks the multicast reduction measured slower than two-shot at every size
   if (nvls_ok && bytes >= t.nvls_min && n > 2) return kVarNvls;
   if (t.ring_min && bytes >= t.ring_min && n >= 2 && n <= t.ring_max_ranks) return kVarRing;
+  if (ll_ok && bytes <= t.ll_max && forced == kVarAuto) return kVarLL;
   return bytes <= t.oneshot_max ? kVarOneShot : kVarTwoShot;
 }
 
@@ -228,6 +236,20 @@ void build_allreduce_oneshot(XchgArgs* a, const WinView& w, uint64_t epoch, cons
   a->fold.ring = order == kOrderRing;
   a->fold.ring_count = count;
   a->push_scaled = plan.premul;
+}
+
+void build_allreduce_ll(LLArgs* a, const WinView& w, uint64_t epoch, const void* send, void* recv,
+                        size_t count, int dt, const OpPlan& plan, int order, bool use_mc) {
+  std::memset(a, 0, sizeof *a);
+  a->w = w;
+  a->epoch = epoch;
+  a->send = static_cast<const char*>(send);
+  a->recv = static_cast<char*>(recv);
+  a->bytes = count * dtype_size(dt);
+  a->fold = make_fold(plan, order == kOrderRing ? kFoldLinear : kFoldDoubling);
+  a->fold.ring = order == kOrderRing;
+  a->fold.ring_count = count;
+  a->use_mc = use_mc && w.mc != nullptr;
 }
 
 void build_allreduce_twoshot(TwoShotArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
@@ -263,6 +285,22 @@ void build_allreduce_nvls(NvlsArgs* a, const WinView& w, uint64_t epoch, const G
   a->postdiv = plan.postdiv ? plan.divisor : 0;
   std::memcpy(&a->scalar_bits, plan.scalar, 8);
   a->scalar_ptr = plan.scalar_dev;
+}
+
+void build_reducescatter_ring(TwoShotArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                              const void* send, void* recv, size_t per, int dt, const OpPlan& plan) {
+  std::memset(a, 0, sizeof *a);
+  a->w = w;
+  a->epoch0 = epoch;
+  a->steps = g.steps;
+  a->sub_bytes = g.sub_bytes;
+  a->send = static_cast<const char*>(send);
+  a->recv = static_cast<char*>(recv);
+  a->bytes = per * dtype_size(dt) * size_t(w.n);
+  a->fold = make_fold(plan, kFoldLinear);
+  a->fold.ring = 1;
+  a->fold.ring_count = per * size_t(w.n);  // n equal blocks
+  a->ring_rs = 1;
 }
 
 void build_reducescatter(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
@@ -306,8 +344,20 @@ void build_reduce(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry&
   a->fold_bytes = bytes;
 }
 
+namespace {
+// One multimem.st reaches every rank's window. It needs the multicast alias, whole 16-byte
+// vectors and a 16-byte aligned source; a rank may decide this for itself, because the bytes
+// land in the same slots either way.
+void offer_multicast(XchgArgs* a, const WinView& w, const void* src, size_t bytes, bool wanted) {
+  if (wanted && w.mc && w.n > 1 && bytes >= 16 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+    a->mc_src = static_cast<const char*>(src);
+    a->mc_bytes = bytes;
+  }
+}
+}  // namespace
+
 void build_allgather(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
-                     const void* send, void* recv, size_t block) {
+                     const void* send, void* recv, size_t block, bool multicast) {
   clear(a, w, epoch, g);
   for (int j = 0; j < w.n; ++j) {
     a->send_ptr[j] = static_cast<const char*>(send);
@@ -315,10 +365,11 @@ void build_allgather(XchgArgs* a, const WinView& w, uint64_t epoch, const Geomet
     a->recv_ptr[j] = static_cast<char*>(recv) + size_t(j) * block;
     a->recv_bytes[j] = block;
   }
+  offer_multicast(a, w, send, block, multicast);
 }
 
 void build_broadcast(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
-                     const void* send, void* recv, size_t bytes, int root) {
+                     const void* send, void* recv, size_t bytes, int root, bool multicast) {
   clear(a, w, epoch, g);
   for (int j = 0; j < w.n; ++j) {
     a->send_ptr[j] = static_cast<const char*>(send);
@@ -326,6 +377,7 @@ void build_broadcast(XchgArgs* a, const WinView& w, uint64_t epoch, const Geomet
     a->recv_ptr[j] = static_cast<char*>(recv);
     a->recv_bytes[j] = j == root ? bytes : 0;  // on the root this is the send -> recv copy
   }
+  if (w.rank == root) offer_multicast(a, w, send, bytes, multicast);
 }
 
 void build_gather(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,

@@ -23,7 +23,7 @@ struct Geometry {
 
 // AllReduce transport variants
 enum : int { kVarAuto = 0, kVarOneShot = 1, kVarTwoShot = 2, kVarNvls = 3, kVarTwoShotRoles = 4, kVarNvlsRoles = 5,
-       kVarRing = 6 };
+       kVarRing = 6, kVarLL = 7 };
 
 struct Tuning {
   int max_ctas = 128;         // upper bound of any collective grid
@@ -41,14 +41,19 @@ struct Tuning {
   size_t roles_min = 96u << 20;       // AllReduce: from here the three-role pipeline
   size_t roles_sub = 64 * 1024;       // its per-lane share of a slice per step
   size_t ring_min = 128u << 20;       // AllReduce: from here the neighbour ring (0 = only when forced)
-  int ring_max_ranks = 2;             // ... on communicators of at most this many ranks
+  int ring_max_ranks = kMaxRanks;     // ... on communicators of at most this many ranks
   size_t ring_sub = 512 * 1024;       // largest per-CTA share of one ring hop
   int p2p_threads = 512;              // CTA width of the Send/Recv lanes
+  size_t ll_max = 16 * 1024;          // AllReduce: up to here the flag-in-data kernel (0 = never)
+  bool ll_mc = true;                  // ... its lines go out through the multicast alias when there is one
+  size_t rs_ring_min = 256u << 20;    // ReduceScatter: neighbour ring from this many input bytes (0 = never)
+  bool mc_copy = true;                // AllGather / Broadcast push through the multicast alias
+  size_t mc_copy_min = 0;             // ... from this many bytes per block
 };
 
 // Sets one tuning knob by name ("max_ctas", "oneshot_max", "nvls_min", "single_sub_max",
 // "sub_max", "min_steps", "threads", "roles_min", "roles_sub", "ring_min", "ring_max_ranks", "ring_sub", "p2p_threads",
-// "exact", "nvls_gather");
+// "exact", "nvls_gather", "mc_copy", "mc_copy_min", "rs_ring_min", "ll_max", "ll_mc");
 // false for an unknown name.
 bool set_knob(Tuning* t, const char* name, long value);
 // Applies a file of knob settings (HXCCL_TUNE_FILE): one "name value" or "name=value" per line,
@@ -63,14 +68,15 @@ Geometry plan_sliced(size_t bytes, int n, size_t half_bytes, const Tuning& t);
 Geometry plan_roles(size_t bytes, int n, size_t half_bytes, const Tuning& t);
 
 // neighbour ring over blocks of at most `max_block` bytes: steps = rounds,
-// epochs = rounds * (2n - 2) + 2
-Geometry plan_ring(size_t max_block, int n, size_t half_bytes, const Tuning& t);
+// epochs = rounds * (2n - 2) + 2; the ReduceScatter form (`rs`) raises n - 1 flags per round:
+// epochs = rounds * (n - 1) + 2 (it uses the same 2n - 2 slots, as two alternating sets)
+Geometry plan_ring(size_t max_block, int n, size_t half_bytes, const Tuning& t, bool rs = false);
 
 // Checks a launch shape against the window layout the kernels assume: every slot a CTA writes
 // lies inside its staging buffer, the steps cover the whole message, the grid fits the flag rows.
 // Returns an empty string when all holds, else what does not. `amount` is what the matching
 // plan_* function was given. Run before every launch (host arithmetic only).
-enum : int { kPlanXchg = 0, kPlanSliced = 1, kPlanRoles = 2, kPlanRing = 3 };
+enum : int { kPlanXchg = 0, kPlanSliced = 1, kPlanRoles = 2, kPlanRing = 3, kPlanRingRs = 4 };
 std::string check_geometry(int kind, const Geometry& g, size_t amount, int n, size_t half_bytes);
 
 FoldSpec make_fold(const OpPlan& plan, int kind);
@@ -81,20 +87,25 @@ int choose_variant(size_t bytes, int dt, const OpPlan& plan, int n, const Tuning
 void build_allreduce_oneshot(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
                              const void* send, void* recv, size_t count, int dt,
                              const OpPlan& plan, int order);
+void build_allreduce_ll(LLArgs* a, const WinView& w, uint64_t epoch, const void* send, void* recv,
+                        size_t count, int dt, const OpPlan& plan, int order, bool use_mc);
 void build_allreduce_twoshot(TwoShotArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
                              const void* send, void* recv, size_t count, int dt,
                              const OpPlan& plan, int order, bool use_mc);
 void build_allreduce_nvls(NvlsArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
                           const void* send, void* recv, size_t count, int dt, const OpPlan& plan);
+void build_reducescatter_ring(TwoShotArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
+                              const void* send, void* recv, size_t per, int dt, const OpPlan& plan);
 void build_reducescatter(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
                          const void* send, void* recv, size_t per, int dt, const OpPlan& plan);
 void build_reduce(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
                   const void* send, void* recv, size_t count, int dt, const OpPlan& plan,
                   int root);
+// `multicast`: push through the multicast alias where this rank's buffer allows it
 void build_allgather(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
-                     const void* send, void* recv, size_t block);
+                     const void* send, void* recv, size_t block, bool multicast);
 void build_broadcast(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
-                     const void* send, void* recv, size_t bytes, int root);
+                     const void* send, void* recv, size_t bytes, int root, bool multicast);
 void build_gather(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
                   const void* send, void* recv, size_t block, int root);
 void build_scatter(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,

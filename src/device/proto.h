@@ -52,7 +52,13 @@ constexpr size_t kOffFlagsA = 64 * 1024;
 constexpr size_t kOffFlagsB = kOffFlagsA + size_t(kMaxCtas) * kMaxRanks * 8;
 constexpr size_t kOffFlagsC = kOffFlagsB + size_t(kMaxCtas) * kMaxRanks * 8;
 constexpr size_t kHeaderBytes = 1u << 20;
-static_assert(kOffFlagsC + size_t(kMaxCtas) * kMaxRanks * 8 <= kHeaderBytes, "flag pages must fit the header");
+// Lines of the small-message AllReduce (kernels/ll_body.cuh): two halves by epoch parity, each
+// with one slot per source rank. A line is 16 bytes and carries 8 bytes of payload.
+constexpr size_t kOffLL = 256 * 1024;
+constexpr size_t kLLBytes = kHeaderBytes - kOffLL;
+static_assert(kOffFlagsC + size_t(kMaxCtas) * kMaxRanks * 8 <= kOffLL, "flag pages must end before the line region");
+inline constexpr size_t ll_slot_bytes(int n) { return kLLBytes / 2 / size_t(n) / 256 * 256; }
+inline constexpr size_t ll_max_payload(int n) { return ll_slot_bytes(n) / 2; }
 constexpr size_t kOffP2pSlots = kHeaderBytes;
 
 inline constexpr size_t p2p_region_bytes(int n) {
@@ -124,6 +130,12 @@ struct XchgArgs {
   size_t fold_elem0;     // index of dst[0] in the full vector (ring-block lookup)
   FoldSpec fold;
   int push_scaled;       // pushes carry input * scalar (fold.premul) instead of raw bytes
+  // Multicast push (AllGather, Broadcast on a window bound to an NVSwitch multicast object):
+  // bytes [0, mc_bytes) at mc_src go to EVERY rank's slot of this rank with one multimem.st per
+  // 16 bytes instead of one store per peer, so the sender's link carries the block once.
+  // 0 = push peer by peer (send_ptr / send_bytes above, which are filled either way).
+  const char* mc_src;
+  size_t mc_bytes;
 };
 
 // ---- two-shot AllReduce: reduce-scatter into owners, owners fold, all-gather the results
@@ -137,6 +149,20 @@ struct TwoShotArgs {
   size_t bytes;        // whole message
   FoldSpec fold;
   int use_mc;          // all-gather phase through the multicast alias
+  // neighbour ring only: 1 = ReduceScatter (the reduce-scatter half alone, every block's chain
+  // shifted by one rank so that block r ends on rank r; `send` holds n blocks, `recv` one)
+  int ring_rs;
+};
+
+// ---- small-message AllReduce with the flag inside the data (kernels/ll_body.cuh)
+struct LLArgs {
+  WinView w;
+  unsigned long long epoch;
+  const char* send;
+  char* recv;
+  size_t bytes;   // at most ll_max_payload(n)
+  FoldSpec fold;
+  int use_mc;     // lines go out through the multicast alias
 };
 
 // ---- NVLS AllReduce: copy in, multimem.ld_reduce own slice, multimem.st, copy out
@@ -172,7 +198,8 @@ struct P2pLane {
 struct P2pArgs {
   WinView w;
   int nlanes;
-  P2pLane lanes[kMaxLanes];  // CTA (lane, worker) = blockIdx.x / kP2pWorkers, % kP2pWorkers
+  int workers_per_cta;       // a power of two up to kP2pWorkers: workers one CTA serves in turn
+  P2pLane lanes[kMaxLanes];  // CTA (lane, group) = blockIdx.x / G, % G with G = kP2pWorkers / workers_per_cta
 };
 
 }  // namespace hx

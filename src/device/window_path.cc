@@ -457,12 +457,23 @@ hxcclResult_t WindowPath::allreduce(const void* send, void* recv, size_t count, 
   // HXCCL_DEBUG=2 (or more): one line per AllReduce on rank 0 with what the tuner chose
   static const int level = [] { const char* v = std::getenv("HXCCL_DEBUG"); return v ? std::atoi(v) : 0; }();
   if (level >= 2 && rank_ == 0) {
-    static const char* const names[] = {"auto", "one-shot", "two-shot", "nvls", "two-shot roles", "nvls roles", "ring"};
+    static const char* const names[] = {"auto", "one-shot", "two-shot", "nvls", "two-shot roles", "nvls roles", "ring", "lines"};
     const int v = eng_.last_variant;
     std::fprintf(stderr, "hxccl: AllReduce %zu bytes, dtype %d, order %s -> %s\n", count * dtype_size(dt), dt,
-                 order == kOrderRing ? "ring" : "doubling", v >= 0 && v <= 6 ? names[v] : "?");
+                 order == kOrderRing ? "ring" : "doubling", v >= 0 && v <= 7 ? names[v] : "?");
   }
   return done(e, "AllReduce launch");
+}
+
+hxcclResult_t WindowPath::allreduce_cast(const void* send, void* recv, size_t count, int wire_dt,
+                                         const OpPlan& plan, void* stream) {
+  if (count == 0) return hxcclSuccess;
+  if (n_ < 2 || count * dtype_size(wire_dt) < kDoublingMaxBytes) {
+    error = "the fused cast AllReduce serves two or more ranks and messages in ring order only";
+    return hxcclInvalidUsage;
+  }
+  RankBufs b{send, recv};
+  return done(eng_.allreduce_cast(&b, count, wire_dt, plan, enter(stream)), "AllReduceCast launch");
 }
 hxcclResult_t WindowPath::allgather(const void* send, void* recv, size_t block, void* stream) {
   if (block == 0) return hxcclSuccess;

@@ -26,6 +26,8 @@ class WindowPath : public DevicePath {
   const char* kind() const override { return nvls_ ? "window+nvls" : "window"; }
   hxcclResult_t allreduce(const void* send, void* recv, size_t count, int dt, const OpPlan& plan,
                           int order, void* stream) override;
+  hxcclResult_t allreduce_cast(const void* send, void* recv, size_t count, int wire_dt, const OpPlan& plan,
+                               void* stream) override;
   hxcclResult_t allgather(const void* send, void* recv, size_t block, void* stream) override;
   hxcclResult_t reducescatter(const void* send, void* recv, size_t per, int dt,
                               const OpPlan& plan, void* stream) override;

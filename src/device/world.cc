@@ -147,6 +147,18 @@ hxcclResult_t hxcclWorldAllReduce(hxcclWorld_t w, const void* const* send, void*
   return rc_of(w->eng.allreduce(b.data(), count, dt, plan, order, static_cast<cudaStream_t>(stream)));
 }
 
+hxcclResult_t hxcclWorldAllReduceCast(hxcclWorld_t w, const void* const* send, void* const* recv,
+                                      size_t count, hxcclDataType_t wire_dt, hxcclRedOp_t op,
+                                      hxcclStream_t stream) {
+  OpPlan plan;
+  if (!w || (wire_dt != hxcclFloat16 && wire_dt != hxcclBfloat16) || !make_plan(w->n, wire_dt, op, nullptr, &plan))
+    return hxcclInvalidArgument;
+  if (count == 0) return hxcclSuccess;
+  if (w->n < 2) return hxcclInvalidUsage;
+  auto b = bufs(w, send, recv);
+  return rc_of(w->eng.allreduce_cast(b.data(), count, wire_dt, plan, static_cast<cudaStream_t>(stream)));
+}
+
 hxcclResult_t hxcclWorldReduceScatter(hxcclWorld_t w, const void* const* send, void* const* recv,
                                       size_t recvcount, hxcclDataType_t dt, hxcclRedOp_t op,
                                       const void* scalar, hxcclStream_t stream) {

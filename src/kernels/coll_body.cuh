@@ -44,15 +44,19 @@ __device__ void xchg_body(const XchgArgs& a, int cta, int ncta, FoldShared& sh) 
   auto push = [&](int step) {
     const size_t lo = (size_t(step) * ncta + cta) * a.sub_bytes;  // offset inside a pair's block
     const size_t buf = stg.at(step);
+    const size_t slot_off = buf + size_t(me) * a.slot_stride + in_slot;
+    size_t by_mc = 0;  // bytes of this step's piece that went out through the switch's multicast
+    if (!kFold && a.mc_bytes > lo)
+      by_mc = cta_copy_multicast(w.mc + slot_off, a.mc_src + lo, min_sz(a.sub_bytes, a.mc_bytes - lo));
     for (int jj = 1; jj < n; ++jj) {
       const int j = (me + jj) % n;
-      if (a.send_bytes[j] <= lo) continue;
-      const size_t len = min_sz(a.sub_bytes, a.send_bytes[j] - lo);
-      char* to = w.win[j] + buf + size_t(me) * a.slot_stride + in_slot;
+      if (a.send_bytes[j] <= lo + by_mc) continue;
+      const size_t len = min_sz(a.sub_bytes, a.send_bytes[j] - lo) - by_mc;
+      char* to = w.win[j] + slot_off + by_mc;
       if (kFold && a.push_scaled)
         cta_scale_copy<T>(to, a.send_ptr[j] + lo, len, scalar);
       else
-        cta_copy(to, a.send_ptr[j] + lo, len);
+        cta_copy(to, a.send_ptr[j] + lo + by_mc, len);
     }
     __syncthreads();
     tm.lap(kTrIn);
@@ -118,7 +122,15 @@ __device__ void xchg_body(const XchgArgs& a, int cta, int ncta, FoldShared& sh) 
 // every peer's window (phase B), and everyone copies the other slices out of its window.
 // A staging buffer holds the phase A slots in its first half and the phase B slots in its
 // second half.
-template <typename T>
+//
+// kCast: the caller's buffers hold fp32 while T (fp16 or bf16) travels and is summed: a gradient
+// bucket reduced in half the bytes without separate cast passes. a.bytes, the slices and all
+// offsets count bytes of T; the fp32 buffers are indexed by element. The push rounds to T and
+// pre-scales, and stages this rank's own contribution in its own window too, so that the fold
+// reads n sources of T as always; the fold leaves the own slice's result in the window, and the
+// gather widens every slice, the own one included, into the fp32 output. Bit for bit this is
+// "cast to T, AllReduce in T, cast back".
+template <typename T, bool kCast = false>
 __device__ void twoshot_body(const TwoShotArgs& a, int cta, int ncta, FoldShared& sh) {
   const WinView& w = a.w;
   const int me = w.rank, n = w.n;
@@ -141,13 +153,16 @@ __device__ void twoshot_body(const TwoShotArgs& a, int cta, int ncta, FoldShared
   // fold instead of stalling the CTA twice per step.
   auto push = [&](int step, bool signal) {  // phase A: my contribution to every other owner's slice
     const size_t step0 = size_t(step) * n * slice, buf = stg.at(step);
-    for (int jj = 1; jj < n; ++jj) {
+    for (int jj = kCast ? 0 : 1; jj < n; ++jj) {
       const int j = (me + jj) % n;
       const size_t lo = step0 + size_t(j) * slice + in_slice;
       if (lo >= a.bytes) continue;
       const size_t len = min_sz(a.sub_bytes, a.bytes - lo);
       char* to = w.win[j] + buf + size_t(me) * slice + in_slice;
-      if (a.fold.premul)
+      if constexpr (kCast)
+        cta_narrow_scale_copy<T>(to, reinterpret_cast<const float*>(a.send) + lo / sizeof(T), len, scalar,
+                                 a.fold.premul != 0);
+      else if (a.fold.premul)
         cta_scale_copy<T>(to, a.send + lo, len, scalar);
       else
         cta_copy(to, a.send + lo, len);
@@ -165,16 +180,24 @@ __device__ void twoshot_body(const TwoShotArgs& a, int cta, int ncta, FoldShared
     __syncthreads();
     if (threadIdx.x < unsigned(n)) {
       const int i = threadIdx.x;
-      sh.src[i] = i == me ? a.send + lo : mine + buf + size_t(i) * slice + in_slice;
+      sh.src[i] = (i == me && !kCast) ? a.send + lo : mine + buf + size_t(i) * slice + in_slice;
       const int q = i < me ? i : i - 1;  // compact list of the other ranks
       if (i != me) sh.remote[q] = w.win[i] + buf + ag_base + size_t(me) * slice + in_slice;
     }
     if (threadIdx.x == 0)
       sh.mc_dst = a.use_mc ? w.mc + buf + ag_base + size_t(me) * slice + in_slice : nullptr;
     __syncthreads();
-    if (lo < a.bytes)
-      cta_fold<T>(a.recv + lo, sh, n - 1, min_sz(a.sub_bytes, a.bytes - lo), lo / sizeof(T), a.fold,
-                  me, n, scalar);
+    if (lo < a.bytes) {
+      if (kCast) {  // every source is staged and already scaled; the result stays in the window
+        FoldSpec plain = a.fold;
+        plain.premul = 0;
+        cta_fold<T>(mine + buf + ag_base + size_t(me) * slice + in_slice, sh, n - 1,
+                    min_sz(a.sub_bytes, a.bytes - lo), lo / sizeof(T), plain, me, n, scalar);
+      } else {
+        cta_fold<T>(a.recv + lo, sh, n - 1, min_sz(a.sub_bytes, a.bytes - lo), lo / sizeof(T), a.fold,
+                    me, n, scalar);
+      }
+    }
     __syncthreads();
     tm.lap(kTrMid);
     signal_all(w, kOffFlagsB, cta, e_step0 + step);
@@ -183,12 +206,15 @@ __device__ void twoshot_body(const TwoShotArgs& a, int cta, int ncta, FoldShared
   };
   auto gather = [&](int step) {  // phase B: the other owners' results
     const size_t step0 = size_t(step) * n * slice, buf = stg.at(step);
-    for (int ii = 1; ii < n; ++ii) {
+    for (int ii = kCast ? 0 : 1; ii < n; ++ii) {
       const int i = (me + ii) % n;
       const size_t lo = step0 + size_t(i) * slice + in_slice;
       if (lo >= a.bytes) continue;
-      cta_copy(a.recv + lo, mine + buf + ag_base + size_t(i) * slice + in_slice,
-               min_sz(a.sub_bytes, a.bytes - lo));
+      const char* from = mine + buf + ag_base + size_t(i) * slice + in_slice;
+      if constexpr (kCast)
+        cta_widen_copy<T>(reinterpret_cast<float*>(a.recv) + lo / sizeof(T), from, min_sz(a.sub_bytes, a.bytes - lo));
+      else
+        cta_copy(a.recv + lo, from, min_sz(a.sub_bytes, a.bytes - lo));
     }
     __syncthreads();
     tm.lap(kTrOut);

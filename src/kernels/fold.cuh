@@ -160,16 +160,8 @@ __device__ inline void fold_linear_vectors(char* dst, const FoldShared& sh, int 
         int idx = first[u];
 #pragma unroll
         for (int k = 0; k < N; ++k) {
-          if (f.premul && idx == rank) {
-#pragma unroll
-            for (int l = 0; l < V; ++l) in[u][k].e[l] = scale(in[u][k].e[l], scalar);
-          }
-          if (k == 0) {
-            out = in[u][0];
-          } else {
-#pragma unroll
-            for (int l = 0; l < V; ++l) out.e[l] = apply(in[u][k].e[l], out.e[l], f.op);
-          }
+          if (f.premul && idx == rank) in[u][k] = apply_lanes(in[u][k], splat(scalar), kProd);
+          out = k == 0 ? in[u][0] : apply_lanes(in[u][k], out, f.op);
           idx += f.dir;
           idx = idx >= N ? idx - N : (idx < 0 ? idx + N : idx);
         }
@@ -279,13 +271,61 @@ __device__ inline void cta_scale_copy(char* dst, const char* src, size_t nbytes,
   for (size_t v = t; v < nvec; v += nt) {
     Vec16<T> x;
     x.raw = ld16(src + (v << 4));
-#pragma unroll
-    for (int l = 0; l < V; ++l) x.e[l] = scale(x.e[l], scalar);
-    st16(dst + (v << 4), x.raw);
+    st16(dst + (v << 4), apply_lanes(x, splat(scalar), kProd).raw);
   }
   const size_t first = (nvec << 4) / sizeof(T), total = nbytes / sizeof(T);
   for (size_t e = first + t; e < total; e += nt)
     reinterpret_cast<T*>(dst)[e] = scale(reinterpret_cast<const T*>(src)[e], scalar);
+}
+
+// ---- fp32 buffers with a narrow type on the wire (gradient buckets) --------------------------------
+// dst[i] = scale(narrow(src[i]), scalar): rounds fp32 values to T (nearest even, the library's
+// overflow and NaN rules) and applies the pre-scale in T's rule, as a cast followed by the
+// ordinary pre-scaled push would. `nbytes` counts bytes of T.
+template <typename T>
+__device__ inline void cta_narrow_scale_copy(char* dst, const float* src, size_t nbytes, T scalar, bool premul) {
+  constexpr int V = 16 / sizeof(T);
+  const int t = threadIdx.x, nt = blockDim.x;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15u) == 0;
+  const size_t nvec = aligned ? nbytes >> 4 : 0;
+  for (size_t v = t; v < nvec; v += nt) {
+    Vec16<T> x;
+    const float4* in = reinterpret_cast<const float4*>(src + v * V);
+#pragma unroll
+    for (int q = 0; q < V / 4; ++q) {
+      const float4 f = in[q];
+      from_f32(f.x, &x.e[4 * q]);
+      from_f32(f.y, &x.e[4 * q + 1]);
+      from_f32(f.z, &x.e[4 * q + 2]);
+      from_f32(f.w, &x.e[4 * q + 3]);
+    }
+    if (premul) x = apply_lanes(x, splat(scalar), kProd);
+    st16(dst + (v << 4), x.raw);
+  }
+  const size_t first = (nvec << 4) / sizeof(T), total = nbytes / sizeof(T);
+  for (size_t e = first + t; e < total; e += nt) {
+    T x;
+    from_f32(src[e], &x);
+    reinterpret_cast<T*>(dst)[e] = premul ? scale(x, scalar) : x;
+  }
+}
+// dst[i] = float(src[i]) (exact). `nbytes` counts bytes of T.
+template <typename T>
+__device__ inline void cta_widen_copy(float* dst, const char* src, size_t nbytes) {
+  constexpr int V = 16 / sizeof(T);
+  const int t = threadIdx.x, nt = blockDim.x;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15u) == 0;
+  const size_t nvec = aligned ? nbytes >> 4 : 0;
+  for (size_t v = t; v < nvec; v += nt) {
+    Vec16<T> x;
+    x.raw = ld16(src + (v << 4));
+    float4* out = reinterpret_cast<float4*>(dst + v * V);
+#pragma unroll
+    for (int q = 0; q < V / 4; ++q)
+      out[q] = make_float4(to_f32(x.e[4 * q]), to_f32(x.e[4 * q + 1]), to_f32(x.e[4 * q + 2]), to_f32(x.e[4 * q + 3]));
+  }
+  const size_t first = (nvec << 4) / sizeof(T), total = nbytes / sizeof(T);
+  for (size_t e = first + t; e < total; e += nt) dst[e] = to_f32(reinterpret_cast<const T*>(src)[e]);
 }
 
 }  // namespace hx

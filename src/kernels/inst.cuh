@@ -4,6 +4,7 @@
 #include "kernels/coll_body.cuh"
 #include "kernels/roles_body.cuh"
 #include "kernels/ring_body.cuh"
+#include "kernels/ll_body.cuh"
 #include "kernels/launch.h"
 
 namespace hx {
@@ -29,6 +30,18 @@ __global__ void __launch_bounds__(512) k_twoshot_world(const TwoShotArgs* a) {
   twoshot_body<T>(a[blockIdx.y], blockIdx.x, gridDim.x, sh);
 }
 
+// fp32 buffers, T on the wire (instantiated for fp16 and bf16 only)
+template <typename T>
+__global__ void __launch_bounds__(512) k_twoshot_cast(const __grid_constant__ TwoShotArgs a) {
+  __shared__ FoldShared sh;
+  twoshot_body<T, true>(a, blockIdx.x, gridDim.x, sh);
+}
+template <typename T>
+__global__ void __launch_bounds__(512) k_twoshot_cast_world(const TwoShotArgs* a) {
+  __shared__ FoldShared sh;
+  twoshot_body<T, true>(a[blockIdx.y], blockIdx.x, gridDim.x, sh);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(512) k_twoshot_roles(const __grid_constant__ TwoShotArgs a) {
   __shared__ FoldShared sh;
@@ -49,6 +62,17 @@ template <typename T>
 __global__ void __launch_bounds__(512) k_ring_world(const TwoShotArgs* a) {
   __shared__ FoldShared sh;
   ring_body<T>(a[blockIdx.y], blockIdx.x, gridDim.x, sh);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) k_ll(const __grid_constant__ LLArgs a) {
+  __shared__ FoldShared sh;
+  ll_body<T>(a, blockIdx.x, gridDim.x, sh);
+}
+template <typename T>
+__global__ void __launch_bounds__(256) k_ll_world(const LLArgs* a) {
+  __shared__ FoldShared sh;
+  ll_body<T>(a[blockIdx.y], blockIdx.x, gridDim.x, sh);
 }
 
 template <typename Args>
@@ -73,6 +97,14 @@ cudaError_t launch_twoshot_t(const TwoShotArgs* args, LaunchShape s, cudaStream_
 }
 
 template <typename T>
+cudaError_t launch_twoshot_cast_t(const TwoShotArgs* args, LaunchShape s, cudaStream_t st) {
+  if (s.world)
+    return launch_world(reinterpret_cast<const void*>(&k_twoshot_cast_world<T>), args, s, st);
+  k_twoshot_cast<T><<<s.ctas, s.threads, 0, st>>>(*args);
+  return cudaGetLastError();
+}
+
+template <typename T>
 cudaError_t launch_twoshot_roles_t(const TwoShotArgs* args, LaunchShape s, cudaStream_t st) {
   if (s.world)
     return launch_world(reinterpret_cast<const void*>(&k_twoshot_roles_world<T>), args, s, st);
@@ -87,6 +119,13 @@ cudaError_t launch_ring_t(const TwoShotArgs* args, LaunchShape s, cudaStream_t s
   return cudaGetLastError();
 }
 
+template <typename T>
+cudaError_t launch_ll_t(const LLArgs* args, LaunchShape s, cudaStream_t st) {
+  if (s.world) return launch_world(reinterpret_cast<const void*>(&k_ll_world<T>), args, s, st);
+  k_ll<T><<<s.ctas, s.threads, 0, st>>>(*args);
+  return cudaGetLastError();
+}
+
 // ---- standalone elementwise kernels --------------------------------------------------------
 template <typename T>
 __global__ void k_reduce(T* dst, const T* src, size_t n, int op) {
@@ -98,9 +137,7 @@ __global__ void k_reduce(T* dst, const T* src, size_t n, int op) {
     Vec16<T> a, b;
     a.raw = ld16(reinterpret_cast<const char*>(dst) + (v << 4));
     b.raw = ld16(reinterpret_cast<const char*>(src) + (v << 4));
-#pragma unroll
-    for (int l = 0; l < V; ++l) a.e[l] = apply(a.e[l], b.e[l], op);
-    st16(reinterpret_cast<char*>(dst) + (v << 4), a.raw);
+    st16(reinterpret_cast<char*>(dst) + (v << 4), apply_lanes(a, b, op).raw);
   }
   for (size_t e = nvec * V + tid; e < n; e += nth) dst[e] = apply(dst[e], src[e], op);
 }
@@ -115,9 +152,7 @@ __global__ void k_scale(T* dst, const T* src, size_t n, unsigned long long scala
   for (size_t v = tid; v < nvec; v += nth) {
     Vec16<T> a;
     a.raw = ld16(reinterpret_cast<const char*>(src) + (v << 4));
-#pragma unroll
-    for (int l = 0; l < V; ++l) a.e[l] = scale(a.e[l], k);
-    st16(reinterpret_cast<char*>(dst) + (v << 4), a.raw);
+    st16(reinterpret_cast<char*>(dst) + (v << 4), apply_lanes(a, splat(k), kProd).raw);
   }
   for (size_t e = nvec * V + tid; e < n; e += nth) dst[e] = scale(src[e], k);
 }
@@ -157,6 +192,7 @@ cudaError_t launch_divide_t(void* buf, size_t count, int divisor, cudaStream_t s
   template cudaError_t launch_twoshot_t<T>(const TwoShotArgs*, LaunchShape, cudaStream_t);   \
   template cudaError_t launch_twoshot_roles_t<T>(const TwoShotArgs*, LaunchShape, cudaStream_t); \
   template cudaError_t launch_ring_t<T>(const TwoShotArgs*, LaunchShape, cudaStream_t);      \
+  template cudaError_t launch_ll_t<T>(const LLArgs*, LaunchShape, cudaStream_t);             \
   template cudaError_t launch_reduce_t<T>(void*, const void*, size_t, int, cudaStream_t);    \
   template cudaError_t launch_scale_t<T>(void*, const void*, size_t, unsigned long long,     \
                                          cudaStream_t);                                      \

@@ -1,4 +1,5 @@
 #include "kernels/inst.cuh"
 namespace hx {
 HX_INSTANTIATE_TYPE(hx::f16)
+template cudaError_t launch_twoshot_cast_t<hx::f16>(const TwoShotArgs*, LaunchShape, cudaStream_t);
 }

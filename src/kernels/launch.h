@@ -19,10 +19,14 @@ struct LaunchShape {
 cudaError_t launch_xchg_copy(const XchgArgs* args, LaunchShape s, cudaStream_t st);
 cudaError_t launch_xchg_fold(int dt, const XchgArgs* args, LaunchShape s, cudaStream_t st);
 cudaError_t launch_twoshot(int dt, const TwoShotArgs* args, LaunchShape s, cudaStream_t st);
+// fp32 buffers with wire_dt (hxcclFloat16 / hxcclBfloat16) on the wire; args as for two-shot, bytes of wire_dt
+cudaError_t launch_twoshot_cast(int wire_dt, const TwoShotArgs* args, LaunchShape s, cudaStream_t st);
 // three-role pipeline for large messages (grid = 3 * lanes)
 cudaError_t launch_twoshot_roles(int dt, const TwoShotArgs* args, LaunchShape s, cudaStream_t st);
 // neighbour ring (reduce-scatter + all-gather around the ring); args->steps = rounds
 cudaError_t launch_ring(int dt, const TwoShotArgs* args, LaunchShape s, cudaStream_t st);
+// small messages: flag inside the data, no hand-shake (threads must be 256)
+cudaError_t launch_ll(int dt, const LLArgs* args, LaunchShape s, cudaStream_t st);
 // production only; roles = three-role pipeline
 cudaError_t launch_nvls(const NvlsArgs* args, LaunchShape s, cudaStream_t st, bool roles = false);
 cudaError_t launch_p2p(const P2pArgs* args, LaunchShape s, cudaStream_t st);

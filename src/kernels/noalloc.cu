@@ -6,6 +6,7 @@
 
 #include <cstdio>
 #include <cstring>
+#include <string>
 
 #include "device/planner.h"
 #include "kernels/launch.h"
@@ -30,9 +31,9 @@ static __device__ __align__(256) unsigned char g_scratch[kScratchBytes];
 
 constexpr int kMaxDevices = 64;
 struct PerDevice {
-  unsigned char* base = nullptr;  // device address of g_scratch on this device
+  unsigned char* base = nullptr;  // device address of g_scratch on this device, as last looked up
   unsigned long long epoch = 2;
-  bool dirty = false;             // the last call failed: flags are in an unknown state
+  bool dirty = false;             // flags are in an unknown state (failed call, or a new context)
 };
 PerDevice g_dev[kMaxDevices];
 char g_error[256] = "";
@@ -69,11 +70,17 @@ extern "C" hxcclResult_t hxcclAllReduceNoAlloc(int nranks, const void* const* se
   if (dev < 0 || dev >= kMaxDevices) return fail(hxcclInvalidArgument, "device ordinal out of range");
   PerDevice& pd = g_dev[dev];
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (!pd.base) {  // set-up, once per device, with that device current
+  {  // The array's device address, with this device current. The first call on a device is
+     // the set-up; later calls repeat the (cheap) look-up instead of trusting a cached pointer,
+     // which a cudaDeviceReset or another context on the same ordinal would leave stale. A
+     // changed address means a fresh array image: start over from cleared flags.
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_scratch);
     if (e != cudaSuccess || !p) return fail(hxcclUnhandledCudaError, "cudaGetSymbolAddress", e);
-    pd.base = static_cast<unsigned char*>(p);
+    if (p != pd.base) {
+      pd.base = static_cast<unsigned char*>(p);
+      pd.dirty = true;
+    }
   }
   if (pd.dirty) {  // start over from zeroed flags
     e = cudaMemsetAsync(pd.base, 0, kScratchBytes, st);
@@ -103,6 +110,10 @@ extern "C" hxcclResult_t hxcclAllReduceNoAlloc(int nranks, const void* const* se
   Tuning tune;
   tune.max_ctas = 16;
   const Geometry g = plan_xchg(bytes, nranks, kHalf, tune);
+  // the host-side bounds check every other launch of this library gets
+  const std::string bad_shape = check_geometry(kPlanXchg, g, bytes, nranks, kHalf);
+  if (!bad_shape.empty() || size_t(g.ctas) * nranks > size_t(max_resident_ctas(g.threads)))
+    return fail(hxcclInternalError, bad_shape.empty() ? "grid too large for a cooperative launch" : bad_shape.c_str());
 
   XchgArgs args[HXCCL_NOALLOC_MAX_RANKS];
   for (int r = 0; r < nranks; ++r) {

@@ -32,9 +32,12 @@ extern "C" {
  * size beyond the maximum; last error text via hxcclNoAllocLastError), hxcclTimeout when a
  * device-side wait ran out, hxcclUnhandledCudaError for CUDA failures.
  *
- * Scratch: one static device array of about 5.3 MiB per GPU that loads the library, held
- * until the process exits. The first call on a device looks the array's device address up
- * (cudaGetSymbolAddress) and caches it; make that first call outside any stream capture.
+ * Scratch: one static device array of 5 251 328 bytes (5.0 MiB) per GPU that loads the
+ * library, held until the process exits. The first call on a device is the set-up: with that
+ * device current it looks the array's device address up (cudaGetSymbolAddress) and clears the
+ * array; make that first call before any stream capture begins. Later calls repeat the look-up
+ * (so a device reset cannot leave a stale pointer behind). Every call copies its argument
+ * blocks from pageable host memory and ends with cudaStreamSynchronize(stream).
  * Every call uses the same array and finds what the previous call left there: flags only grow
  * from call to call and the status words are cleared at the start of each call. Two calls that
  * overlap on the GPU (different streams, or different threads) therefore race on the array;

@@ -41,7 +41,8 @@ __device__ __forceinline__ unsigned long long p2p_rounds(size_t total) {
   return r ? r : 1;  // an empty message still takes one hand-shake
 }
 
-__device__ inline void p2p_body(const P2pArgs& a, int lane_idx, int wk, int* sh_fail, unsigned long long* sh_word) {
+// One worker's share of every operation of a lane. False when a wait gave up.
+__device__ inline bool p2p_body(const P2pArgs& a, int lane_idx, int wk, int* sh_fail, unsigned long long* sh_word) {
   const WinView& w = a.w;
   const P2pLane& lane = a.lanes[lane_idx];
   const int me = w.rank, peer = lane.peer;
@@ -60,7 +61,7 @@ __device__ inline void p2p_body(const P2pArgs& a, int lane_idx, int wk, int* sh_
       for (unsigned long long q = 0; q < rounds; ++q, ++tx) {
         if (threadIdx.x == 0 && tx >= kP2pDepth && !wait_flag(w, done, tx - kP2pDepth + 1, peer)) *sh_fail = 1;
         __syncthreads();
-        if (*sh_fail) return;
+        if (*sh_fail) return false;
         size_t off, len;
         p2p_share(total, q, wk, &off, &len);
         if (len) cta_copy(p2p_slot(theirs, me, wk, unsigned(tx % kP2pDepth)), lane.ops[k].buf + off, len);
@@ -86,7 +87,7 @@ __device__ inline void p2p_body(const P2pArgs& a, int lane_idx, int wk, int* sh_
           *sh_word = ld_relaxed_sys(p2p_hdr(mine, peer, wk, unsigned(rx % kP2pDepth)));
         }
         __syncthreads();
-        if (*sh_fail) return;
+        if (*sh_fail) return false;
         const size_t total = *sh_word;
         if (q == 0) rounds = p2p_rounds(total);
         size_t off, len;
@@ -103,6 +104,7 @@ __device__ inline void p2p_body(const P2pArgs& a, int lane_idx, int wk, int* sh_
     }
     if (threadIdx.x == 0) *rx_state = rx;
   }
+  return true;
 }
 
 }  // namespace hx

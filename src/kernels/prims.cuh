@@ -169,11 +169,119 @@ __device__ inline void cta_copy(char* dst, const char* src, size_t n) {
   for (size_t k = t; k < n; k += nt) dst[k] = src[k];
 }
 
+__device__ __forceinline__ void mc_st16(char* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+// The same bytes to every rank at once: mc_dst is an address in the multicast alias of the
+// windows. Whole 16-byte vectors only (both addresses 16-byte aligned); returns the bytes it
+// covered, the caller sends the rest peer by peer.
+__device__ inline size_t cta_copy_multicast(char* mc_dst, const char* src, size_t n) {
+  const int t = threadIdx.x, nt = blockDim.x;
+  const size_t nv = n >> 4;
+  size_t i = t;
+  for (; i + 3 * size_t(nt) < nv; i += 4 * size_t(nt)) {
+    uint4 r[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) r[u] = ld16(src + ((i + u * size_t(nt)) << 4));
+#pragma unroll
+    for (int u = 0; u < 4; ++u) mc_st16(mc_dst + ((i + u * size_t(nt)) << 4), r[u]);
+  }
+  for (; i < nv; i += nt) mc_st16(mc_dst + (i << 4), ld16(src + (i << 4)));
+  return nv << 4;
+}
+
 // 16 bytes of elements of type T
 template <typename T>
 union Vec16 {
   uint4 raw;
   T e[16 / sizeof(T)];
 };
+
+// ---- a whole vector of elements through the element rule ------------------------------------------
+// out.e[l] = apply(a.e[l], b.e[l], op) for every lane. The generic form is the lane loop; the
+// fp8 types go two lanes at a time, because their hardware converters work on pairs
+// (cvt...x2) and converting one value per instruction, as the scalar rule in math/fpconv.h does,
+// leaves half of the converter's rate unused, which is what bounds an fp8 fold.
+template <typename T>
+__device__ __forceinline__ Vec16<T> apply_lanes(const Vec16<T>& a, const Vec16<T>& b, int op) {
+  Vec16<T> out;
+#pragma unroll
+  for (int l = 0; l < int(16 / sizeof(T)); ++l) out.e[l] = apply(a.e[l], b.e[l], op);
+  return out;
+}
+
+template <typename T>
+__device__ __forceinline__ Vec16<T> splat(T k) {
+  Vec16<T> v;
+#pragma unroll
+  for (int l = 0; l < int(16 / sizeof(T)); ++l) v.e[l] = k;
+  return v;
+}
+
+__device__ __forceinline__ float2 f16x2_to_f32(unsigned pair) {
+  float lo, hi;
+  asm("cvt.f32.f16 %0, %1;" : "=f"(lo) : "h"(static_cast<unsigned short>(pair & 0xffffu)));
+  asm("cvt.f32.f16 %0, %1;" : "=f"(hi) : "h"(static_cast<unsigned short>(pair >> 16)));
+  return make_float2(lo, hi);
+}
+// two e4m3 codes (low byte = first element) -> two floats, exact
+__device__ __forceinline__ float2 decode_pair(unsigned short codes, e4m3) {
+  unsigned pair;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(pair) : "h"(codes));
+  return f16x2_to_f32(pair);
+}
+// an e5m2 code is the upper byte of an fp16
+__device__ __forceinline__ float2 decode_pair(unsigned short codes, e5m2) {
+  return f16x2_to_f32(((unsigned(codes) & 0xff00u) << 16) | ((unsigned(codes) & 0xffu) << 8));
+}
+// two floats -> two codes under the library's rules (math/fpconv.h: hardware rounding, then the
+// overflow and NaN codes patched in, per element exactly as from_f32 does)
+__device__ __forceinline__ unsigned short encode_pair(float lo, float hi, e4m3) {
+  unsigned short pair;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(hi), "f"(lo));
+  const uint32_t ul = f32_bits(lo), al = ul & 0x7fffffffu, uh = f32_bits(hi), ah = uh & 0x7fffffffu;
+  unsigned r0 = pair & 0xffu, r1 = pair >> 8;
+  if (al > 0x43e80000u) r0 = al > 0x7f800000u ? 0x7fu : (((ul >> 24) & 0x80u) | 0x7fu);
+  if (ah > 0x43e80000u) r1 = ah > 0x7f800000u ? 0x7fu : (((uh >> 24) & 0x80u) | 0x7fu);
+  return static_cast<unsigned short>(r0 | (r1 << 8));
+}
+__device__ __forceinline__ unsigned short encode_pair(float lo, float hi, e5m2) {
+  unsigned short pair;
+  asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(hi), "f"(lo));
+  const uint32_t ul = f32_bits(lo), al = ul & 0x7fffffffu, uh = f32_bits(hi), ah = uh & 0x7fffffffu;
+  unsigned r0 = pair & 0xffu, r1 = pair >> 8;
+  if (al >= 0x47700000u) r0 = al > 0x7f800000u ? 0x7eu : (((ul >> 24) & 0x80u) | 0x7cu);
+  if (ah >= 0x47700000u) r1 = ah > 0x7f800000u ? 0x7eu : (((uh >> 24) & 0x80u) | 0x7cu);
+  return static_cast<unsigned short>(r0 | (r1 << 8));
+}
+template <typename F8>
+__device__ __forceinline__ Vec16<F8> apply_lanes_fp8(const Vec16<F8>& a, const Vec16<F8>& b, int op) {
+  Vec16<F8> out;
+  const unsigned wa[4] = {a.raw.x, a.raw.y, a.raw.z, a.raw.w}, wb[4] = {b.raw.x, b.raw.y, b.raw.z, b.raw.w};
+  unsigned wo[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    unsigned short half[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float2 x = decode_pair(static_cast<unsigned short>(wa[k] >> (16 * h)), F8{});
+      const float2 y = decode_pair(static_cast<unsigned short>(wb[k] >> (16 * h)), F8{});
+      half[h] = encode_pair(narrow_combine(x.x, y.x, op), narrow_combine(x.y, y.y, op), F8{});
+    }
+    wo[k] = unsigned(half[0]) | (unsigned(half[1]) << 16);
+  }
+  out.raw = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+  return out;
+}
+template <>
+__device__ __forceinline__ Vec16<e4m3> apply_lanes<e4m3>(const Vec16<e4m3>& a, const Vec16<e4m3>& b, int op) {
+  return apply_lanes_fp8<e4m3>(a, b, op);
+}
+template <>
+__device__ __forceinline__ Vec16<e5m2> apply_lanes<e5m2>(const Vec16<e5m2>& a, const Vec16<e5m2>& b, int op) {
+  return apply_lanes_fp8<e5m2>(a, b, op);
+}
 
 }  // namespace hx

@@ -28,6 +28,16 @@
 // finished hop s+1 of round k, so no extra hand-shake is needed between rounds. The launch
 // opens and closes with a hand-shake among all ranks like every multi-step launch
 // (coll_body.cuh). Epochs used: rounds * (2n-2) + 2.
+//
+// ReduceScatter (ring_rs) is the first half alone with every chain shifted by one rank, which is
+// the reference's ring_reducescatter schedule (src/algo_ring.cc:59-80): block b starts at rank
+// b+1 and ends, complete, on rank b. Hop s at rank r concerns block (r - s - 1) mod n and a round
+// has n hops (n-1 flags). Without the all-gather half the chain of dependencies around the ring
+// is one hop too short to protect a slot from the next round's writer (it proves only that the
+// slot's owner has finished hop s of the previous round, not hop s+1, which reads the slot), so
+// the slots alternate between two sets by the round's parity: the writer of a slot in round k+2
+// has seen, through that chain, every rank past hop s of round k+1, hence through with round k.
+// Epochs used: rounds * (n-1) + 2.
 #pragma once
 #include "kernels/coll_body.cuh"
 
@@ -60,6 +70,20 @@ __device__ inline void ring_pass(char* d0, char* d1, const char* own, const char
     if (completes && r.postdiv) v = div_trunc(v, r.postdiv);
     return v;
   };
+  auto lanes = [&](const Vec16<T>& x_own, const Vec16<T>& x_arr) -> Vec16<T> {  // `one` for 16 bytes
+    Vec16<T> v;
+    if (kOwn) {
+      v = r.premul ? apply_lanes(x_own, splat(r.scalar), kProd) : x_own;
+      if (kArr) v = apply_lanes(v, x_arr, r.op);
+    } else {
+      v = x_arr;
+    }
+    if (completes && r.postdiv) {
+#pragma unroll
+      for (int l = 0; l < V; ++l) v.e[l] = div_trunc(v.e[l], r.postdiv);
+    }
+    return v;
+  };
   const uintptr_t bits = reinterpret_cast<uintptr_t>(d0) | reinterpret_cast<uintptr_t>(d1) |
                          (kOwn ? reinterpret_cast<uintptr_t>(own) : 0) |
                          (kArr ? reinterpret_cast<uintptr_t>(arr) : 0);
@@ -76,19 +100,16 @@ __device__ inline void ring_pass(char* d0, char* d1, const char* own, const char
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const size_t off = (i + u * size_t(nt)) << 4;
-      Vec16<T> o;
-#pragma unroll
-      for (int l = 0; l < V; ++l) o.e[l] = one(kOwn ? a[u].e[l] : T{}, kArr ? b[u].e[l] : T{});
+      const Vec16<T> o = lanes(a[u], b[u]);
       if (d0) st16(d0 + off, o.raw);
       if (d1) st16(d1 + off, o.raw);
     }
   }
   for (; i < nvec; i += nt) {
-    Vec16<T> a, b, o;
+    Vec16<T> a, b;
     if (kOwn) a.raw = ld16(own + (i << 4));
     if (kArr) b.raw = ld16(arr + (i << 4));
-#pragma unroll
-    for (int l = 0; l < V; ++l) o.e[l] = one(kOwn ? a.e[l] : T{}, kArr ? b.e[l] : T{});
+    const Vec16<T> o = lanes(a, b);
     if (d0) st16(d0 + (i << 4), o.raw);
     if (d1) st16(d1 + (i << 4), o.raw);
   }
@@ -114,9 +135,14 @@ __device__ void ring_body(const TwoShotArgs& a, int cta, int ncta, FoldShared& s
   if (!signal_and_wait(w, kOffFlagsA, cta, a.epoch0, &sh.fail)) return;  // entry
   tm.lap(kTrWaitB);
 
-  const int hops = 2 * n - 2;  // slots per round, and flags raised per round
+  const bool rs = a.ring_rs != 0;
+  const int shift = rs ? 1 : 0;
+  const int hops = rs ? n - 1 : 2 * n - 2;  // flags raised per round (and slots of one set)
   const size_t base = w.half_off[0];
-  auto slot = [&](char* win, int s) { return win + base + (size_t(s) * ncta + cta) * a.sub_bytes; };
+  int set = 0;  // ReduceScatter: slot set of the current round
+  auto slot = [&](char* win, int s) {
+    return win + base + (size_t(set * hops + s) * ncta + cta) * a.sub_bytes;
+  };
   unsigned long long* to_right = flag_at(w.win[right], kOffFlagsA, cta, me);
   const unsigned long long* from_left = flag_at(w.win[me], kOffFlagsA, cta, left);
   char* mine = w.win[me];
@@ -125,8 +151,9 @@ __device__ void ring_body(const TwoShotArgs& a, int cta, int ncta, FoldShared& s
   for (int k = 0; k < a.steps; ++k) {
     const unsigned long long e0 = a.epoch0 + 1 + static_cast<unsigned long long>(k) * hops;
     const size_t rel = (size_t(k) * ncta + cta) * a.sub_bytes;
+    set = rs ? (k & 1) : 0;
     for (int s = 0; s <= hops; ++s) {
-      int b = (me - s) % n;
+      int b = (me - s - shift) % n;
       if (b < 0) b += n;
       const size_t blk0 = sh.bound[b] * sizeof(T), blk_bytes = (sh.bound[b + 1] - sh.bound[b]) * sizeof(T);
       const size_t len = rel < blk_bytes ? min_sz(a.sub_bytes, blk_bytes - rel) : 0;
@@ -137,14 +164,14 @@ __device__ void ring_body(const TwoShotArgs& a, int cta, int ncta, FoldShared& s
         tm.lap(kTrWaitA);
       }
       const char* own = a.send + blk0 + rel;
-      char* out = a.recv + blk0 + rel;
+      char* out = rs ? a.recv + rel : a.recv + blk0 + rel;
       if (len) {
         if (s == 0)
           ring_pass<T, true, false>(slot(peer, 0), nullptr, own, nullptr, len, rule, false);
         else if (s < n - 1)
           ring_pass<T, true, true>(slot(peer, s), nullptr, own, slot(mine, s - 1), len, rule, false);
         else if (s == n - 1)
-          ring_pass<T, true, true>(slot(peer, s), out, own, slot(mine, s - 1), len, rule, true);
+          ring_pass<T, true, true>(rs ? nullptr : slot(peer, s), out, own, slot(mine, s - 1), len, rule, true);
         else
           ring_pass<T, false, true>(s < hops ? slot(peer, s) : nullptr, out, nullptr, slot(mine, s - 1), len, rule, false);
       }

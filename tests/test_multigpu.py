@@ -114,7 +114,7 @@ def _nvls_body(comm, rank, n):
 def test_allreduce_nvls(n):
     import torch
 
-    res = run_ranks(n, _nvls_body, gpus=True, timeout=120)
+    res = run_ranks(n, _nvls_body, gpus=True, timeout=120, nvls=True)
     if res[0][1] is None:
         pytest.skip("no NVSwitch multicast on this node: " + res[0][0]["kind"])
     count = 1 << 20

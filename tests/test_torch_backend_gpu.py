@@ -13,6 +13,7 @@ import torch.multiprocessing as mp  # noqa: E402
 
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 NGPU = gpu_count()
+WAIT_LIMIT_MS = 5000
 
 
 def _worker(rank, world, port, q):
@@ -23,7 +24,10 @@ def _worker(rank, world, port, q):
 
         torch.cuda.set_device(rank)
         hp.register()
-        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        # not about multicast: windows stay unbound, and waits are short, so that a rank whose
+        # peer failed leaves through its bounded wait instead of being ended from outside
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), HXCCL_NVLS="0",
+                          HXCCL_WAIT_LIMIT_MS=str(WAIT_LIMIT_MS))
         dist.init_process_group("hxccl", rank=rank, world_size=world)
         assert hp.device_info()["kind"].startswith("window")
         dev = torch.device("cuda", rank)
@@ -96,8 +100,14 @@ def test_backend_on_gpus(world):
             if got[-1][1] != "ok":
                 break
     finally:
+        # survivors of a failed run leave on their own once their device-side waits run out and
+        # their process group is torn down; only after that grace period is a process ended
+        import time
+
+        give_up = time.monotonic() + WAIT_LIMIT_MS / 1000.0 + 10.0
         for p in procs:
-            p.join(5 if all(m == "ok" for _, m in got) and len(got) == world else 0.5)
+            p.join(max(0.1, give_up - time.monotonic()))
+        for p in procs:
             if p.is_alive():
                 p.kill()
     assert len(got) == world and all(m == "ok" for _, m in got), got

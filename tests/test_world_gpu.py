@@ -155,6 +155,109 @@ def test_allreduce_neighbour_ring(worlds, n):
         w.knob("ring_sub", 512 * 1024)
 
 
+@pytest.mark.parametrize("n", [2, 3, 4, 8])
+def test_allreduce_flag_in_data_lines(worlds, n):
+    """The small-message kernel whose 16-byte lines carry their own epoch: every type and
+    operator in both operand orders, in place and out of place, sizes from one element to the
+    most a slot holds, and back-to-back launches (the halves alternate with the epoch)."""
+    w = worlds(n)
+    most = (768 * 1024 // 2 // n // 256 * 256) // 2  # payload bytes of one slot
+    for order in (1, 0):
+        w.tune(variant=7, exact=True)
+        for dt in ALL_DT:
+            es = L.DTYPE_SIZE[dt]
+            for op in (L.SUM, L.PROD, L.MAX, L.MIN, L.AVG):
+                for count in (1, 7, 1021, most // es):
+                    xs = rand_inputs(n, count, dt, seed=dt * 100 + op * 10 + n + 11 * order)
+                    send = [to_dev(x) for x in xs]
+                    recv = [torch.zeros_like(s) for s in send]
+                    w.all_reduce(send, recv, count, dt, op=op, order=order)
+                    assert w.info()["variant"] == 7
+                    w.all_reduce(send, send, count, dt, op=op, order=order)  # in place, next epoch
+                    torch.cuda.synchronize()
+                    want = oracle.allreduce(xs, dt, op, order=order)
+                    for r in range(n):
+                        assert np.array_equal(back(recv[r], dt), want[r]), (n, order, dt, op, count, r)
+                        assert np.array_equal(back(send[r], dt), want[r]), ("in place", n, order, dt, op, count, r)
+    # left to the tuner, small messages take it and larger ones do not
+    w.tune(variant=0, exact=True)
+    x = [to_dev(v) for v in rand_inputs(n, 64, L.FLOAT32, 1)]
+    w.all_reduce(x, x, 64, L.FLOAT32)
+    assert w.info()["variant"] == 7
+    y = [to_dev(v) for v in rand_inputs(n, 1 << 18, L.FLOAT32, 2)]
+    w.all_reduce(y, y, 1 << 18, L.FLOAT32)
+    assert w.info()["variant"] != 7
+    # one element more than a slot holds: forcing the variant falls back to the one-shot kernel
+    w.tune(variant=7, exact=True)
+    big = [to_dev(v) for v in rand_inputs(n, most + 8, L.UINT8, 3)]
+    w.all_reduce(big, big, most + 8, L.UINT8)
+    torch.cuda.synchronize()
+    assert w.info()["variant"] != 7
+    w.tune(variant=0, exact=True)
+    assert all(w.status(r) == (0, 0) for r in range(n))
+
+
+@pytest.mark.parametrize("n", [2, 3, 8])
+def test_allreduce_with_narrow_wire_type(worlds, n):
+    """fp32 buffers with bf16 / fp16 on the wire (hxcclAllReduceCast): the bits of "cast, AllReduce
+    in the narrow type, cast back", computed here with torch's casts and the host oracle.
+    Single-step and pipelined sizes, odd counts, in place."""
+    w = worlds(n)
+    w.tune(variant=0, exact=True)
+    for wire, tdt in ((L.BFLOAT16, torch.bfloat16), (L.FLOAT16, torch.float16)):
+        for op in (L.AVG, L.SUM, L.MAX):
+            for count in (32768, 70001, (3 << 20) // 2 + 5):
+                g = torch.Generator().manual_seed(count + wire + op)
+                xs = [(torch.randn(count, generator=g) * 3).float() for _ in range(n)]
+                narrow = [x.to(tdt).view(torch.uint16).numpy().copy() for x in xs]
+                want = oracle.allreduce(narrow, wire, op, order=0)
+                want32 = [torch.from_numpy(v.copy()).view(tdt).float() for v in want]
+                send = [x.cuda() for x in xs]
+                recv = [torch.zeros_like(s) for s in send]
+                w.all_reduce_cast(send, recv, count, wire, op=op)
+                w.all_reduce_cast(send, send, count, wire, op=op)  # in place
+                torch.cuda.synchronize()
+                for r in range(n):
+                    assert torch.equal(recv[r].cpu().view(torch.int32), want32[r].view(torch.int32)), (n, wire, op, count, r)
+                    assert torch.equal(send[r].cpu().view(torch.int32), want32[r].view(torch.int32)), ("in place", n, wire, op, count, r)
+    assert all(w.status(r) == (0, 0) for r in range(n))
+
+
+@pytest.mark.parametrize("n", [2, 3, 4, 8])
+def test_reducescatter_neighbour_ring(worlds, n):
+    """ReduceScatter around the ring (the large-input form) forced onto small inputs: all types,
+    blocks of one element, many rounds with small slots (both slot sets), in place."""
+    w = worlds(n)
+    w.knob("rs_ring_min", 1)
+    try:
+        for sub in (512 * 1024, 4096):
+            w.knob("ring_sub", sub)
+            for dt in ALL_DT:
+                for op in (L.SUM, L.MAX, L.AVG):
+                    for per in ((1, 1031) if sub > 4096 else ((300 * 1024) // L.DTYPE_SIZE[dt] + 3,)):
+                        xs = rand_inputs(n, per * n, dt, seed=per + dt + n)
+                        if dt in FLOATS and per > 2000:
+                            for x in xs:
+                                x &= x.dtype.type(~(1 << (8 * L.DTYPE_SIZE[dt] - 2)) & ((1 << (8 * L.DTYPE_SIZE[dt])) - 1))
+                        send = [to_dev(x) for x in xs]
+                        recv = [torch.zeros(per * L.DTYPE_SIZE[dt], dtype=torch.uint8, device="cuda") for _ in range(n)]
+                        before = w.info()["launches"]
+                        w.reduce_scatter(send, recv, per, dt, op=op)
+                        # in place: recv is the rank's own block of send
+                        nb = per * L.DTYPE_SIZE[dt]
+                        w.reduce_scatter(send, [send[r][r * nb:(r + 1) * nb] for r in range(n)], per, dt, op=op)
+                        torch.cuda.synchronize()
+                        assert w.info()["launches"] == before + 2
+                        want = oracle.reducescatter(xs, dt, op)
+                        for r in range(n):
+                            assert np.array_equal(back(recv[r], dt), want[r]), ("ring rs", n, sub, dt, op, per, r)
+                            assert np.array_equal(back(send[r][r * nb:(r + 1) * nb].contiguous(), dt), want[r]), ("in place", n, dt, op, r)
+        assert all(w.status(r) == (0, 0) for r in range(n))
+    finally:
+        w.knob("rs_ring_min", 256 << 20)
+        w.knob("ring_sub", 512 * 1024)
+
+
 @pytest.mark.parametrize("n", [2, 3, 8])
 def test_reducescatter_and_reduce(worlds, n):
     w = worlds(n)

@@ -53,6 +53,33 @@ def test_matches_world_allreduce_twice(n):
                     assert torch.equal(got[r], want[r]), (n, round_no, dt, op, r)
 
 
+@pytest.mark.parametrize("n", [1, 2, 3, 4])
+def test_matches_the_host_rules(n):
+    """An oracle that shares no code with the kernels: the reduction orders and element rules of
+    the host path, restated in hxccl_b200/ops/oracle.py. One rank included (its result is its
+    input, scaled by 1/1 for a float average)."""
+    from hxccl_b200.ops import oracle
+
+    lib, fn = _entry()
+    stream = torch.cuda.current_stream().cuda_stream
+    for dt, op, count in ((L.FLOAT32, L.SUM, 70001), (L.FLOAT16, L.AVG, 513), (L.INT32, L.AVG, 11),
+                          (L.BFLOAT16, L.MAX, 3), (L.FLOAT32, L.SUM, 5)):
+        es = L.DTYPE_SIZE[dt]
+        xs_np = []
+        for r in range(n):
+            x = np.random.default_rng(1000 * dt + r).integers(0, 256, count * es, dtype=np.uint8).view(oracle.raw_dtype(dt))
+            if dt >= L.FLOAT16:  # moderate magnitudes: clear the top exponent bit
+                x &= x.dtype.type(~(1 << (8 * es - 2)) & ((1 << (8 * es)) - 1))
+            xs_np.append(x)
+        want = oracle.allreduce(xs_np, dt, op)
+        xs = [torch.from_numpy(x.view(np.uint8).copy()).cuda() for x in xs_np]
+        got = [torch.zeros_like(x) for x in xs]
+        rc = fn(n, _ptrs(xs), _ptrs(got), count, dt, op, stream)
+        assert rc == 0, lib.hxcclNoAllocLastError().decode()
+        for r in range(n):
+            assert np.array_equal(got[r].cpu().numpy().view(oracle.raw_dtype(dt)), want[r]), (n, dt, op, count, r)
+
+
 def test_rejects_what_it_cannot_hold():
     lib, fn = _entry()
     x = [torch.zeros(16, device="cuda") for _ in range(2)]
