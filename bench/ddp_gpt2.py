@@ -33,7 +33,9 @@ def main() -> int:
     ap.add_argument("--exact", type=int, default=1)
     ap.add_argument("--max-ctas", type=int, default=48, help="grid bound of the hxccl kernels during training")
     ap.add_argument("--check", action="store_true", help="print the loss of every step")
-    ap.add_argument("--compress", action="store_true", help="hxccl: average the buckets in bfloat16 (half the bytes)")
+    ap.add_argument("--compress", action="store_true",
+                    help="average the buckets in bfloat16 (half the bytes): hxccl's one-kernel cast AllReduce, or "
+                         "torch's bf16_compress_hook around NCCL")
     args = ap.parse_args()
 
     import torch
@@ -65,6 +67,10 @@ def main() -> int:
         from hxccl_b200.parallel import bf16_compress_average_hook, fused_average_hook
 
         ddp.register_comm_hook(None, bf16_compress_average_hook if args.compress else fused_average_hook)
+    elif args.compress and world > 1:
+        from torch.distributed.algorithms.ddp_comm_hooks.default_hooks import bf16_compress_hook
+
+        ddp.register_comm_hook(None, bf16_compress_hook)
     opt = torch.optim.AdamW(ddp.parameters(), lr=3e-4, fused=True)
     g = torch.Generator(device="cuda").manual_seed(1000 + rank)
 
@@ -107,6 +113,7 @@ def main() -> int:
                           "value": round(world * args.batch * seq / (ms * 1e-3), 1), "ms_per_step": round(ms, 3),
                           "model": "gpt2-tiny" if args.tiny else "gpt2-small", "params": model.num_params(),
                           "micro_batch": args.batch, "seq_len": seq, "dtype": "bf16 autocast", "bucket_mb": 25,
+                          "wire": "bf16" if args.compress else "fp32", "max_ctas": args.max_ctas,
                           "device_path": info, "losses": losses[:8]}))
     return 0
 

@@ -6,10 +6,15 @@
 //   hx_perf -g 8 [-o allreduce|allgather|reducescatter|alltoall|broadcast|reduce|gather|scatter|sendrecv]
 //           [-b 8] [-e 1073741824] [-f 2] [-n 20] [-w 5] [-t float|bf16|half|int32|...] [-r sum|max|avg|...]
 //           [-H]   host buffers instead of device buffers
+//           [-I nccl]  time NCCL instead (libnccl.so.2 found by the loader, or the file named by
+//                      HX_PERF_NCCL_LIB), same processes, buffers, barriers and timing, so that
+//                      both libraries are measured without an interpreter; allreduce, allgather,
+//                      reducescatter, broadcast, reduce, alltoall and sendrecv
 //
 // Plays the role of the reference's bench/hxccl_perf.cc:53-205 (which compares with MPI and
 // times on the host, valid there because its calls block).
 #include <cuda_runtime.h>
+#include <dlfcn.h>
 #include <sys/wait.h>
 #include <time.h>
 #include <unistd.h>
@@ -37,7 +42,62 @@ namespace {
 int g_rank = 0;
 hxcclComm_t g_comm = nullptr;
 
+// The few NCCL entry points the comparison arm needs, resolved at run time so that the tool
+// builds and runs where NCCL is absent. Types and values follow nccl.h (ncclDataType_t and
+// ncclRedOp_t share hxccl's numbering, which is NCCL's).
+struct Nccl {
+  void* so = nullptr;
+  int (*GetUniqueId)(void*) = nullptr;
+  int (*CommInitRank)(void**, int, hxcclUniqueId, int) = nullptr;  // ncclUniqueId is 128 bytes too
+  int (*CommDestroy)(void*) = nullptr;
+  int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
+  int (*ReduceScatter)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+  int (*Broadcast)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+  int (*Reduce)(const void*, void*, size_t, int, int, int, void*, cudaStream_t) = nullptr;
+  int (*Send)(const void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+  int (*Recv)(void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+  int (*GroupStart)() = nullptr;
+  int (*GroupEnd)() = nullptr;
+  void* comm = nullptr;
+  bool load() {
+    const char* path = std::getenv("HX_PERF_NCCL_LIB");
+    so = dlopen(path && *path ? path : "libnccl.so.2", RTLD_NOW | RTLD_LOCAL);
+    if (!so) {
+      std::fprintf(stderr, "cannot load NCCL: %s\n", dlerror());
+      return false;
+    }
+    auto sym = [&](const char* name) { return dlsym(so, name); };
+#define HX_NCCL_SYM(field, name) field = reinterpret_cast<decltype(field)>(sym(name))
+    HX_NCCL_SYM(GetUniqueId, "ncclGetUniqueId");
+    HX_NCCL_SYM(CommInitRank, "ncclCommInitRank");
+    HX_NCCL_SYM(CommDestroy, "ncclCommDestroy");
+    HX_NCCL_SYM(AllReduce, "ncclAllReduce");
+    HX_NCCL_SYM(AllGather, "ncclAllGather");
+    HX_NCCL_SYM(ReduceScatter, "ncclReduceScatter");
+    HX_NCCL_SYM(Broadcast, "ncclBroadcast");
+    HX_NCCL_SYM(Reduce, "ncclReduce");
+    HX_NCCL_SYM(Send, "ncclSend");
+    HX_NCCL_SYM(Recv, "ncclRecv");
+    HX_NCCL_SYM(GroupStart, "ncclGroupStart");
+    HX_NCCL_SYM(GroupEnd, "ncclGroupEnd");
+#undef HX_NCCL_SYM
+    return GetUniqueId && CommInitRank && CommDestroy && AllReduce && AllGather && ReduceScatter && Broadcast &&
+           Reduce && Send && Recv && GroupStart && GroupEnd;
+  }
+};
+Nccl g_nccl;
+#define NK(x)                                                                   \
+  do {                                                                          \
+    const int r_ = (x);                                                         \
+    if (r_ != 0) {                                                              \
+      std::fprintf(stderr, "[rank %d] %s failed: NCCL result %d\n", g_rank, #x, r_); \
+      std::exit(2);                                                             \
+    }                                                                           \
+  } while (0)
+
 struct Options {
+  bool nccl = false;
   int gpus = 1;
   std::string op = "allreduce", type = "float", red = "sum";
   size_t min_bytes = 8, max_bytes = size_t(1) << 30;
@@ -68,9 +128,11 @@ hxcclRedOp_t parse_red(const std::string& r) {
   std::exit(1);
 }
 
-int run_rank(const Options& o, int rank, const hxcclUniqueId& id) {
+int run_rank(const Options& o, int rank, const hxcclUniqueId& id, const hxcclUniqueId& nccl_id) {
   g_rank = rank;
   const int n = o.gpus;
+  // the NCCL arm keeps an hxccl communicator for the host-side barriers only: no device path
+  if (o.nccl) setenv("HXCCL_DEVICE", "0", 1);
   if (!o.host) {
     int ndev = 0;
     cudaGetDeviceCount(&ndev);
@@ -82,6 +144,7 @@ int run_rank(const Options& o, int rank, const hxcclUniqueId& id) {
     cudaFree(nullptr);
   }
   CK(hxcclCommInitRank(&g_comm, n, id, rank));
+  if (o.nccl) NK(g_nccl.CommInitRank(&g_nccl.comm, n, nccl_id, rank));
   size_t es = 4;
   const hxcclDataType_t dt = parse_type(o.type, &es);
   const hxcclRedOp_t red = parse_red(o.red);
@@ -107,6 +170,7 @@ int run_rank(const Options& o, int rank, const hxcclUniqueId& id) {
   }
   char kind[32] = "host";
   if (!o.host) hxcclCommDeviceInfo(g_comm, kind, sizeof kind, nullptr, nullptr);
+  if (o.nccl) std::snprintf(kind, sizeof kind, "nccl");
   if (rank == 0)
     std::printf("# hx_perf  op=%s type=%s red=%s ranks=%d buffers=%s path=%s iters=%d warmup=%d\n"
                 "# %12s %12s %12s %12s %12s\n",
@@ -117,6 +181,31 @@ int run_rank(const Options& o, int rank, const hxcclUniqueId& id) {
     // gathered / scattered total for the others
     const size_t count = std::max<size_t>(1, bytes / es / (gathers || scatters ? n : 1));
     auto call = [&]() {
+      if (o.nccl) {
+        void* c = g_nccl.comm;
+        if (o.op == "allreduce") NK(g_nccl.AllReduce(send, recv, count, dt, red, c, st));
+        else if (o.op == "allgather") NK(g_nccl.AllGather(send, recv, count, dt, c, st));
+        else if (o.op == "reducescatter") NK(g_nccl.ReduceScatter(send, recv, count, dt, red, c, st));
+        else if (o.op == "broadcast") NK(g_nccl.Broadcast(send, recv, count, dt, 0, c, st));
+        else if (o.op == "reduce") NK(g_nccl.Reduce(send, recv, count, dt, red, 0, c, st));
+        else if (o.op == "alltoall") {
+          NK(g_nccl.GroupStart());
+          for (int p = 0; p < n; ++p) {
+            NK(g_nccl.Send(send + size_t(p) * count * es, count, dt, p, c, st));
+            NK(g_nccl.Recv(recv + size_t(p) * count * es, count, dt, p, c, st));
+          }
+          NK(g_nccl.GroupEnd());
+        } else if (o.op == "sendrecv") {
+          NK(g_nccl.GroupStart());
+          NK(g_nccl.Send(send, count, dt, (rank + 1) % n, c, st));
+          NK(g_nccl.Recv(recv, count, dt, (rank + n - 1) % n, c, st));
+          NK(g_nccl.GroupEnd());
+        } else {
+          std::fprintf(stderr, "the NCCL arm has no %s\n", o.op.c_str());
+          std::exit(1);
+        }
+        return;
+      }
       if (o.op == "allreduce") CK(hxcclAllReduce(send, recv, count, dt, red, g_comm, st));
       else if (o.op == "allgather") CK(hxcclAllGather(send, recv, count, dt, g_comm, st));
       else if (o.op == "reducescatter") CK(hxcclReduceScatter(send, recv, count, dt, red, g_comm, st));
@@ -168,6 +257,10 @@ int run_rank(const Options& o, int rank, const hxcclUniqueId& id) {
   hxcclResult_t async = hxcclSuccess;
   hxcclCommGetAsyncError(g_comm, &async);
   if (async != hxcclSuccess) std::fprintf(stderr, "[rank %d] asynchronous error: %s\n", rank, hxcclGetLastError(g_comm));
+  if (o.nccl) {
+    cudaStreamSynchronize(st);
+    NK(g_nccl.CommDestroy(g_nccl.comm));
+  }
   CK(hxcclCommDestroy(g_comm));
   return async == hxcclSuccess ? 0 : 3;
 }
@@ -175,7 +268,7 @@ int run_rank(const Options& o, int rank, const hxcclUniqueId& id) {
 
 int main(int argc, char** argv) {
   Options o;
-  for (int c; (c = getopt(argc, argv, "g:o:b:e:f:n:w:t:r:H")) != -1;) {
+  for (int c; (c = getopt(argc, argv, "g:o:b:e:f:n:w:t:r:HI:")) != -1;) {
     switch (c) {
       case 'g': o.gpus = std::atoi(optarg); break;
       case 'o': o.op = optarg; break;
@@ -187,10 +280,12 @@ int main(int argc, char** argv) {
       case 't': o.type = optarg; break;
       case 'r': o.red = optarg; break;
       case 'H': o.host = true; break;
+      case 'I': o.nccl = std::string(optarg) == "nccl"; break;
       default: std::fprintf(stderr, "see the header of bench/hx_perf.cc for usage\n"); return 1;
     }
   }
   if (o.gpus < 1 || o.min_bytes < 1 || o.max_bytes < o.min_bytes) return 1;
+  if (o.nccl && (o.host || !g_nccl.load())) return 1;
   // rank 0 is this process; the id reaches each child through its own pipe (fork comes first,
   // so that no child inherits a CUDA context or the id's listening socket)
   std::vector<int> wr(o.gpus, -1);
@@ -201,21 +296,25 @@ int main(int argc, char** argv) {
     const pid_t pid = fork();
     if (pid == 0) {
       close(p[1]);
-      hxcclUniqueId id;
+      hxcclUniqueId id, nid;
       if (read(p[0], &id, sizeof id) != ssize_t(sizeof id)) _exit(2);
-      _exit(run_rank(o, r, id));
+      if (read(p[0], &nid, sizeof nid) != ssize_t(sizeof nid)) _exit(2);
+      _exit(run_rank(o, r, id, nid));
     }
     close(p[0]);
     wr[r] = p[1];
     kids.push_back(pid);
   }
-  hxcclUniqueId id;
+  hxcclUniqueId id, nid;
+  std::memset(&nid, 0, sizeof nid);
   if (hxcclGetUniqueId(&id) != hxcclSuccess) return 2;
+  if (o.nccl && g_nccl.GetUniqueId(&nid) != 0) return 2;
   for (int r = 1; r < o.gpus; ++r) {
     if (write(wr[r], &id, sizeof id) != ssize_t(sizeof id)) return 2;
+    if (write(wr[r], &nid, sizeof nid) != ssize_t(sizeof nid)) return 2;
     close(wr[r]);
   }
-  int rc = run_rank(o, 0, id);
+  int rc = run_rank(o, 0, id, nid);
   for (pid_t k : kids) {
     int status = 0;
     waitpid(k, &status, 0);

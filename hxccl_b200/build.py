@@ -120,7 +120,7 @@ def build_perf(verbose: bool = False) -> Path:
     if out.exists() and out.stat().st_mtime > max(src.stat().st_mtime, LIB.stat().st_mtime):
         return out
     cmd = [NVCC, "-std=c++17", "-O2", *INCLUDES, str(src), "-o", str(out), f"-L{LIB_DIR}", "-lhxccl",
-           "-Xlinker", f"-rpath={LIB_DIR}", "-Xlinker", "-rpath=$ORIGIN/../hxccl_b200/lib", "-cudart", "static"]
+           "-Xlinker", f"-rpath={LIB_DIR}", "-Xlinker", "-rpath=$ORIGIN/../hxccl_b200/lib", "-cudart", "static", "-ldl"]
     if verbose:
         print(" ".join(cmd), flush=True)
     res = subprocess.run(cmd, capture_output=True, text=True)

@@ -103,7 +103,10 @@ def run_ranks(n: int, fn: Callable, *args: Any, env: Optional[Dict[str, str]] = 
     while pending:
         for r in sorted(pending):
             if outs[r][0].poll(0.05):
-                kind, val = outs[r][0].recv()
+                try:
+                    kind, val = outs[r][0].recv()
+                except Exception as e:  # noqa: BLE001  (a result that cannot be rebuilt here)
+                    kind, val = "err", f"rank {r}: its result could not be received: {e!r}"
                 if kind == "ok":
                     results[r] = val
                 else:

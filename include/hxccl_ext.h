@@ -83,6 +83,16 @@ hxcclResult_t hxcclTestNarrowConvert(hxcclDataType_t dt, unsigned long long* mis
 hxcclResult_t hxcclTestPlan(int kind, size_t amount, int nranks, size_t half_bytes, int max_ctas,
                             const char* knob, long knob_value, size_t shape[5], char* why, size_t why_len);
 
+/* Which AllReduce variant the tuner picks for `bytes` of `dt` on `nranks` ranks in exact (1) or
+ * fast (0) mode, with (1) or without (0) NVSwitch multicast, from the compiled-in table, then
+ * HXCCL_TUNE_FILE when set. *from_table: 1 when a table row decided, 0 when the fixed thresholds
+ * did. shape = {grid limit, CTA width (0 = by size), per-step share} after the row was applied. */
+hxcclResult_t hxcclTestChooseVariant(size_t bytes, hxcclDataType_t dt, int nranks, int exact, int nvls,
+                                     int* variant, int* from_table, size_t shape[3]);
+
+/* Rows of the compiled-in tuning table that parsed. */
+int hxcclTestTableRows(void);
+
 /* ---- fault injection (host side only) ---------------------------------------------------------- */
 /* The (after+1)-th host-path send from now fails with hxcclSystemError; after < 0 disarms. */
 hxcclResult_t hxcclTestFailSends(hxcclComm_t comm, long after);

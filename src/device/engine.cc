@@ -57,7 +57,9 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
     ++launches;
     return launch_copy(b[0].recv, b[0].send, bytes, st);
   }
-  int var = choose_variant(bytes, dt, plan, n(), tune, forced_variant);
+  const TuneRow* row = nullptr;
+  int var = choose_variant(bytes, dt, plan, n(), tune, forced_variant, &row);
+  const Tuning tune = with_row(this->tune, row, var);  // the row's launch shape, for this call only
   // recursive doubling gives every rank its own operand order; only the variant in which each
   // rank folds for itself can replay that
   if (order == kOrderDoubling && tune.exact && !is_integer(dt) && var != kVarLL) var = kVarOneShot;
@@ -117,8 +119,9 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
   }
   // The three-role pipeline wins for the multicast reduction from three ranks on; for the
   // exact two-shot it measured faster than the single-role kernel only on eight ranks.
-  const bool roles = bytes >= tune.roles_min && tune.max_ctas >= 3 &&
-                     (var == kVarNvls ? n() > 2 : n() >= tune.roles_min_ranks);
+  const bool roles = tune.max_ctas >= 3 &&
+                     (row ? (row->variant == kVarTwoShotRoles || row->variant == kVarNvlsRoles)
+                          : bytes >= tune.roles_min && (var == kVarNvls ? n() > 2 : n() >= tune.roles_min_ranks));
   const Geometry g = roles ? plan_roles(bytes, n(), views[0].half_bytes, tune)
                            : plan_sliced(bytes, n(), views[0].half_bytes, tune);
   HX_CHECK_PLAN(roles ? kPlanRoles : kPlanSliced, g, bytes);
@@ -164,7 +167,11 @@ cudaError_t Engine::reducescatter(const RankBufs* b, size_t per, int dt, const O
   const size_t block = per * dtype_size(dt);
   // Large inputs go around the neighbour ring (one sender per receiver through the switch, the
   // same schedule and therefore the same bits); smaller ones are pushed to their owners at once.
-  if (n() >= 2 && block > 0 && ((tune.rs_ring_min && block * n() >= tune.rs_ring_min) || forced_variant == kVarRing)) {
+  const TuneRow* row = forced_variant == kVarAuto ? find_row(this->tune, kCollReduceScatter, n(), int(dtype_size(dt)), true, block) : nullptr;
+  const bool ring = row ? row->variant == 1
+                        : ((this->tune.rs_ring_min && block * n() >= this->tune.rs_ring_min) || forced_variant == kVarRing);
+  const Tuning tune = with_row(this->tune, row, ring ? kVarRing : kVarOneShot);
+  if (n() >= 2 && block > 0 && ring) {
     const Geometry g = plan_ring(block, n(), views[0].half_bytes, tune, true);
     HX_CHECK_PLAN(kPlanRingRs, g, block);
     std::vector<TwoShotArgs> args(views.size());
@@ -214,11 +221,21 @@ cudaError_t Engine::reduce(const RankBufs* b, size_t count, int dt, const OpPlan
   return rc != cudaSuccess ? rc : launch_xchg_copy(a, shape(g), st);
 
 cudaError_t Engine::allgather(const RankBufs* b, size_t block, cudaStream_t st) {
-  const bool mc = tune.nvls && tune.mc_copy && !world() && block >= tune.mc_copy_min;
+  // AllGather moves the same bytes into every rank whichever way they are pushed, so multicast
+  // only spares the sender's link; it pays where the table measured it to.
+  const TuneRow* row = find_row(this->tune, kCollAllGather, n(), 0, true, block);
+  const Tuning tune = with_row(this->tune, row, kVarOneShot);
+  const bool mc = tune.nvls && tune.mc_copy && !world() && block >= tune.mc_copy_min &&
+                  (tune.mc_force >= 0 ? tune.mc_force == 1 : (row && row->variant == 1));
   HX_COPY_COLLECTIVE(block, build_allgather(&args[r], views[r], epoch, g, b[r].send, b[r].recv, block, mc))
 }
 cudaError_t Engine::broadcast(const RankBufs* b, size_t bytes, int root, cudaStream_t st) {
-  const bool mc = tune.nvls && tune.mc_copy && !world() && bytes >= tune.mc_copy_min;
+  // A root that stores to every peer sends the message n-1 times over its one link; through
+  // the switch's multicast it sends it once. Without a table row: multicast from three ranks on.
+  const TuneRow* row = find_row(this->tune, kCollBroadcast, n(), 0, true, bytes);
+  const Tuning tune = with_row(this->tune, row, kVarOneShot);
+  const bool mc = tune.nvls && tune.mc_copy && !world() && bytes >= tune.mc_copy_min &&
+                  (tune.mc_force >= 0 ? tune.mc_force == 1 : (row ? row->variant == 1 : n() > 2));
   HX_COPY_COLLECTIVE(bytes, build_broadcast(&args[r], views[r], epoch, g, b[r].send, b[r].recv, bytes, root, mc))
 }
 cudaError_t Engine::gather(const RankBufs* b, size_t block, int root, cudaStream_t st) {

@@ -131,6 +131,7 @@ hxcclResult_t hxcclTestPlan(int kind, size_t amount, int nranks, size_t half_byt
   using namespace hx;
   if (nranks < 1 || nranks > kMaxRanks || !shape) return hxcclInvalidArgument;
   Tuning t;
+  load_default_table(&t);
   if (const char* path = std::getenv("HXCCL_TUNE_FILE")) {
     std::string bad_line;
     if (!load_tune_file(&t, path, &bad_line)) {
@@ -160,6 +161,39 @@ hxcclResult_t hxcclTestPlan(int kind, size_t amount, int nranks, size_t half_byt
   const std::string bad = check_geometry(kind, g, amount, nranks, half_bytes);
   if (why && why_len) std::snprintf(why, why_len, "%s", bad.c_str());
   return bad.empty() ? hxcclSuccess : hxcclInternalError;
+}
+
+int hxcclTestTableRows(void) {
+  hx::Tuning t;
+  hx::load_default_table(&t);
+  return t.rows ? int(t.rows->size()) : 0;
+}
+
+hxcclResult_t hxcclTestChooseVariant(size_t bytes, hxcclDataType_t dt, int nranks, int exact, int nvls,
+                                     int* variant, int* from_table, size_t shape[3]) {
+  using namespace hx;
+  if (nranks < 2 || nranks > kMaxRanks || !variant || dtype_size(dt) == 0) return hxcclInvalidArgument;
+  Tuning t;
+  load_default_table(&t);
+  if (const char* path = std::getenv("HXCCL_TUNE_FILE")) {
+    std::string bad_line;
+    if (!load_tune_file(&t, path, &bad_line)) return hxcclInvalidArgument;
+  }
+  t.exact = exact != 0;
+  t.nvls = nvls != 0;
+  OpPlan plan;
+  plan.base = hxcclSum;
+  const TuneRow* row = nullptr;
+  *variant = choose_variant(bytes, dt, plan, nranks, t, kVarAuto, &row);
+  if (from_table) *from_table = row ? 1 : 0;
+  if (row && (row->variant == kVarTwoShotRoles || row->variant == kVarNvlsRoles)) *variant = row->variant;
+  if (shape) {
+    const Tuning used = with_row(t, row, *variant);
+    shape[0] = size_t(used.max_ctas);
+    shape[1] = size_t(used.threads);
+    shape[2] = *variant == kVarRing ? used.ring_sub : used.sub_max;
+  }
+  return hxcclSuccess;
 }
 
 }  // extern "C"

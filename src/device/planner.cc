@@ -4,6 +4,7 @@
 #include <cstdio>
 #include <cstring>
 #include <fstream>
+#include <sstream>
 #include <string>
 
 #include "device/nvls_modes.h"
@@ -72,10 +73,138 @@ bool set_knob(Tuning* t, const char* name, long v) {
   else if (k == "ll_max") t->ll_max = size_t(std::max(0L, v));
   else if (k == "ll_mc") t->ll_mc = v != 0;
   else if (k == "rs_ring_min") t->rs_ring_min = size_t(std::max(0L, v));
+  else if (k == "table") t->use_table = v != 0;
+  else if (k == "mc_force") t->mc_force = v < 0 ? -1 : (v != 0);
   else if (k == "mc_copy") t->mc_copy = v != 0;
   else if (k == "mc_copy_min") t->mc_copy_min = size_t(std::max(0L, v));
   else return false;
   return true;
+}
+
+namespace {
+const char* const kDefaultTable =
+#include "device/tune_default.inc"
+    ;
+const char* const kCollNames[] = {"allreduce", "allgather", "reducescatter", "broadcast"};
+const char* const kVariantNames[] = {"auto", "oneshot", "twoshot", "nvls", "twoshot_roles", "nvls_roles", "ring", "lines"};
+}  // namespace
+
+bool parse_row(const std::string& line, TuneRow* row, std::string* why) {
+  std::istringstream in(line);
+  std::string word;
+  in >> word;  // "row"
+  if (!(in >> word)) {
+    *why = "row without a collective";
+    return false;
+  }
+  *row = TuneRow{};
+  row->coll = -1;
+  for (int c = 0; c < 4; ++c)
+    if (word == kCollNames[c]) row->coll = c;
+  if (row->coll < 0) {
+    *why = "unknown collective '" + word + "' in a table row";
+    return false;
+  }
+  bool have_n = false, have_variant = false;
+  while (in >> word) {
+    const size_t eq = word.find('=');
+    if (eq == std::string::npos) {
+      *why = "table row field '" + word + "' is not key=value";
+      return false;
+    }
+    const std::string key = word.substr(0, eq), val = word.substr(eq + 1);
+    char* end = nullptr;
+    const long long num = std::strtoll(val.c_str(), &end, 10);
+    const bool numeric = !val.empty() && *end == 0;
+    if (key == "mode") {
+      if (val != "exact" && val != "fast" && val != "any") {
+        *why = "table row mode '" + val + "'";
+        return false;
+      }
+      row->exact = val == "exact" ? 1 : (val == "fast" ? 0 : -1);
+      continue;
+    }
+    if (key == "variant") {
+      have_variant = true;
+      if (numeric) {
+        row->variant = int(num);
+        continue;
+      }
+      row->variant = -1;
+      for (int v = 0; v < 8; ++v)
+        if (val == kVariantNames[v]) row->variant = v;
+      if (val == "multicast" || val == "ring_rs") row->variant = 1;
+      if (val == "unicast" || val == "push") row->variant = 0;
+      if (row->variant < 0) {
+        *why = "unknown variant '" + val + "' in a table row";
+        return false;
+      }
+      continue;
+    }
+    if (!numeric || num < 0) {
+      *why = "table row field '" + word + "' needs a non-negative number";
+      return false;
+    }
+    if (key == "n") row->n = int(num), have_n = true;
+    else if (key == "es") row->es = int(num);
+    else if (key == "from") row->from = size_t(num);
+    else if (key == "ctas") row->ctas = int(std::min<long long>(num, kMaxCtas));
+    else if (key == "threads") row->threads = (num == 256 || num == 512) ? int(num) : 0;
+    else if (key == "sub") row->sub = size_t(num) / 16 * 16;
+    else {
+      *why = "unknown table row field '" + key + "'";
+      return false;
+    }
+  }
+  if (!have_n || !have_variant || row->n < 2 || row->n > kMaxRanks) {
+    *why = "a table row needs n=<2..16> and variant=";
+    return false;
+  }
+  return true;
+}
+
+void load_default_table(Tuning* t) {
+  std::istringstream in(kDefaultTable);
+  std::string line, why;
+  while (std::getline(in, line)) {
+    const size_t hash = line.find('#');
+    if (hash != std::string::npos) line.erase(hash);
+    if (line.find("row") == std::string::npos) continue;
+    TuneRow row;
+    if (parse_row(line, &row, &why)) {
+      if (!t->rows) t->rows = std::make_shared<std::vector<TuneRow>>();
+      t->rows->push_back(row);
+    }
+  }
+}
+
+const TuneRow* find_row(const Tuning& t, int coll, int n, int es, bool exact, size_t bytes) {
+  if (!t.use_table || !t.rows) return nullptr;
+  int best_n = 0;  // the tabled rank count that serves n
+  for (const TuneRow& r : *t.rows)
+    if (r.coll == coll && r.n <= n && r.n > best_n) best_n = r.n;
+  const TuneRow* best = nullptr;
+  for (const TuneRow& r : *t.rows) {
+    if (r.coll != coll || r.n != best_n || r.from > bytes) continue;
+    if (r.es != 0 && r.es != es) continue;
+    if (r.exact >= 0 && r.exact != (exact ? 1 : 0)) continue;
+    // later criteria break ties of earlier ones: exact element size, then the largest `from`
+    if (!best || (r.es != 0) > (best->es != 0) || ((r.es != 0) == (best->es != 0) && r.from >= best->from)) best = &r;
+  }
+  return best;
+}
+
+Tuning with_row(const Tuning& t, const TuneRow* row, int variant) {
+  Tuning out = t;
+  if (!row) return out;
+  if (row->ctas > 0) out.max_ctas = std::min(row->ctas, kMaxCtas);
+  if (row->threads) out.threads = row->threads;
+  if (row->sub >= 16) {
+    if (variant == kVarRing) out.ring_sub = row->sub;
+    else if (variant == kVarTwoShotRoles || variant == kVarNvlsRoles) out.roles_sub = row->sub;
+    else out.sub_max = row->sub;
+  }
+  return out;
 }
 
 bool load_tune_file(Tuning* t, const char* path, std::string* why) {
@@ -85,9 +214,25 @@ bool load_tune_file(Tuning* t, const char* path, std::string* why) {
     return false;
   }
   std::string line;
+  bool own_rows = false;
   while (std::getline(in, line)) {
     const size_t hash = line.find('#');
     if (hash != std::string::npos) line.erase(hash);
+    {
+      std::istringstream first(line);
+      std::string word;
+      if ((first >> word) && word == "row") {
+        TuneRow row;
+        if (!parse_row(line, &row, why)) {
+          *why = "HXCCL_TUNE_FILE: " + *why;
+          return false;
+        }
+        if (!own_rows) t->rows = std::make_shared<std::vector<TuneRow>>();  // replaces the compiled-in table
+        own_rows = true;
+        t->rows->push_back(row);
+        continue;
+      }
+    }
     for (char& ch : line)
       if (ch == '=' || ch == '\t' || ch == '\r') ch = ' ';
     char name[64];
@@ -102,9 +247,19 @@ bool load_tune_file(Tuning* t, const char* path, std::string* why) {
   return true;
 }
 
+namespace {
+// Every CTA of a collective launch waits for the same CTA of its peers, so a grid must be
+// co-resident: one 512-thread CTA per SM, two of 256 threads. Only a fixed width of 256 can
+// count on the second.
+int grid_cap(const Tuning& t) {
+  const int resident = (t.threads == 256 ? 2 : 1) * std::max(1, t.sm_count);
+  return std::max(1, std::min(std::min(t.max_ctas, kMaxCtas), resident));
+}
+}  // namespace
+
 Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t, size_t cta_bytes) {
   Geometry g;
-  const int cap = std::max(1, std::min(t.max_ctas, kMaxCtas));
+  const int cap = grid_cap(t);
   g.ctas = int(std::min<size_t>(cap, std::max<size_t>(1, ceil_div(max_pair, std::max<size_t>(256, cta_bytes)))));
   const size_t fit1 = round_down(round_down(buffer_bytes(half_bytes, 1) / n, 256) / g.ctas, 16);
   const size_t fitr = round_down(round_down(buffer_bytes(half_bytes, 2) / n, 256) / g.ctas, 16);
@@ -116,7 +271,7 @@ Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t, s
 
 Geometry plan_sliced(size_t bytes, int n, size_t half_bytes, const Tuning& t) {
   Geometry g;
-  const int cap = std::max(1, std::min(t.max_ctas, kMaxCtas));
+  const int cap = grid_cap(t);
   g.ctas = int(std::min<size_t>(cap, std::max<size_t>(1, ceil_div(bytes, size_t(n) * 16 * 1024))));
   // a buffer holds the phase A slots in its first half and the phase B slots in its second
   const size_t fit1 = round_down(round_down(buffer_bytes(half_bytes, 1) / 2, 256) / n / g.ctas, 16);
@@ -148,7 +303,7 @@ Geometry plan_roles(size_t bytes, int n, size_t half_bytes, const Tuning& t) {
 
 Geometry plan_ring(size_t max_block, int n, size_t half_bytes, const Tuning& t, bool rs) {
   Geometry g;
-  const int cap = std::max(1, std::min(t.max_ctas, kMaxCtas));
+  const int cap = grid_cap(t);
   g.ctas = int(std::min<size_t>(cap, std::max<size_t>(1, ceil_div(max_block, 16 * 1024))));
   // the staging area holds one slot per hop (2n - 2) and CTA
   const size_t hops = size_t(2 * n - 2);
@@ -204,7 +359,9 @@ FoldSpec make_fold(const OpPlan& plan, int kind) {
   return f;
 }
 
-int choose_variant(size_t bytes, int dt, const OpPlan& plan, int n, const Tuning& t, int forced) {
+int choose_variant(size_t bytes, int dt, const OpPlan& plan, int n, const Tuning& t, int forced,
+                   const TuneRow** row_out) {
+  if (row_out) *row_out = nullptr;
   const bool nvls_ok = t.nvls && bytes % 16 == 0 && bytes > 0 &&
                        nvls_mode(dt, plan.base) != kNvNone && (is_integer(dt) || !t.exact);
   if (forced == kVarNvls && nvls_ok) return kVarNvls;
@@ -212,6 +369,19 @@ int choose_variant(size_t bytes, int dt, const OpPlan& plan, int n, const Tuning
   const bool ll_ok = bytes > 0 && bytes <= ll_max_payload(n) && n >= 2;
   if (forced == kVarLL && ll_ok) return kVarLL;
   if (forced == kVarRing && n >= 2 && bytes > 0) return kVarRing;
+  if (forced == kVarAuto && bytes > 0) {  // the measured table first, where it has an answer that can run
+    if (const TuneRow* r = find_row(t, kCollAllReduce, n, int(dtype_size(dt)), t.exact, bytes)) {
+      int v = r->variant;
+      if (v == kVarTwoShotRoles) v = kVarTwoShot;  // the role pipeline is the planner's choice by size
+      if (v == kVarNvlsRoles) v = kVarNvls;
+      const bool can = (v == kVarLL && ll_ok) || v == kVarOneShot || v == kVarTwoShot || (v == kVarRing && n >= 2) ||
+                       (v == kVarNvls && nvls_ok);
+      if (can) {
+        if (row_out) *row_out = r;
+        return v;
+      }
+    }
+  }
   // with two ranks the multicast reduction measured slower than two-shot at every size
   if (nvls_ok && bytes >= t.nvls_min && n > 2) return kVarNvls;
   if (t.ring_min && bytes >= t.ring_min && n >= 2 && n <= t.ring_max_ranks) return kVarRing;

@@ -5,7 +5,9 @@
 #pragma once
 #include <cstddef>
 #include <cstdint>
+#include <memory>
 #include <string>
+#include <vector>
 
 #include "core/devpath.h"
 #include "core/schedule.h"
@@ -24,6 +26,22 @@ struct Geometry {
 // AllReduce transport variants
 enum : int { kVarAuto = 0, kVarOneShot = 1, kVarTwoShot = 2, kVarNvls = 3, kVarTwoShotRoles = 4, kVarNvlsRoles = 5,
        kVarRing = 6, kVarLL = 7 };
+
+// One row of the measured tuning table: for collective `coll` on `n` ranks with elements of
+// `es` bytes (0 = any) in exact / fast mode (-1 = either), messages of at least `from` bytes
+// take `variant`, launched with the given grid limit, CTA width and per-step share (0 = the
+// planner's own choice). The row with the largest `from` not above the message wins. Rows come
+// from bench/sweep.py --emit-tune (the compiled-in default, src/device/tune_default.inc, was
+// produced that way on 8 x B200) or from HXCCL_TUNE_FILE. `bytes` is the message size for
+// AllReduce and Broadcast and the per-rank block for AllGather and ReduceScatter.
+enum : int { kCollAllReduce = 0, kCollAllGather = 1, kCollReduceScatter = 2, kCollBroadcast = 3 };
+struct TuneRow {
+  int coll = 0, n = 0, es = 0, exact = -1;
+  size_t from = 0;
+  int variant = 0;  // AllReduce: kVar*; AllGather / Broadcast: 1 = multicast push; ReduceScatter: 1 = ring
+  int ctas = 0, threads = 0;
+  size_t sub = 0;
+};
 
 struct Tuning {
   int max_ctas = 128;         // upper bound of any collective grid
@@ -47,17 +65,33 @@ struct Tuning {
   size_t ll_max = 16 * 1024;          // AllReduce: up to here the flag-in-data kernel (0 = never)
   bool ll_mc = true;                  // ... its lines go out through the multicast alias when there is one
   size_t rs_ring_min = 256u << 20;    // ReduceScatter: neighbour ring from this many input bytes (0 = never)
+  // the measured table (shared, so that copying a Tuning per call stays cheap); null or empty =
+  // the thresholds above only
+  std::shared_ptr<std::vector<TuneRow>> rows;
+  bool use_table = true;              // "table 0" (or HXCCL_TUNE_TABLE=0) ignores the rows
+  int mc_force = -1;                  // AllGather / Broadcast multicast push: 1 always, 0 never, -1 table / default
   bool mc_copy = true;                // AllGather / Broadcast push through the multicast alias
   size_t mc_copy_min = 0;             // ... from this many bytes per block
 };
 
+// The row that applies, or null. n matches exactly or falls back to the largest tabled rank
+// count below it; an exact element size beats es = 0.
+const TuneRow* find_row(const Tuning& t, int coll, int n, int es, bool exact, size_t bytes);
+// Appends the rows of the compiled-in default table.
+void load_default_table(Tuning* t);
+// Parses one "row ..." line (see load_tune_file); false with *why set when malformed.
+bool parse_row(const std::string& line, TuneRow* row, std::string* why);
+
 // Sets one tuning knob by name ("max_ctas", "oneshot_max", "nvls_min", "single_sub_max",
 // "sub_max", "min_steps", "threads", "roles_min", "roles_sub", "ring_min", "ring_max_ranks", "ring_sub", "p2p_threads",
-// "exact", "nvls_gather", "mc_copy", "mc_copy_min", "rs_ring_min", "ll_max", "ll_mc");
+// "exact", "nvls_gather", "table", "mc_force", "mc_copy", "mc_copy_min", "rs_ring_min", "ll_max", "ll_mc");
 // false for an unknown name.
 bool set_knob(Tuning* t, const char* name, long value);
-// Applies a file of knob settings (HXCCL_TUNE_FILE): one "name value" or "name=value" per line,
-// '#' starts a comment. False, with the reason in *why, for an unreadable file or a bad line.
+// Applies a tuning file (HXCCL_TUNE_FILE): knob lines "name value" or "name=value", and table
+// rows "row <allreduce|allgather|reducescatter|broadcast> n=<ranks> [es=<bytes>] [mode=exact|fast]
+// from=<bytes> variant=<name|number> [ctas=<c>] [threads=<256|512>] [sub=<bytes>]"; the first
+// row line of a file replaces the compiled-in table. '#' starts a comment. False, with the
+// reason in *why, for an unreadable file or a bad line.
 bool load_tune_file(Tuning* t, const char* path, std::string* why);
 
 // generic exchange where the largest block of any pair is `max_pair` bytes
@@ -81,8 +115,11 @@ std::string check_geometry(int kind, const Geometry& g, size_t amount, int n, si
 
 FoldSpec make_fold(const OpPlan& plan, int kind);
 
-// which variant an AllReduce takes
-int choose_variant(size_t bytes, int dt, const OpPlan& plan, int n, const Tuning& t, int forced);
+// which variant an AllReduce takes; *row (when given) receives the table row behind the choice
+int choose_variant(size_t bytes, int dt, const OpPlan& plan, int n, const Tuning& t, int forced,
+                   const TuneRow** row = nullptr);
+// `t` with a row's grid limit, CTA width and per-step share applied
+Tuning with_row(const Tuning& t, const TuneRow* row, int variant);
 
 void build_allreduce_oneshot(XchgArgs* a, const WinView& w, uint64_t epoch, const Geometry& g,
                              const void* send, void* recv, size_t count, int dt,

@@ -87,6 +87,8 @@ hxcclResult_t WindowPath::setup_local() {
   if (cudaEventCreateWithFlags(&order_event_, cudaEventDisableTiming) != cudaSuccess)
     return fail(hxcclUnhandledCudaError, "cannot create an event");
   Tuning& t = eng_.tune;
+  load_default_table(&t);
+  t.use_table = env_long("HXCCL_TUNE_TABLE", 1) != 0;
   t.max_ctas = int(std::max(1L, std::min<long>(env_long("HXCCL_MAX_CTAS", t.max_ctas), kMaxCtas)));
   t.threads = int(env_long("HXCCL_THREADS", 0));
   if (t.threads != 256 && t.threads != 512) t.threads = 0;
@@ -116,7 +118,12 @@ hxcclResult_t WindowPath::setup_local() {
     if (!std::strcmp(v, "twoshot")) eng_.forced_variant = kVarTwoShot;
     if (!std::strcmp(v, "nvls")) eng_.forced_variant = kVarNvls;
     if (!std::strcmp(v, "ring")) eng_.forced_variant = kVarRing;
+    if (!std::strcmp(v, "lines")) eng_.forced_variant = kVarLL;
   }
+  t.ll_max = size_t(std::max(0L, env_long("HXCCL_LL_MAX", long(t.ll_max))));
+  t.ll_mc = env_long("HXCCL_LL_MC", 1) != 0;
+  t.mc_copy = env_long("HXCCL_MC_COPY", 1) != 0;
+  t.rs_ring_min = size_t(std::max(0L, env_long("HXCCL_RS_RING_MIN", long(t.rs_ring_min))));
   return hxcclSuccess;
 }
 

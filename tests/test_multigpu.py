@@ -131,6 +131,197 @@ def test_allreduce_nvls(n):
         assert res[r][1]["i32avg"][1] == 3 and np.array_equal(res[r][1]["i32avg"][0], want)
 
 
+def _pipelines_body(comm, rank, n, cases):
+    """The large-message role pipelines forced onto small messages: exact two-shot whose results
+    go out with multimem.st (variant 4 on a multicast window), and the in-switch reduction
+    (variant 5)."""
+    import torch
+
+    info = comm.device_info()
+    comm.knob("roles_min", 1)
+    comm.knob("roles_sub", 8192)
+    comm.knob("roles_min_ranks", 2)
+    comm.knob("nvls_min", 1)
+    outs = []
+    for (dt, op, count, exact, seed) in cases:
+        comm.tune(variant=0 if not exact else 2, exact=bool(exact))
+        x = torch.from_numpy(inputs_for(n, count, dt, seed, tame=True)[rank].view(np.uint8).copy()).cuda()
+        y = torch.zeros_like(x)
+        comm.all_reduce(x, y, op=op, count=count, dtype=dt)
+        comm.all_reduce(x, x, op=op, count=count, dtype=dt)  # in place, the ring buffers in their next cycle
+        torch.cuda.synchronize()
+        outs.append((y.cpu().numpy(), x.cpu().numpy(), comm.device_info()["variant"]))
+    return info, outs, comm.async_error()
+
+
+@needs2
+@pytest.mark.parametrize("n", WORLDS)
+def test_allreduce_role_pipelines_with_multicast(n):
+    import torch
+
+    cases = []
+    for dt, op in ((L.FLOAT32, L.SUM), (L.BFLOAT16, L.AVG), (L.INT32, L.AVG), (L.FLOAT8E4M3, L.SUM), (L.INT64, L.MAX)):
+        es = L.DTYPE_SIZE[dt]
+        for count in ((3 << 20) // es + 16 // es * 3, (1 << 20) // es):
+            cases.append((dt, op, count, 1, len(cases)))            # exact: variant 4
+            if dt in (L.INT32, L.INT64):
+                cases.append((dt, op, count, 0, len(cases)))        # integers: the switch is exact too
+    cases.append((L.FLOAT32, L.SUM, 1 << 20, 0, 77))               # floats through the switch: tolerance
+    cases.append((L.BFLOAT16, L.SUM, 1 << 20, 0, 78))
+    res = run_ranks(n, _pipelines_body, cases, gpus=True, timeout=180, nvls=True)
+    nvls = "nvls" in res[0][0]["kind"]
+    for k, (dt, op, count, exact, seed) in enumerate(cases):
+        xs = inputs_for(n, count, dt, seed, tame=True)
+        for r in range(n):
+            y, x, variant = res[r][1][k]
+            if exact or dt <= L.UINT64:
+                want = oracle.allreduce(xs, dt, op, order=0)
+                assert np.array_equal(y.view(oracle.raw_dtype(dt)), want[r]), (n, dt, op, count, exact, r, variant)
+                assert np.array_equal(x.view(oracle.raw_dtype(dt)), want[r]), ("in place", n, dt, op, count, exact, r, variant)
+            else:
+                tdt = {L.FLOAT32: torch.float32, L.BFLOAT16: torch.bfloat16}[dt]
+                ref = sum(torch.from_numpy(v.copy()).view(tdt).double() for v in xs)
+                got = torch.from_numpy(y.copy()).view(tdt).double()
+                scale = float(ref.abs().max()) + 1.0
+                assert float((got - ref).abs().max()) <= scale * (1e-5 if dt == L.FLOAT32 else 3e-2) * n
+            if n > 2 or exact:
+                assert variant == (4 if exact else (5 if nvls else 4)), (variant, exact, nvls)
+    assert all(r[2] == 0 for r in res)
+
+
+def _multicast_copy_body(comm, rank, n):
+    """AllGather and Broadcast whose pushes go through the multicast alias, sizes from below one
+    vector (peer stores only) over odd tails to several pipelined steps; the lines of the small
+    AllReduce through the alias too."""
+    import torch
+
+    out = {"kind": comm.device_info()["kind"], "ag": [], "bc": [], "ll": []}
+    for nb in (8, 16, 1000, 65536 + 24, (5 << 20) + 7):
+        x = torch.from_numpy(np.random.default_rng(100 + rank).integers(0, 256, nb, dtype=np.uint8)).cuda()
+        ag = torch.zeros(nb * n, dtype=torch.uint8, device="cuda")
+        comm.all_gather(x, ag)
+        inplace = torch.zeros(nb * n, dtype=torch.uint8, device="cuda")
+        inplace[rank * nb:(rank + 1) * nb] = x
+        comm.all_gather(inplace[rank * nb:(rank + 1) * nb], inplace)
+        for root in (0, n - 1):
+            b = x.clone()
+            comm.bcast(b, root=root)
+            o = torch.zeros_like(x)
+            comm.broadcast(x, o, root=root)
+            torch.cuda.synchronize()
+            want = np.random.default_rng(100 + root).integers(0, 256, nb, dtype=np.uint8)
+            out["bc"].append(bool((b.cpu().numpy() == want).all() and (o.cpu().numpy() == want).all()))
+        torch.cuda.synchronize()
+        want = np.concatenate([np.random.default_rng(100 + r).integers(0, 256, nb, dtype=np.uint8) for r in range(n)])
+        out["ag"].append(bool((ag.cpu().numpy() == want).all() and (inplace.cpu().numpy() == want).all()))
+    for dt, op, count in ((L.FLOAT32, L.SUM, 1), (L.FLOAT32, L.SUM, 2049), (L.BFLOAT16, L.AVG, 777), (L.INT64, L.MIN, 5),
+                          (L.FLOAT8E5M2, L.SUM, 4001)):
+        xs = inputs_for(n, count, dt, 900 + count)
+        x = torch.from_numpy(xs[rank].view(np.uint8).copy()).cuda()
+        for _ in range(3):  # both halves of the line region, and one reuse
+            y = torch.zeros_like(x)
+            comm.all_reduce(x, y, op=op, count=count, dtype=dt)
+        torch.cuda.synchronize()
+        out["ll"].append((y.cpu().numpy(), comm.device_info()["variant"]))
+    out["err"] = comm.async_error()
+    return out
+
+
+@needs2
+@pytest.mark.parametrize("n", WORLDS)
+@pytest.mark.parametrize("multicast", [True, False])
+def test_multicast_allgather_broadcast_and_lines(n, multicast):
+    res = run_ranks(n, _multicast_copy_body, gpus=True, timeout=180, nvls=multicast)
+    if multicast and "nvls" not in res[0]["kind"]:
+        pytest.skip("no NVSwitch multicast on this node: " + res[0]["kind"])
+    cases = ((L.FLOAT32, L.SUM, 1), (L.FLOAT32, L.SUM, 2049), (L.BFLOAT16, L.AVG, 777), (L.INT64, L.MIN, 5),
+             (L.FLOAT8E5M2, L.SUM, 4001))
+    for r in range(n):
+        assert all(res[r]["ag"]) and all(res[r]["bc"]) and res[r]["err"] == 0, (r, res[r]["ag"], res[r]["bc"], res[r]["err"])
+        for k, (dt, op, count) in enumerate(cases):
+            want = oracle.allreduce(inputs_for(n, count, dt, 900 + count), dt, op)
+            got, variant = res[r]["ll"][k]
+            assert variant == 7 and np.array_equal(got.view(oracle.raw_dtype(dt)), want[r]), (n, dt, op, count, r, variant)
+
+
+def _cast_and_ring_rs_body(comm, rank, n):
+    import torch
+
+    out = {}
+    count = (3 << 20) // 2 + 5
+    g = torch.Generator().manual_seed(4242 + rank)
+    x = (torch.randn(count, generator=g) * 3).float().cuda()
+    y = torch.zeros_like(x)
+    comm.all_reduce_cast(x, y, wire_dtype=L.BFLOAT16, op=L.AVG)
+    torch.cuda.synchronize()
+    out["cast"] = y.cpu().numpy()  # numpy, not a tensor: a tensor's storage would travel by file descriptor
+    out["cast_small"] = comm.all_reduce_cast(x[:100], y[:100], wire_dtype=L.BFLOAT16, op=L.AVG, check=False)
+    comm.knob("rs_ring_min", 1)
+    per = 300001
+    xs = inputs_for(n, per * n, L.FLOAT32, 31, tame=True)
+    s = torch.from_numpy(xs[rank].view(np.uint8).copy()).cuda()
+    r_out = torch.zeros(per * 4, dtype=torch.uint8, device="cuda")
+    comm.reduce_scatter(s, r_out, op=L.SUM, count=per, dtype=L.FLOAT32)
+    torch.cuda.synchronize()
+    out["rs"] = r_out.cpu().numpy().view(np.uint32)
+    out["err"] = comm.async_error()
+    return out
+
+
+@needs2
+@pytest.mark.parametrize("n", WORLDS)
+def test_fused_cast_allreduce_and_ring_reducescatter(n):
+    import torch
+
+    res = run_ranks(n, _cast_and_ring_rs_body, gpus=True, timeout=180)
+    count = (3 << 20) // 2 + 5
+    narrow = [(torch.randn(count, generator=torch.Generator().manual_seed(4242 + r)) * 3).float().to(torch.bfloat16)
+              .view(torch.uint16).numpy().copy() for r in range(n)]
+    want = oracle.allreduce(narrow, L.BFLOAT16, L.AVG, order=0)
+    want_rs = oracle.reducescatter(inputs_for(n, 300001 * n, L.FLOAT32, 31, tame=True), L.FLOAT32, L.SUM)
+    for r in range(n):
+        w32 = torch.from_numpy(want[r].copy()).view(torch.bfloat16).float()
+        assert np.array_equal(res[r]["cast"].view(np.uint32), w32.numpy().view(np.uint32)), r
+        assert res[r]["cast_small"] == L.INVALID_USAGE and res[r]["err"] == 0
+        assert np.array_equal(res[r]["rs"], want_rs[r]), r
+
+
+def _crossed_group_body(comm, rank, n):
+    """One group over two communicators whose calls name them in opposite order on the two ranks
+    (the crossed form of the reference's tests/repro_two_comm_group.cc), with messages far beyond
+    what the slot rings hold and several operations per lane: completes only when every rank
+    launches the communicators' kernels in the same order."""
+    import torch
+    import hxccl_b200 as hx
+
+    other = comm.split(0, rank)
+    nb = 40 << 20
+    peer = 1 - rank
+    src = [torch.full((nb,), 10 * rank + k, dtype=torch.uint8, device="cuda") for k in range(3)]
+    dst = [torch.zeros(nb, dtype=torch.uint8, device="cuda") for _ in range(3)]
+    first, second = (comm, other) if rank == 0 else (other, comm)
+    hx.group_start()
+    for k in range(3):
+        first.send(src[k], peer)
+    for k in range(3):
+        second.recv(dst[k], peer)
+    rc = hx.group_end()
+    torch.cuda.synchronize()
+    got = [(int(d[0]), int(d[-1])) for d in dst]
+    errs = (comm.async_error(), other.async_error())
+    other.destroy()
+    return rc, got, errs
+
+
+@needs2
+def test_crossed_group_over_two_communicators_with_large_messages():
+    res = run_ranks(2, _crossed_group_body, gpus=True, timeout=120)
+    for rank, (rc, got, errs) in enumerate(res):
+        peer = 1 - rank
+        assert rc == 0 and errs == (0, 0), (rank, rc, errs)
+        assert got == [(10 * peer + k, 10 * peer + k) for k in range(3)], (rank, got)
+
+
 def _collectives_body(comm, rank, n):
     import torch
     import hxccl_b200 as hx

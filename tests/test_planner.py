@@ -8,7 +8,7 @@ import pytest
 
 from hxccl_b200 import _lib as L
 
-KINDS = {"xchg": 0, "sliced": 1, "roles": 2, "ring": 3}
+KINDS = {"xchg": 0, "sliced": 1, "roles": 2, "ring": 3, "ring_rs": 4}
 
 
 def plan(kind, amount, n, half, max_ctas=0, knob=None, value=0):
@@ -28,7 +28,7 @@ SIZES = [1, 15, 16, 17, 4099, 65536, 262144, 262145, (1 << 20) + 16, 3 << 20, (6
 def test_every_plan_fits_its_window(kind):
     bad = []
     for n in (1, 2, 3, 4, 8, 16):
-        if kind == "ring" and n < 2:
+        if kind in ("ring", "ring_rs") and n < 2:
             continue
         for half in (3 << 20, 61 << 20, 253 << 20):
             for max_ctas in (0, 1, 8, 48, 512):
@@ -77,3 +77,61 @@ def test_tune_file(tmp_path, monkeypatch):
     assert rc == L.INVALID_ARGUMENT and "no_such_knob" in why
     monkeypatch.setenv("HXCCL_TUNE_FILE", str(tmp_path / "missing.txt"))
     assert plan("sliced", 1 << 20, 2, 253 << 20)[0] == L.INVALID_ARGUMENT
+
+
+def choose(nbytes, dt, n, exact=1, nvls=1):
+    lib = L.lib()
+    lib.hxcclTestChooseVariant.argtypes = [C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int),
+                                           C.POINTER(C.c_int), C.POINTER(C.c_size_t)]
+    v, tab = C.c_int(), C.c_int()
+    shape = (C.c_size_t * 3)()
+    rc = lib.hxcclTestChooseVariant(nbytes, dt, n, exact, nvls, C.byref(v), C.byref(tab), shape)
+    return rc, v.value, bool(tab.value), list(shape)
+
+
+def test_tuning_table_rows_decide_the_variant(tmp_path, monkeypatch):
+    """A table row picks the AllReduce variant and its launch shape for its size range, rank
+    count, element size and mode; outside the rows the fixed thresholds hold; a row that cannot
+    run (multicast reduction without multicast) is skipped."""
+    table = tmp_path / "table.tune"
+    table.write_text(
+        "# measured elsewhere\n"
+        "row allreduce n=8 mode=exact from=0 variant=lines\n"
+        "row allreduce n=8 mode=exact from=4096 variant=oneshot\n"
+        "row allreduce n=8 mode=exact from=1048576 variant=twoshot ctas=64 sub=65536\n"
+        "row allreduce n=8 es=2 mode=exact from=1048576 variant=ring ctas=200 threads=256 sub=131072\n"
+        "row allreduce n=8 mode=exact from=268435456 variant=twoshot_roles\n"
+        "row allreduce n=8 mode=fast from=65536 variant=nvls\n"
+        "row allreduce n=4 from=0 variant=twoshot\n"
+        "max_ctas 96\n")
+    monkeypatch.setenv("HXCCL_TUNE_FILE", str(table))
+    assert choose(8, L.FLOAT32, 8)[1:3] == (7, True)
+    assert choose(8192, L.FLOAT32, 8)[1:3] == (1, True)
+    rc, v, tab, shape = choose(4 << 20, L.FLOAT32, 8)
+    assert (rc, v, tab, shape) == (0, 2, True, [64, 0, 65536])
+    rc, v, tab, shape = choose(4 << 20, L.BFLOAT16, 8)          # the row for 2-byte elements wins
+    assert (v, tab, shape) == (6, True, [200, 256, 131072])
+    assert choose(1 << 30, L.FLOAT32, 8)[1:3] == (4, True)
+    assert choose(1 << 20, L.FLOAT32, 8, exact=0)[1:3] == (3, True)
+    assert choose(1 << 20, L.FLOAT32, 8, exact=0, nvls=0)[2] is False  # cannot run: thresholds decide
+    assert choose(100, L.FLOAT32, 5)[1:3] == (2, True)           # five ranks use the rows of four
+    assert choose(100, L.FLOAT32, 2)[2] is False                 # nothing tabled for two ranks
+    assert choose(100, L.FLOAT32, 2)[1] == 7 and choose(1 << 20, L.FLOAT32, 2)[1] == 2
+    bad = tmp_path / "bad.tune"
+    bad.write_text("row allreduce n=8 from=0 variant=warp_drive\n")
+    monkeypatch.setenv("HXCCL_TUNE_FILE", str(bad))
+    assert choose(8, L.FLOAT32, 8)[0] == L.INVALID_ARGUMENT
+
+
+def test_compiled_in_table_parses():
+    """Every row of the compiled-in table is well formed: the source text and what the library
+    loaded agree on the number of rows."""
+    import re
+    from pathlib import Path
+
+    text = (Path(__file__).resolve().parent.parent / "src" / "device" / "tune_default.inc").read_text()
+    body = text[text.index('R"TUNE(') + 7:text.index(')TUNE"')]
+    rows = [ln for ln in body.splitlines() if re.match(r"\s*row\b", ln.split("#")[0])]
+    lib = L.lib()
+    lib.hxcclTestTableRows.restype = C.c_int
+    assert lib.hxcclTestTableRows() == len(rows)

@@ -61,6 +61,13 @@ def _worker(rank, world, port, q):
             t = torch.zeros(1, device=dev)
             dist.recv(t, src=0)
             assert t.item() == 42.0
+        # fp32 bucket with bfloat16 on the wire: the one-kernel form against the casts done here
+        g32 = torch.randn(300007, device=dev, generator=torch.Generator(device=dev).manual_seed(9 + rank))
+        two_pass = g32.to(torch.bfloat16)
+        dist.all_reduce(two_pass, op=dist.ReduceOp.AVG)
+        fused = g32.clone()
+        hp.all_reduce_cast(fused, bf16=True, average=True).wait()
+        assert torch.equal(fused.view(torch.int32), two_pass.float().view(torch.int32))
         dist.barrier()
         # DDP: two steps with the fused-average hook; gradients equal the average of the ranks'
         torch.manual_seed(0)
