@@ -31,7 +31,7 @@ def parse_size(s: str) -> int:
 
 
 DEFAULT_KNOBS = {"max_ctas": 128, "threads": 0, "ring_sub": 512 * 1024, "sub_max": 256 * 1024, "roles_min": 96 << 20,
-                 "roles_min_ranks": 8, "roles_sub": 64 * 1024, "rs_ring_min": 256 << 20, "mc_force": -1}
+                 "roles_min_ranks": 8, "roles_sub": 64 * 1024, "rs_ring_min": 256 << 20, "mc_force": -1, "grain": 16 * 1024}
 
 
 def tune_candidates(coll: str, world: int, nbytes: int):
@@ -43,8 +43,12 @@ def tune_candidates(coll: str, world: int, nbytes: int):
             c.append(("lines", 7, True, {}, {"variant": "lines"}))
         if nbytes <= (2 << 20):
             c.append(("oneshot", 1, True, {}, {"variant": "oneshot"}))
+            if nbytes >= (32 << 10):
+                c.append(("oneshot g4K", 1, True, {"grain": 4096}, {"variant": "oneshot", "grain": 4096}))
         if nbytes >= (16 << 10):
             c.append(("twoshot", 2, True, {"roles_min": 1 << 40}, {"variant": "twoshot"}))
+            if (128 << 10) <= nbytes <= (64 << 20):
+                c.append(("twoshot g4K", 2, True, {"roles_min": 1 << 40, "grain": 4096}, {"variant": "twoshot", "grain": 4096}))
             if nbytes >= (1 << 20):
                 c.append(("twoshot c64", 2, True, {"roles_min": 1 << 40, "max_ctas": 64}, {"variant": "twoshot", "ctas": 64}))
         if nbytes >= (32 << 20) and world > 2:
@@ -61,12 +65,17 @@ def tune_candidates(coll: str, world: int, nbytes: int):
     elif coll in ("allgather", "broadcast"):
         c.append(("unicast", 0, True, {"mc_force": 0}, {"variant": "unicast"}))
         c.append(("multicast", 0, True, {"mc_force": 1}, {"variant": "multicast"}))
+        if (64 << 10) <= nbytes <= (64 << 20):
+            c.append(("unicast g4K", 0, True, {"mc_force": 0, "grain": 4096}, {"variant": "unicast", "grain": 4096}))
+            c.append(("multicast g4K", 0, True, {"mc_force": 1, "grain": 4096}, {"variant": "multicast", "grain": 4096}))
         if nbytes >= (1 << 20):
             c.append(("unicast t256 c256", 0, True, {"mc_force": 0, "threads": 256, "max_ctas": 256},
                       {"variant": "unicast", "threads": 256, "ctas": 256}))
             c.append(("multicast c64", 0, True, {"mc_force": 1, "max_ctas": 64}, {"variant": "multicast", "ctas": 64}))
     elif coll == "reducescatter":
         c.append(("push", 0, True, {"rs_ring_min": 0}, {"variant": "push"}))
+        if (64 << 10) <= nbytes <= (64 << 20):
+            c.append(("push g4K", 0, True, {"rs_ring_min": 0, "grain": 4096}, {"variant": "push", "grain": 4096}))
         if nbytes >= (64 << 10):
             c.append(("ring_rs", 0, True, {"rs_ring_min": 1}, {"variant": "ring_rs"}))
             c.append(("ring_rs t256 c256", 0, True, {"rs_ring_min": 1, "threads": 256, "max_ctas": 256, "ring_sub": 256 << 10},

@@ -22,7 +22,7 @@ from typing import Any, Callable, Dict, List, Optional
 
 
 def _child(rank: int, n: int, fn: Callable, args: tuple, uid_recv, uid_send: List, out, env: Dict[str, str],
-           gpus: bool, make_comm: bool) -> None:
+           gpus: bool, make_comm: bool, one_gpu: bool = False) -> None:
     try:
         import faulthandler  # noqa: PLC0415
 
@@ -39,7 +39,7 @@ def _child(rank: int, n: int, fn: Callable, args: tuple, uid_recv, uid_send: Lis
         if gpus:
             import torch  # noqa: PLC0415
 
-            torch.cuda.set_device(rank % torch.cuda.device_count())
+            torch.cuda.set_device(0 if one_gpu else rank % torch.cuda.device_count())
             torch.cuda.init()
             torch.zeros(1, device="cuda")
         if rank == 0:
@@ -67,10 +67,12 @@ GPU_WAIT_LIMIT_MS = 5000  # default device-side wait limit of ranks started with
 
 def run_ranks(n: int, fn: Callable, *args: Any, env: Optional[Dict[str, str]] = None, gpus: bool = False,
               timeout: float = 120.0, make_comm: bool = True,
-              rank_env: Optional[Dict[int, Dict[str, str]]] = None, nvls: bool = False) -> List[Any]:
+              rank_env: Optional[Dict[int, Dict[str, str]]] = None, nvls: bool = False,
+              one_gpu: bool = False) -> List[Any]:
     """Returns [fn's result on rank 0, ..., on rank n-1]. `fn` must be importable (module level).
     `rank_env[r]` adds environment variables for rank r only. `nvls` leaves NVSwitch multicast
-    on for GPU ranks (default off, see the module text)."""
+    on for GPU ranks (default off, see the module text). `one_gpu` puts every GPU rank on device
+    0 (the ranks then cannot share windows and fall back to the staged path together)."""
     ctx = mp.get_context("spawn")
     env = dict(env or {})
     if gpus:
@@ -90,7 +92,7 @@ def run_ranks(n: int, fn: Callable, *args: Any, env: Optional[Dict[str, str]] = 
         e.update((rank_env or {}).get(r, {}))
         p = ctx.Process(target=_child, args=(r, n, fn, args, uid_pipes[r - 1][0] if r else None,
                                              [w for _, w in uid_pipes] if r == 0 else [], outs[r][1], e,
-                                             gpus, make_comm))
+                                             gpus, make_comm, one_gpu))
         p.start()
         procs.append(p)
     results: List[Any] = [None] * n

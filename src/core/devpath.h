@@ -40,6 +40,9 @@ class DevicePath {
   // failed and every later device call returns the same code.
   virtual hxcclResult_t broken(std::string* why) = 0;
   virtual const char* kind() const = 0;  // "window", "window+nvls" or "staged"
+  // The CUDA device whose memory this path's kernels can address, or -1 when buffers of any
+  // device will do (the staged path copies through the host).
+  virtual int device() const { return -1; }
 
   virtual hxcclResult_t allreduce(const void* send, void* recv, size_t count, int dt,
                                   const OpPlan& plan, int order, void* stream) = 0;
@@ -76,6 +79,8 @@ class DevicePath {
 enum class MemKind { Null, Host, Device };
 // Where `p` lives, asked of the driver without creating a CUDA context.
 MemKind classify(const void* p);
+// CUDA device a device pointer belongs to, or -1 (host memory, unknown).
+int device_ordinal_of(const void* p);
 // True when this process already has a CUDA context (again without creating one).
 bool cuda_context_exists();
 // Collective over the communicator's ranks. Returns null with *rc/*why set on failure.

@@ -107,6 +107,20 @@ hxcclResult_t pick_path(hxcclComm* c, const void* a, const void* b, Path* out) {
     }
   }
   if (c->device.down != hxcclSuccess) return comm_fail(c, c->device.down, c->device.down_why);
+  // The kernels address the memory of the communicator's own GPU (and its peers' windows): a
+  // buffer that lives on another device of this process would fault them.
+  const int home = c->device.path ? c->device.path->device() : -1;
+  if (home >= 0) {
+    const void* const ptrs[2] = {a, b};
+    const MemKind kinds[2] = {ka, kb};
+    for (int k = 0; k < 2; ++k) {
+      const int where = kinds[k] == MemKind::Device ? device_ordinal_of(ptrs[k]) : -1;
+      if (where >= 0 && where != home)
+        return comm_fail(c, hxcclInvalidArgument,
+                         "the buffer lives on CUDA device " + std::to_string(where) +
+                             " but the communicator was created on device " + std::to_string(home));
+    }
+  }
   *out = Path::Device;
   return hxcclSuccess;
 }

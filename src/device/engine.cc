@@ -97,7 +97,7 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
   if (var == kVarOneShot) {
     // the recursive-doubling order costs n log n combines per element: give a CTA less of it
     const Geometry g = plan_xchg(bytes, n(), views[0].half_bytes, tune,
-                                 order == kOrderDoubling ? 2 * 1024 : 16 * 1024);
+                                 order == kOrderDoubling ? std::min<size_t>(2 * 1024, tune.grain) : tune.grain);
     HX_CHECK_PLAN(kPlanXchg, g, bytes);
     std::vector<XchgArgs> args(views.size());
     for (size_t r = 0; r < views.size(); ++r)

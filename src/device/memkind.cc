@@ -24,6 +24,16 @@ MemKind classify(const void* p) {
   return MemKind::Host;  // pinned / registered host memory
 }
 
+int device_ordinal_of(const void* p) {
+  const CuDriver& d = cu();
+  if (!p || !d.ok) return -1;
+  int ordinal = -1;
+  if (d.PointerGetAttribute(&ordinal, CU_POINTER_ATTRIBUTE_DEVICE_ORDINAL, reinterpret_cast<CUdeviceptr>(p)) !=
+      CUDA_SUCCESS)
+    return -1;
+  return ordinal;
+}
+
 bool cuda_context_exists() {
   const CuDriver& d = cu();
   if (!d.ok) return false;

@@ -74,6 +74,7 @@ bool set_knob(Tuning* t, const char* name, long v) {
   else if (k == "ll_mc") t->ll_mc = v != 0;
   else if (k == "rs_ring_min") t->rs_ring_min = size_t(std::max(0L, v));
   else if (k == "table") t->use_table = v != 0;
+  else if (k == "grain") t->grain = size_t(std::max(256L, v));
   else if (k == "mc_force") t->mc_force = v < 0 ? -1 : (v != 0);
   else if (k == "mc_copy") t->mc_copy = v != 0;
   else if (k == "mc_copy_min") t->mc_copy_min = size_t(std::max(0L, v));
@@ -151,6 +152,7 @@ bool parse_row(const std::string& line, TuneRow* row, std::string* why) {
     else if (key == "ctas") row->ctas = int(std::min<long long>(num, kMaxCtas));
     else if (key == "threads") row->threads = (num == 256 || num == 512) ? int(num) : 0;
     else if (key == "sub") row->sub = size_t(num) / 16 * 16;
+    else if (key == "grain") row->grain = size_t(num);
     else {
       *why = "unknown table row field '" + key + "'";
       return false;
@@ -199,6 +201,7 @@ Tuning with_row(const Tuning& t, const TuneRow* row, int variant) {
   if (!row) return out;
   if (row->ctas > 0) out.max_ctas = std::min(row->ctas, kMaxCtas);
   if (row->threads) out.threads = row->threads;
+  if (row->grain >= 256) out.grain = row->grain;
   if (row->sub >= 16) {
     if (variant == kVarRing) out.ring_sub = row->sub;
     else if (variant == kVarTwoShotRoles || variant == kVarNvlsRoles) out.roles_sub = row->sub;
@@ -260,6 +263,7 @@ int grid_cap(const Tuning& t) {
 Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t, size_t cta_bytes) {
   Geometry g;
   const int cap = grid_cap(t);
+  if (cta_bytes == 0) cta_bytes = t.grain;
   g.ctas = int(std::min<size_t>(cap, std::max<size_t>(1, ceil_div(max_pair, std::max<size_t>(256, cta_bytes)))));
   const size_t fit1 = round_down(round_down(buffer_bytes(half_bytes, 1) / n, 256) / g.ctas, 16);
   const size_t fitr = round_down(round_down(buffer_bytes(half_bytes, 2) / n, 256) / g.ctas, 16);
@@ -272,7 +276,7 @@ Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t, s
 Geometry plan_sliced(size_t bytes, int n, size_t half_bytes, const Tuning& t) {
   Geometry g;
   const int cap = grid_cap(t);
-  g.ctas = int(std::min<size_t>(cap, std::max<size_t>(1, ceil_div(bytes, size_t(n) * 16 * 1024))));
+  g.ctas = int(std::min<size_t>(cap, std::max<size_t>(1, ceil_div(bytes, size_t(n) * std::max<size_t>(256, t.grain)))));
   // a buffer holds the phase A slots in its first half and the phase B slots in its second
   const size_t fit1 = round_down(round_down(buffer_bytes(half_bytes, 1) / 2, 256) / n / g.ctas, 16);
   const size_t fitr = round_down(round_down(buffer_bytes(half_bytes, 2) / 2, 256) / n / g.ctas, 16);

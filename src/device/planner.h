@@ -41,6 +41,7 @@ struct TuneRow {
   int variant = 0;  // AllReduce: kVar*; AllGather / Broadcast: 1 = multicast push; ReduceScatter: 1 = ring
   int ctas = 0, threads = 0;
   size_t sub = 0;
+  size_t grain = 0;  // see Tuning::grain
 };
 
 struct Tuning {
@@ -69,6 +70,7 @@ struct Tuning {
   // the thresholds above only
   std::shared_ptr<std::vector<TuneRow>> rows;
   bool use_table = true;              // "table 0" (or HXCCL_TUNE_TABLE=0) ignores the rows
+  size_t grain = 16 * 1024;           // bytes of a pair's block (a slice) one CTA takes before the grid grows
   int mc_force = -1;                  // AllGather / Broadcast multicast push: 1 always, 0 never, -1 table / default
   bool mc_copy = true;                // AllGather / Broadcast push through the multicast alias
   size_t mc_copy_min = 0;             // ... from this many bytes per block
@@ -84,18 +86,19 @@ bool parse_row(const std::string& line, TuneRow* row, std::string* why);
 
 // Sets one tuning knob by name ("max_ctas", "oneshot_max", "nvls_min", "single_sub_max",
 // "sub_max", "min_steps", "threads", "roles_min", "roles_sub", "ring_min", "ring_max_ranks", "ring_sub", "p2p_threads",
-// "exact", "nvls_gather", "table", "mc_force", "mc_copy", "mc_copy_min", "rs_ring_min", "ll_max", "ll_mc");
+// "exact", "nvls_gather", "table", "grain", "mc_force", "mc_copy", "mc_copy_min", "rs_ring_min", "ll_max", "ll_mc");
 // false for an unknown name.
 bool set_knob(Tuning* t, const char* name, long value);
 // Applies a tuning file (HXCCL_TUNE_FILE): knob lines "name value" or "name=value", and table
 // rows "row <allreduce|allgather|reducescatter|broadcast> n=<ranks> [es=<bytes>] [mode=exact|fast]
-// from=<bytes> variant=<name|number> [ctas=<c>] [threads=<256|512>] [sub=<bytes>]"; the first
+// from=<bytes> variant=<name|number> [ctas=<c>] [threads=<256|512>] [sub=<bytes>] [grain=<bytes>]"; the first
 // row line of a file replaces the compiled-in table. '#' starts a comment. False, with the
 // reason in *why, for an unreadable file or a bad line.
 bool load_tune_file(Tuning* t, const char* path, std::string* why);
 
 // generic exchange where the largest block of any pair is `max_pair` bytes
-Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t, size_t cta_bytes = 16 * 1024);
+// cta_bytes: bytes of a pair's block per CTA before the grid grows (0 = t.grain)
+Geometry plan_xchg(size_t max_pair, int n, size_t half_bytes, const Tuning& t, size_t cta_bytes = 0);
 // two-shot / NVLS AllReduce of `bytes`
 Geometry plan_sliced(size_t bytes, int n, size_t half_bytes, const Tuning& t);
 // the same as a three-role pipeline: ctas = 3 * lanes, epochs = steps + 1

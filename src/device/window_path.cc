@@ -123,6 +123,10 @@ hxcclResult_t WindowPath::setup_local() {
   t.ll_max = size_t(std::max(0L, env_long("HXCCL_LL_MAX", long(t.ll_max))));
   t.ll_mc = env_long("HXCCL_LL_MC", 1) != 0;
   t.mc_copy = env_long("HXCCL_MC_COPY", 1) != 0;
+  {
+    const long f = env_long("HXCCL_MC_FORCE", -1);
+    t.mc_force = f < 0 ? -1 : (f != 0);
+  }
   t.rs_ring_min = size_t(std::max(0L, env_long("HXCCL_RS_RING_MIN", long(t.rs_ring_min))));
   return hxcclSuccess;
 }
@@ -433,8 +437,15 @@ hxcclResult_t WindowPath::broken(std::string* why) {
   return broken_;
 }
 
+// Launches belong on the communicator's device whatever device the caller has current; done()
+// puts the caller's device back.
 cudaStream_t WindowPath::enter(void* stream) {
-  cudaSetDevice(dev_);
+  int cur = dev_;
+  caller_dev_ = -1;
+  if (cudaGetDevice(&cur) == cudaSuccess && cur != dev_) {
+    caller_dev_ = cur;
+    cudaSetDevice(dev_);
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (used_ && st != last_stream_) {  // keep the communicator's launches in one order
     cudaEventRecord(order_event_, last_stream_);
@@ -446,6 +457,10 @@ cudaStream_t WindowPath::enter(void* stream) {
 }
 
 hxcclResult_t WindowPath::done(cudaError_t e, const char* what) {
+  if (caller_dev_ >= 0) {
+    cudaSetDevice(caller_dev_);
+    caller_dev_ = -1;
+  }
   if (e == cudaSuccess) return hxcclSuccess;
   if (!eng_.error.empty()) {
     error = eng_.error;

@@ -24,6 +24,7 @@ class WindowPath : public DevicePath {
 
   hxcclResult_t broken(std::string* why) override;
   const char* kind() const override { return nvls_ ? "window+nvls" : "window"; }
+  int device() const override { return dev_; }
   hxcclResult_t allreduce(const void* send, void* recv, size_t count, int dt, const OpPlan& plan,
                           int order, void* stream) override;
   hxcclResult_t allreduce_cast(const void* send, void* recv, size_t count, int wire_dt, const OpPlan& plan,
@@ -75,6 +76,7 @@ class WindowPath : public DevicePath {
   bool nvls_ = false;
   unsigned long long* status_ = nullptr;  // pinned host: [0] sticky, [1] soft
   Engine eng_;
+  int caller_dev_ = -1;  // the caller's current device while a launch switched to dev_
   cudaStream_t last_stream_ = nullptr;
   bool used_ = false;
   cudaEvent_t order_event_ = nullptr;

@@ -75,7 +75,7 @@ def test_allreduce_exact_with_small_chunks():
                 cases.append((dt, op, count, variant, 100 + len(cases)))
     cases.append((L.FLOAT32, L.SUM, (5 << 20) // 4 + 1, 0, 99))  # above HXCCL_RING_MIN: the tuner picks the ring
     res = run_ranks(n, _allreduce_body, cases, gpus=True, timeout=120,
-                    env={"HXCCL_IPC_CHUNK": "4096", "HXCCL_RING_MIN": str(4 << 20)},
+                    env={"HXCCL_IPC_CHUNK": "4096", "HXCCL_RING_MIN": str(4 << 20), "HXCCL_TUNE_TABLE": "0"},
                     rank_env={1: {"HXCCL_IPC_CHUNK": "65536"}})
     for k, (dt, op, count, variant, seed) in enumerate(cases):
         want = oracle.allreduce(inputs_for(n, count, dt, seed, tame=True), dt, op)
@@ -168,7 +168,7 @@ def test_allreduce_role_pipelines_with_multicast(n):
                 cases.append((dt, op, count, 0, len(cases)))        # integers: the switch is exact too
     cases.append((L.FLOAT32, L.SUM, 1 << 20, 0, 77))               # floats through the switch: tolerance
     cases.append((L.BFLOAT16, L.SUM, 1 << 20, 0, 78))
-    res = run_ranks(n, _pipelines_body, cases, gpus=True, timeout=180, nvls=True)
+    res = run_ranks(n, _pipelines_body, cases, gpus=True, timeout=180, nvls=True, env={"HXCCL_TUNE_TABLE": "0"})
     nvls = "nvls" in res[0][0]["kind"]
     for k, (dt, op, count, exact, seed) in enumerate(cases):
         xs = inputs_for(n, count, dt, seed, tame=True)
@@ -231,7 +231,9 @@ def _multicast_copy_body(comm, rank, n):
 @pytest.mark.parametrize("n", WORLDS)
 @pytest.mark.parametrize("multicast", [True, False])
 def test_multicast_allgather_broadcast_and_lines(n, multicast):
-    res = run_ranks(n, _multicast_copy_body, gpus=True, timeout=180, nvls=multicast)
+    # the fixed thresholds, not the measured table, so that the variants asserted below are known
+    res = run_ranks(n, _multicast_copy_body, gpus=True, timeout=180, nvls=multicast,
+                    env={"HXCCL_TUNE_TABLE": "0", "HXCCL_MC_FORCE": "1" if multicast else "0"})
     if multicast and "nvls" not in res[0]["kind"]:
         pytest.skip("no NVSwitch multicast on this node: " + res[0]["kind"])
     cases = ((L.FLOAT32, L.SUM, 1), (L.FLOAT32, L.SUM, 2049), (L.BFLOAT16, L.AVG, 777), (L.INT64, L.MIN, 5),
@@ -351,6 +353,9 @@ def _collectives_body(comm, rank, n):
     out["shift"] = bool((got.cpu().numpy() == np.random.default_rng((rank - 1) % n).integers(0, 256, nb, dtype=np.uint8)).all())
     out["a2a"] = a2a.cpu().numpy()[::nb].tolist()
     out["rs"] = rs.cpu().numpy().view(np.uint32)
+    # a buffer on another GPU of this process is refused before anything is launched
+    stranger = torch.ones(8, device=f"cuda:{(torch.cuda.current_device() + 1) % torch.cuda.device_count()}")
+    out["foreign"] = (comm.all_reduce(stranger, check=False), comm.last_error())
     out["err"] = comm.async_error()
     return out
 
@@ -362,6 +367,7 @@ def test_other_collectives(n):
     want_rs = oracle.reducescatter(inputs_for(n, 1000 * n, L.FLOAT32, 5), L.FLOAT32, L.SUM)
     for r in range(n):
         assert res[r]["ag"] and res[r]["bc"] and res[r]["shift"] and res[r]["err"] == 0, (r, res[r])
+        assert res[r]["foreign"][0] == L.INVALID_ARGUMENT and "lives on CUDA device" in res[r]["foreign"][1]
         assert np.array_equal(res[r]["rs"], want_rs[r])
         first = [int(np.random.default_rng(r).integers(0, 256, 3 << 20, dtype=np.uint8)[0])] * n
         # block j of rank r's result is block r of rank j's send buffer: x_r + j (uint8, wrapping)

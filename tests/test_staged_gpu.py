@@ -61,7 +61,8 @@ def _body(comm, rank, n, force):
 def test_staged_path_matches_host_path(force):
     n = 2
     env = {"HXCCL_DEVICE_TRANSPORT": "staged"} if force else {}
-    res = run_ranks(n, _body, force, gpus=True, timeout=180, env=env)
+    # both ranks on device 0, also on a machine with more GPUs: that is the case under test
+    res = run_ranks(n, _body, force, gpus=True, timeout=180, env=env, one_gpu=True)
     k = 0
     for r in range(n):
         assert res[r]["kind"] == "staged", res[r]["kind"]
@@ -91,7 +92,7 @@ def _copy_failure(comm, rank, n):
 def test_injected_copy_failure_is_an_error_on_the_failing_rank():
     """Host-side fault injection: the device-to-host copy of rank 0 'fails'."""
     res = run_ranks(2, _copy_failure, gpus=True, timeout=60, env={"HXCCL_NET_TIMEOUT_MS": "3000"},
-                    rank_env={0: {"HXCCL_TEST_FAIL_DEVICE_COPY": "1"}})
+                    rank_env={0: {"HXCCL_TEST_FAIL_DEVICE_COPY": "1"}}, one_gpu=True)
     rc0, msg0, again0 = res[0]
     assert rc0 == L.UNHANDLED_CUDA and "injected" in msg0 and again0 == L.UNHANDLED_CUDA  # sticky
     assert res[1][0] != 0  # the peer does not hang: its receive times out or sees the closed mesh
