@@ -29,6 +29,8 @@ typedef struct { int MPI_SOURCE, MPI_TAG, MPI_ERROR; } MPI_Status;
 #define MPI_STATUSES_IGNORE ((MPI_Status*)0)
 #define MPI_ERRORS_RETURN 1
 #define MPI_MAX_ERROR_STRING 256
+#define MPI_ANY_SOURCE (-1)
+#define MPI_ANY_TAG (-1)
 int MPI_Init(int*, char***);
 int MPI_Comm_size(MPI_Comm, int*);
 int MPI_Comm_rank(MPI_Comm, int*);
@@ -53,6 +55,9 @@ int MPI_Bcast(void*, int, MPI_Datatype, int, MPI_Comm);
 int MPI_Allgather(const void*, int, MPI_Datatype, void*, int, MPI_Datatype, MPI_Comm);
 int MPI_Allreduce(const void*, void*, int, MPI_Datatype, MPI_Op, MPI_Comm);
 int MPI_Error_string(int, char*, int*);
+int MPI_Iprobe(int, int, MPI_Comm, int*, MPI_Status*);
+int MPI_Testall(int, MPI_Request*, int*, MPI_Status*);
+int MPI_Wait(MPI_Request*, MPI_Status*);
 #ifdef __cplusplus
 }
 #endif

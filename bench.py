@@ -43,6 +43,8 @@ def parse_args():
     ap.add_argument("--exact", type=int, default=1, help="1: bit-exact reduction order; 0: NVLS fast mode")
     ap.add_argument("--no-sweep", action="store_true", help="skip the small size sweep in the extras")
     ap.add_argument("--no-nccl", action="store_true", help="skip the NCCL comparison in the extras")
+    ap.add_argument("--bind-numa", type=int, default=1,
+                    help="1: pin the rank to the CPUs next to its GPU before host buffers are allocated")
     return ap.parse_args()
 
 
@@ -266,6 +268,11 @@ def main() -> int:
     value = algbw * factor
 
     # ---- end to end: pinned host -> device, AllReduce, slice of the result back -------------
+    numa = None
+    if comm is not None and args.bind_numa:
+        from hxccl_b200.utils.env import bind_to_gpu_numa  # noqa: PLC0415
+
+        numa = bind_to_gpu_numa(local)  # before the pinned buffers exist: they follow the CPUs
     host_in = torch.empty(count, dtype=tdt).pin_memory()
     host_in.copy_(src.cpu())
     host_out = torch.empty(4096 // es, dtype=tdt).pin_memory()
@@ -370,7 +377,7 @@ def main() -> int:
             "verified": verified, "verified_variant": variant_checked,
             "algbw_GBps": round(algbw, 2),
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "ms_per_step": round(e2e_ms, 4),
-                    "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": host_out.numel() * es},
+                    "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": host_out.numel() * es, "numa": numa},
             "gpu_launches": int(launches), "clocks": clocks, "fast_mode": fast, "ring_mode": ring, "sweep": sweep, "nccl": nccl, "async_error": err,
         }
         print(json.dumps(line))

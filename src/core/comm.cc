@@ -18,16 +18,24 @@ int next_op_tag() {
   return tag;
 }
 
-hxcclResult_t make_comm(hxcclComm_t* out, std::shared_ptr<Channel> chan) {
+}  // namespace
+
+hxcclResult_t comm_from_channel(hxcclComm_t* out, std::shared_ptr<Channel> chan, bool derived) {
   auto* c = new hxcclComm;
   c->rank = chan->rank();
   c->nranks = chan->size();
   c->chan = std::move(chan);
   c->wire = std::make_unique<HostWire>(c->chan);
   c->ops = OpTable(next_op_tag());
+  c->device.derived = derived;
   device_eager_start(c);
   *out = c;
   return hxcclSuccess;
+}
+
+namespace {
+hxcclResult_t make_comm(hxcclComm_t* out, std::shared_ptr<Channel> chan, bool derived = false) {
+  return comm_from_channel(out, std::move(chan), derived);
 }
 
 hxcclResult_t check_config(const hxcclConfig_t* cfg) {
@@ -104,7 +112,7 @@ hxcclResult_t hxcclCommSplit(hxcclComm_t comm, int color, int key, hxcclComm_t* 
                    [&](int a, int b) { return all[2 * a + 1] < all[2 * b + 1]; });
   const int me = int(std::find(members.begin(), members.end(), comm->rank) - members.begin());
   return make_comm(newcomm,
-                   comm->chan->child(members, me, mix_id(comm->chan->id(), seq, uint32_t(color))));
+                   comm->chan->child(members, me, mix_id(comm->chan->id(), seq, uint32_t(color))), true);
 }
 
 hxcclResult_t hxcclCommShrink(hxcclComm_t comm, int* excl, int nexcl, hxcclComm_t* newcomm,
@@ -132,7 +140,7 @@ hxcclResult_t hxcclCommShrink(hxcclComm_t comm, int* excl, int nexcl, hxcclComm_
   }
   const int me = int(std::find(members.begin(), members.end(), comm->rank) - members.begin());
   return make_comm(newcomm,
-                   comm->chan->child(members, me, mix_id(comm->chan->id(), comm->offspring.shrinks[salt]++, salt)));
+                   comm->chan->child(members, me, mix_id(comm->chan->id(), comm->offspring.shrinks[salt]++, salt)), true);
 }
 
 hxcclResult_t hxcclCommAbort(hxcclComm_t comm) {

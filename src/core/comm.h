@@ -64,6 +64,9 @@ struct DeviceSide {
   hxcclResult_t down = hxcclSuccess;  // not Success: every later device call returns this
   std::string down_why;
   uint64_t bytes = 0, msgs = 0;
+  // true for communicators made by Split / Shrink: their windows are sized more modestly
+  // (HXCCL_CHILD_WINDOW_MB, smaller Send/Recv slots) than a communicator made from scratch
+  bool derived = false;
 };
 
 // What the caller can ask about failures: the text of the latest one, and the code that
@@ -96,6 +99,9 @@ struct hxcclComm {
 };
 
 namespace hx {
+
+// Builds a communicator on a connected channel (collective: the device path may start).
+hxcclResult_t comm_from_channel(hxcclComm_t* out, std::shared_ptr<Channel> chan, bool derived = false);
 
 // Records `msg` as the communicator's last error; System/Internal/Remote (and Timeout, which
 // only the bounded device-side waits produce) also become the sticky asynchronous error.

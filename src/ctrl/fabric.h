@@ -28,29 +28,46 @@ namespace hx {
 constexpr const char* kTruncatedMsg =
     "message truncated: the receive buffer is smaller than the message";
 
-class Fabric {
+// What a communicator needs from the layer that connects its processes: tagged messages
+// between pairs, matched per (sender, channel, tag) in posting order, handed out as tickets.
+// Two carriers exist: the TCP mesh below (Fabric) and, in builds with MPI, MpiCarrier
+// (ctrl/mpi_carrier.cc), which stands where the reference has MpiNet and MpiTransport
+// (src/net_mpi.cc:5-84, src/transport_mpi.cc:9-110).
+class Carrier {
+ public:
+  virtual ~Carrier() = default;
+  virtual int self() const = 0;
+  virtual int nprocs() const = 0;
+  // Post a transfer; the returned ticket is polled with poll_ticket. peer == self() pairs a
+  // send with a receive of this process.
+  virtual int post_send(int peer, uint64_t chan, int tag, const void* buf, size_t bytes) = 0;
+  virtual int post_recv(int peer, uint64_t chan, int tag, void* buf, size_t bytes) = 0;
+  // Non-blocking progress + completion check. When *done the ticket is released and the result
+  // of the transfer returned (*why explains a failure).
+  virtual hxcclResult_t poll_ticket(int ticket, bool* done, std::string* why) = 0;
+  // Blocks (making progress) until the ticket completes or the optional limit runs out.
+  virtual hxcclResult_t wait_ticket(int ticket, std::string* why) = 0;
+  virtual void cancel(int ticket) = 0;
+  // Test hook: treats the connection to `peer` as lost, as if the process had died.
+  virtual void sever(int peer) = 0;
+};
+
+class Fabric : public Carrier {
  public:
   // socks[i] is a connected, non-blocking stream socket to process i; socks[self] is -1.
   Fabric(int self, std::vector<int> socks);
-  ~Fabric();
+  ~Fabric() override;
   Fabric(const Fabric&) = delete;
   Fabric& operator=(const Fabric&) = delete;
 
-  int self() const { return self_; }
-  int nprocs() const { return static_cast<int>(links_.size()); }
-
-  // Post a transfer; the returned ticket is polled with poll_ticket. peer == self() pairs a
-  // send with a receive of this process.
-  int post_send(int peer, uint64_t chan, int tag, const void* buf, size_t bytes);
-  int post_recv(int peer, uint64_t chan, int tag, void* buf, size_t bytes);
-  // Non-blocking progress + completion check. When *done the ticket is released and the result
-  // of the transfer returned (*why explains a failure).
-  hxcclResult_t poll_ticket(int ticket, bool* done, std::string* why);
-  // Blocks (polling the sockets) until the ticket completes or the optional limit runs out.
-  hxcclResult_t wait_ticket(int ticket, std::string* why);
-  void cancel(int ticket);
-  // Test hook: shuts the connection to `peer` down as if the process had died.
-  void sever(int peer);
+  int self() const override { return self_; }
+  int nprocs() const override { return static_cast<int>(links_.size()); }
+  int post_send(int peer, uint64_t chan, int tag, const void* buf, size_t bytes) override;
+  int post_recv(int peer, uint64_t chan, int tag, void* buf, size_t bytes) override;
+  hxcclResult_t poll_ticket(int ticket, bool* done, std::string* why) override;
+  hxcclResult_t wait_ticket(int ticket, std::string* why) override;  // polls the sockets
+  void cancel(int ticket) override;
+  void sever(int peer) override;  // shuts the connection down
 
  private:
   struct Wire {  // frame header on the socket
@@ -134,12 +151,12 @@ class Fabric {
 // numbers), traffic is tagged with the communicator's channel id.
 class Channel {
  public:
-  Channel(std::shared_ptr<Fabric> f, uint64_t id, std::vector<int> members, int rank)
+  Channel(std::shared_ptr<Carrier> f, uint64_t id, std::vector<int> members, int rank)
       : fabric_(std::move(f)), id_(id), members_(std::move(members)), rank_(rank) {}
   int rank() const { return rank_; }
   int size() const { return static_cast<int>(members_.size()); }
   uint64_t id() const { return id_; }
-  Fabric& fabric() { return *fabric_; }
+  Carrier& fabric() { return *fabric_; }
   const std::vector<int>& members() const { return members_; }
 
   int post_send(int peer, int tag, const void* buf, size_t bytes) {
@@ -168,7 +185,7 @@ class Channel {
     if (r != hxcclSuccess) error = why_;
     return r;
   }
-  std::shared_ptr<Fabric> fabric_;
+  std::shared_ptr<Carrier> fabric_;
   uint64_t id_;
   std::vector<int> members_;
   int rank_;

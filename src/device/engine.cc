@@ -85,7 +85,7 @@ cudaError_t Engine::allreduce(const RankBufs* b, size_t count, int dt, const OpP
     const size_t lines = (bytes + 7) / 8;
     Geometry g;
     g.threads = 256;
-    g.ctas = int(std::max<size_t>(1, std::min<size_t>(std::min(32, tune.max_ctas), (lines + 255) / 256)));
+    g.ctas = int(std::max<size_t>(1, std::min<size_t>(std::min(128, tune.max_ctas), (lines + 255) / 256)));
     std::vector<LLArgs> args(views.size());
     for (size_t r = 0; r < views.size(); ++r)
       build_allreduce_ll(&args[r], views[r], epoch, b[r].send, b[r].recv, count, dt, plan, order,

@@ -11,6 +11,7 @@
 //   [flags A]  one 64-bit epoch per (CTA, source rank): "my step-e data is in your window"
 //   [flags B]  same, for the second phase of two-phase kernels
 //   [flags C]  same, for the third role of the three-role pipeline (kernels/roles_body.cuh)
+//   [lines]    data-with-epoch lines of the small-message AllReduce (kernels/ll_body.cuh)
 //   [p2p]      Send/Recv slots, a ring of kP2pDepth per (sender, worker)
 //   [half 0] [half 1]  collective staging, alternating per step
 //
@@ -37,7 +38,7 @@ constexpr int kP2pWorkers = 16;     // independent sub-channels per directed pai
 // Two slots of 512 KiB measured faster than four of 256 KiB (256 MiB ring shift on two GPUs:
 // 425 against 349 GB/s): the per-piece hand-shake, not the depth, is what limits a lane.
 constexpr int kP2pDepth = 2;        // slots a (sender, worker) cycles through
-constexpr size_t kP2pSlotBytes = 512 * 1024;  // per (sender, worker, slot)
+constexpr size_t kP2pSlotBytes = 512 * 1024;  // per (sender, worker, slot): the default, see WinView::p2p_slot
 
 // byte offsets inside a window
 constexpr size_t kOffAbort = 0;
@@ -51,18 +52,19 @@ static_assert(size_t(kMaxRanks) * kP2pWorkers * 8 <= 4096 && kOffP2pHdr + size_t
 constexpr size_t kOffFlagsA = 64 * 1024;
 constexpr size_t kOffFlagsB = kOffFlagsA + size_t(kMaxCtas) * kMaxRanks * 8;
 constexpr size_t kOffFlagsC = kOffFlagsB + size_t(kMaxCtas) * kMaxRanks * 8;
-constexpr size_t kHeaderBytes = 1u << 20;
 // Lines of the small-message AllReduce (kernels/ll_body.cuh): two halves by epoch parity, each
-// with one slot per source rank. A line is 16 bytes and carries 8 bytes of payload.
-constexpr size_t kOffLL = 256 * 1024;
-constexpr size_t kLLBytes = kHeaderBytes - kOffLL;
+// with one slot per source rank. A line is 16 bytes and carries 8 bytes of payload. The region
+// is part of the header, which is what gets cleared when a window is created.
+constexpr size_t kOffLL = 1u << 20;
+constexpr size_t kLLBytes = 8u << 20;
+constexpr size_t kHeaderBytes = kOffLL + kLLBytes;
 static_assert(kOffFlagsC + size_t(kMaxCtas) * kMaxRanks * 8 <= kOffLL, "flag pages must end before the line region");
 inline constexpr size_t ll_slot_bytes(int n) { return kLLBytes / 2 / size_t(n) / 256 * 256; }
 inline constexpr size_t ll_max_payload(int n) { return ll_slot_bytes(n) / 2; }
 constexpr size_t kOffP2pSlots = kHeaderBytes;
 
-inline constexpr size_t p2p_region_bytes(int n) {
-  return size_t(n) * kP2pWorkers * kP2pDepth * kP2pSlotBytes;
+inline constexpr size_t p2p_region_bytes(int n, size_t slot_bytes = kP2pSlotBytes) {
+  return size_t(n) * kP2pWorkers * kP2pDepth * slot_bytes;
 }
 
 // status word (pinned host memory, one per communicator): 0 fine, else
@@ -76,6 +78,10 @@ struct WinView {
   unsigned long long* soft;    // pinned host word for truncation reports (not sticky)
   size_t half_off[2];     // offsets of the two staging halves
   size_t half_bytes;
+  // Bytes of one Send/Recv slot; the same on every rank of the communicator. Communicators made
+  // by Split / Shrink use smaller slots (and staging halves) than the one they came from, so
+  // that a program with many sub-communicators does not pay the full window for each.
+  size_t p2p_slot;
   unsigned long long wait_ns;  // limit of every device-side wait
   // Optional phase timing (HXCCL_TRACE=1): kTraceSlots accumulators of nanoseconds per CTA,
   // filled by thread 0 of each CTA from %globaltimer; null when off.

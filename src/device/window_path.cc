@@ -143,8 +143,9 @@ hxcclResult_t WindowPath::init() {
   w.mc = nvls_ ? reinterpret_cast<char*>(mc_va_) : nullptr;
   w.status = status_;
   w.soft = status_ + 1;
-  const size_t p2p_bytes = round_up(p2p_region_bytes(n_), 1u << 20);
+  const size_t p2p_bytes = round_up(p2p_region_bytes(n_, p2p_slot_), 1u << 20);
   const size_t half = (win_bytes_ - kHeaderBytes - p2p_bytes) / 2 / 4096 * 4096;
+  w.p2p_slot = p2p_slot_;
   w.half_off[0] = kHeaderBytes + p2p_bytes;
   w.half_off[1] = w.half_off[0] + half;
   w.half_bytes = half;
@@ -166,8 +167,24 @@ hxcclResult_t WindowPath::init() {
 
 hxcclResult_t WindowPath::setup_windows() {
   const CuDriver& d = cu();
-  const long half_mb = std::max(1L, env_long("HXCCL_WINDOW_MB", 512) / 2);
-  const size_t want = kHeaderBytes + round_up(p2p_region_bytes(n_), 1u << 20) + 2 * (size_t(half_mb) << 20);
+  // A communicator made from scratch stages through 512 MiB and moves Send/Recv payload in
+  // 512 KiB slots; one made by Split / Shrink gets a quarter of both unless told otherwise, so
+  // that many sub-communicators stay affordable (large messages take more pipelined steps,
+  // nothing else changes). The values are the same on every rank of a communicator: every
+  // rank reads them from the same kind of communicator, and the smallest wish wins below.
+  const bool child = c_->device.derived;
+  long win_mb = env_long(child ? "HXCCL_CHILD_WINDOW_MB" : "HXCCL_WINDOW_MB", child ? 128 : 512);
+  long slot_kb = env_long(child ? "HXCCL_CHILD_P2P_SLOT_KB" : "HXCCL_P2P_SLOT_KB", child ? 128 : 512);
+  {
+    int neg[2] = {int(-std::max(2L, win_mb)), int(-std::max(16L, std::min(slot_kb, 4096L)))};
+    if (c_->chan->max_int(&neg[0]) != hxcclSuccess || c_->chan->max_int(&neg[1]) != hxcclSuccess)
+      return fail(hxcclSystemError, "window size agreement failed: " + c_->chan->error);
+    win_mb = -neg[0];
+    slot_kb = -neg[1];
+  }
+  p2p_slot_ = size_t(slot_kb) * 1024 / 16 * 16;
+  const long half_mb = std::max(1L, win_mb / 2);
+  const size_t want = kHeaderBytes + round_up(p2p_region_bytes(n_, p2p_slot_), 1u << 20) + 2 * (size_t(half_mb) << 20);
   va_.assign(n_, 0);
   peer_h_.assign(n_, 0);
 

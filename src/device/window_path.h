@@ -66,6 +66,7 @@ class WindowPath : public DevicePath {
   int dev_ = 0;
   CUdevice cudev_ = 0;
   size_t win_bytes_ = 0;
+  size_t p2p_slot_ = kP2pSlotBytes;  // Send/Recv slot size of this communicator
   bool vmm_ = false;  // windows came from cuMemCreate (else one cudaMalloc, n == 1)
   CUmemGenericAllocationHandle own_h_ = 0;
   std::vector<CUmemGenericAllocationHandle> peer_h_;

@@ -97,6 +97,7 @@ hxcclResult_t hxcclWorldCreate(hxcclWorld_t* out, int n, int window_mb, int wait
     v.half_off[0] = kHeaderBytes + p2p;
     v.half_off[1] = v.half_off[0] + half;
     v.half_bytes = half;
+    v.p2p_slot = kP2pSlotBytes;
     v.wait_ns = uint64_t(wait_ms) * 1000000ull;
     v.rank = r;
     v.n = n;

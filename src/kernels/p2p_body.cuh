@@ -20,8 +20,8 @@ namespace hx {
 __device__ __forceinline__ unsigned long long* p2p_word(char* win, size_t base, int peer, int worker) {
   return reinterpret_cast<unsigned long long*>(win + base) + size_t(peer) * kP2pWorkers + worker;
 }
-__device__ __forceinline__ char* p2p_slot(char* win, int sender, int worker, unsigned idx) {
-  return win + kOffP2pSlots + ((size_t(sender) * kP2pWorkers + worker) * kP2pDepth + idx) * kP2pSlotBytes;
+__device__ __forceinline__ char* p2p_slot(char* win, size_t slot_bytes, int sender, int worker, unsigned idx) {
+  return win + kOffP2pSlots + ((size_t(sender) * kP2pWorkers + worker) * kP2pDepth + idx) * slot_bytes;
 }
 __device__ __forceinline__ unsigned long long* p2p_hdr(char* win, int sender, int worker, unsigned idx) {
   return reinterpret_cast<unsigned long long*>(win + kOffP2pHdr) +
@@ -29,14 +29,14 @@ __device__ __forceinline__ unsigned long long* p2p_hdr(char* win, int sender, in
 }
 
 // bytes of `total` that worker `wk` moves in round q (rounds advance by kP2pWorkers slots)
-__device__ __forceinline__ void p2p_share(size_t total, unsigned long long q, int wk, size_t* off,
+__device__ __forceinline__ void p2p_share(size_t total, size_t slot_bytes, unsigned long long q, int wk, size_t* off,
                                           size_t* len) {
-  const size_t o = (q * kP2pWorkers + wk) * kP2pSlotBytes;
+  const size_t o = (q * kP2pWorkers + wk) * slot_bytes;
   *off = o;
-  *len = o >= total ? 0 : (total - o < kP2pSlotBytes ? total - o : kP2pSlotBytes);
+  *len = o >= total ? 0 : (total - o < slot_bytes ? total - o : slot_bytes);
 }
-__device__ __forceinline__ unsigned long long p2p_rounds(size_t total) {
-  const size_t per = size_t(kP2pWorkers) * kP2pSlotBytes;
+__device__ __forceinline__ unsigned long long p2p_rounds(size_t total, size_t slot_bytes) {
+  const size_t per = size_t(kP2pWorkers) * slot_bytes;
   const unsigned long long r = (total + per - 1) / per;
   return r ? r : 1;  // an empty message still takes one hand-shake
 }
@@ -57,14 +57,14 @@ __device__ inline bool p2p_body(const P2pArgs& a, int lane_idx, int wk, int* sh_
     unsigned long long* ready = p2p_word(theirs, kOffP2pReady, me, wk);
     for (int k = 0; k < lane.nops; ++k) {
       const size_t total = lane.ops[k].bytes;
-      const unsigned long long rounds = p2p_rounds(total);
+      const unsigned long long rounds = p2p_rounds(total, w.p2p_slot);
       for (unsigned long long q = 0; q < rounds; ++q, ++tx) {
         if (threadIdx.x == 0 && tx >= kP2pDepth && !wait_flag(w, done, tx - kP2pDepth + 1, peer)) *sh_fail = 1;
         __syncthreads();
         if (*sh_fail) return false;
         size_t off, len;
-        p2p_share(total, q, wk, &off, &len);
-        if (len) cta_copy(p2p_slot(theirs, me, wk, unsigned(tx % kP2pDepth)), lane.ops[k].buf + off, len);
+        p2p_share(total, w.p2p_slot, q, wk, &off, &len);
+        if (len) cta_copy(p2p_slot(theirs, w.p2p_slot, me, wk, unsigned(tx % kP2pDepth)), lane.ops[k].buf + off, len);
         __syncthreads();
         if (threadIdx.x == 0) {
           st_relaxed_sys(p2p_hdr(theirs, me, wk, unsigned(tx % kP2pDepth)), total);
@@ -89,12 +89,12 @@ __device__ inline bool p2p_body(const P2pArgs& a, int lane_idx, int wk, int* sh_
         __syncthreads();
         if (*sh_fail) return false;
         const size_t total = *sh_word;
-        if (q == 0) rounds = p2p_rounds(total);
+        if (q == 0) rounds = p2p_rounds(total, w.p2p_slot);
         size_t off, len;
-        p2p_share(total, q, wk, &off, &len);
+        p2p_share(total, w.p2p_slot, q, wk, &off, &len);
         if (off < room && len) {
           const size_t take = room - off < len ? room - off : len;
-          cta_copy(lane.ops[k].buf + off, p2p_slot(mine, peer, wk, unsigned(rx % kP2pDepth)), take);
+          cta_copy(lane.ops[k].buf + off, p2p_slot(mine, w.p2p_slot, peer, wk, unsigned(rx % kP2pDepth)), take);
         }
         if (q == 0 && wk == 0 && threadIdx.x == 0 && total > room)
           st_relaxed_sys(w.soft, (static_cast<unsigned long long>(kStatTruncated) << 56) | unsigned(peer));

@@ -103,3 +103,20 @@ def test_measurement_session_on_host_buffers(tmp_path):
     subprocess.run([sys.executable, os.path.join(ROOT, "bench", "plot.py"), "curves", str(out / "allreduce_np2_host.txt"),
                     str(out / "allreduce_np3_host.txt"), "-o", str(svg)], check=True, timeout=60)
     assert len(xml.dom.minidom.parse(str(svg)).getElementsByTagName("path")) == 2
+
+
+def test_gpu_numa_cpus_reads_sysfs(tmp_path):
+    """The NUMA helper of the launcher against a made-up sysfs tree."""
+    from hxccl_b200.utils.env import _parse_cpulist, gpu_numa_cpus
+
+    dev = tmp_path / "bus/pci/devices/0000:1b:00.0"
+    dev.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    node = tmp_path / "devices/system/node/node1"
+    node.mkdir(parents=True)
+    (node / "cpulist").write_text("32-47,96-99\n")
+    assert gpu_numa_cpus("0000:1B:00.0", sysfs=str(tmp_path)) == set(range(32, 48)) | set(range(96, 100))
+    (dev / "numa_node").write_text("-1\n")
+    assert gpu_numa_cpus("0000:1b:00.0", sysfs=str(tmp_path)) == set()
+    assert gpu_numa_cpus("0000:ff:00.0", sysfs=str(tmp_path)) == set()
+    assert _parse_cpulist("0,2-3") == {0, 2, 3}

@@ -359,3 +359,34 @@ def test_cancelled_send_keeps_its_own_copy():
     res = run_ranks(2, _cancel)
     assert res[0] == L.SYSTEM_ERROR
     assert res[1] == (7, 7, 5)
+
+
+def test_mpi_carrier_against_a_loopback_mpi(tmp_path):
+    """No MPI is installed here, so the MPI carrier (the counterpart of the reference's MpiNet
+    and MpiTransport) runs against tests/fake_mpi/fake_mpi.cc, a one-process MPI whose messages
+    to self work: its matching, parking, truncation and cancel rules, and hxcclCommInitMPI with
+    host collectives on top. The sources are compiled here with -DHXCCL_HAVE_MPI."""
+    import subprocess
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    src = root / "src"
+    exe = tmp_path / "carrier_check"
+    host_sources = [str(p) for d in ("core", "ctrl", "host", "math") for p in sorted((src / d).glob("*.cc"))]
+    stubs = tmp_path / "no_device.cc"
+    stubs.write_text(
+        '#include "core/devpath.h"\n'
+        "namespace hx {\n"
+        "MemKind classify(const void* p) { return p ? MemKind::Host : MemKind::Null; }\n"
+        "int device_ordinal_of(const void*) { return -1; }\n"
+        "bool cuda_context_exists() { return false; }\n"
+        "std::unique_ptr<DevicePath> start_device_path(hxcclComm*, hxcclResult_t* rc, std::string* why) {\n"
+        '  *rc = hxcclInvalidUsage; *why = "no device path in this build"; return nullptr; }\n'
+        "}\n")
+    cmd = ["g++", "-std=c++17", "-O1", "-DHXCCL_HAVE_MPI", "-DHXCCL_NO_NVTX", f"-I{root / 'baseline' / 'mpi_stub'}",
+           f"-I{root / 'include'}", f"-I{src}", str(root / "tests" / "fake_mpi" / "fake_mpi.cc"),
+           str(root / "tests" / "fake_mpi" / "carrier_check.cc"), str(stubs), *host_sources, "-pthread", "-o", str(exe)]
+    built = subprocess.run(cmd, capture_output=True, text=True)
+    assert built.returncode == 0, built.stderr[-3000:]
+    ran = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
+    assert ran.returncode == 0 and ran.stdout.strip().endswith("ok"), ran.stdout + ran.stderr
