@@ -79,6 +79,9 @@ class DevicePath {
 enum class MemKind { Null, Host, Device };
 // Where `p` lives, asked of the driver without creating a CUDA context.
 MemKind classify(const void* p);
+// The same with the CUDA device the memory belongs to (*ordinal, -1 for host memory), in one
+// driver call.
+MemKind classify_on(const void* p, int* ordinal);
 // CUDA device a device pointer belongs to, or -1 (host memory, unknown).
 int device_ordinal_of(const void* p);
 // True when this process already has a CUDA context (again without creating one).

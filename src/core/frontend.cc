@@ -89,7 +89,8 @@ void device_eager_start(hxcclComm* c) {
 }
 
 hxcclResult_t pick_path(hxcclComm* c, const void* a, const void* b, Path* out) {
-  const MemKind ka = classify(a), kb = classify(b);
+  int where_a = -1, where_b = -1;
+  const MemKind ka = classify_on(a, &where_a), kb = classify_on(b, &where_b);
   if (ka != MemKind::Null && kb != MemKind::Null && ka != kb)
     return comm_fail(c, hxcclInvalidArgument,
                      "send and recv buffers must both be host or both be device memory");
@@ -111,10 +112,9 @@ hxcclResult_t pick_path(hxcclComm* c, const void* a, const void* b, Path* out) {
   // buffer that lives on another device of this process would fault them.
   const int home = c->device.path ? c->device.path->device() : -1;
   if (home >= 0) {
-    const void* const ptrs[2] = {a, b};
-    const MemKind kinds[2] = {ka, kb};
+    const int wheres[2] = {where_a, where_b};
     for (int k = 0; k < 2; ++k) {
-      const int where = kinds[k] == MemKind::Device ? device_ordinal_of(ptrs[k]) : -1;
+      const int where = wheres[k];
       if (where >= 0 && where != home)
         return comm_fail(c, hxcclInvalidArgument,
                          "the buffer lives on CUDA device " + std::to_string(where) +

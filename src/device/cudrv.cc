@@ -53,6 +53,7 @@ CuDriver load() {
   HX_BIND(DeviceGetAttribute);
   HX_BIND(DevicePrimaryCtxGetState);
   HX_BIND(PointerGetAttribute);
+  HX_BIND(PointerGetAttributes);
   HX_BIND(MemGetAllocationGranularity);
   HX_BIND(MemCreate);
   HX_BIND(MemRelease);

@@ -20,6 +20,7 @@ struct CuDriver {
   CUresult (*DeviceGetAttribute)(int*, CUdevice_attribute, CUdevice) = nullptr;
   CUresult (*DevicePrimaryCtxGetState)(CUdevice, unsigned*, int*) = nullptr;
   CUresult (*PointerGetAttribute)(void*, CUpointer_attribute, CUdeviceptr) = nullptr;
+  CUresult (*PointerGetAttributes)(unsigned, CUpointer_attribute*, void**, CUdeviceptr) = nullptr;
   CUresult (*MemGetAllocationGranularity)(size_t*, const CUmemAllocationProp*,
                                           CUmemAllocationGranularity_flags) = nullptr;
   CUresult (*MemCreate)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*,

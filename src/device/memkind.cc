@@ -7,6 +7,27 @@
 
 namespace hx {
 
+// One driver call per pointer on the path of every collective: memory type, managed flag and
+// device ordinal together. Unknown pointers (plain host memory) make the call fail or leave the
+// type zero.
+MemKind classify_on(const void* p, int* ordinal) {
+  *ordinal = -1;
+  if (!p) return MemKind::Null;
+  const CuDriver& d = cu();
+  if (!d.ok) return MemKind::Host;
+  unsigned type = 0, managed = 0;
+  int where = -1;
+  CUpointer_attribute what[3] = {CU_POINTER_ATTRIBUTE_MEMORY_TYPE, CU_POINTER_ATTRIBUTE_IS_MANAGED,
+                                 CU_POINTER_ATTRIBUTE_DEVICE_ORDINAL};
+  void* into[3] = {&type, &managed, &where};
+  if (d.PointerGetAttributes(3, what, into, reinterpret_cast<CUdeviceptr>(p)) != CUDA_SUCCESS) return MemKind::Host;
+  if (type == CU_MEMORYTYPE_DEVICE || type == CU_MEMORYTYPE_UNIFIED || managed) {
+    *ordinal = where;
+    return MemKind::Device;
+  }
+  return MemKind::Host;  // ordinary, pinned or registered host memory
+}
+
 MemKind classify(const void* p) {
   if (!p) return MemKind::Null;
   const CuDriver& d = cu();

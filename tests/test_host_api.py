@@ -378,6 +378,7 @@ def test_mpi_carrier_against_a_loopback_mpi(tmp_path):
         '#include "core/devpath.h"\n'
         "namespace hx {\n"
         "MemKind classify(const void* p) { return p ? MemKind::Host : MemKind::Null; }\n"
+        "MemKind classify_on(const void* p, int* o) { *o = -1; return classify(p); }\n"
         "int device_ordinal_of(const void*) { return -1; }\n"
         "bool cuda_context_exists() { return false; }\n"
         "std::unique_ptr<DevicePath> start_device_path(hxcclComm*, hxcclResult_t* rc, std::string* why) {\n"
