@@ -346,8 +346,14 @@ def main() -> int:
     # ---- extras: torch's NCCL backend on the same sizes, same process, same timing -------------
     nccl = None
     if args.impl == "hxccl" and world > 1 and not args.no_sweep and not args.no_nccl:
+        saved_stdout = None
         try:
             os.environ.setdefault("MASTER_PORT", "29533")
+            # NCCL prints its banner (and, with NCCL_DEBUG set, its log) on stdout: this program's
+            # stdout is one JSON line, so while NCCL runs fd 1 is stderr's file
+            sys.stdout.flush()
+            saved_stdout = os.dup(1)
+            os.dup2(2, 1)
             pg = dist.new_group(backend="nccl")
 
             def nccl_allreduce(a, b):
@@ -362,6 +368,11 @@ def main() -> int:
                     "note": "torch.distributed all_reduce, NCCL backend, in place, fp32 sum"}
         except Exception as e:  # noqa: BLE001
             nccl = {"error": str(e)[:200]}
+        finally:
+            if saved_stdout is not None:
+                torch.cuda.synchronize()
+                os.dup2(saved_stdout, 1)
+                os.close(saved_stdout)
     if world > 1:
         dist.destroy_process_group()
     if rank == 0:

@@ -54,7 +54,8 @@ def tune_candidates(coll: str, world: int, nbytes: int):
         if nbytes >= (32 << 20) and world > 2:
             c.append(("twoshot_roles", 2, True, {"roles_min": 1, "roles_min_ranks": 2}, {"variant": "twoshot_roles"}))
         if nbytes >= (256 << 10):
-            for threads, ctas, sub in ((512, 128, 512 << 10), (256, 256, 256 << 10), (256, 256, 128 << 10), (256, 192, 512 << 10)):
+            for threads, ctas, sub in ((512, 128, 512 << 10), (512, 128, 128 << 10), (512, 128, 64 << 10),
+                                       (256, 256, 128 << 10), (256, 256, 64 << 10), (256, 256, 32 << 10)):
                 c.append((f"ring t{threads} c{ctas} s{sub >> 10}K", 6, True,
                           {"threads": threads, "max_ctas": ctas, "ring_sub": sub},
                           {"variant": "ring", "threads": threads, "ctas": ctas, "sub": sub}))
@@ -78,8 +79,10 @@ def tune_candidates(coll: str, world: int, nbytes: int):
             c.append(("push g4K", 0, True, {"rs_ring_min": 0, "grain": 4096}, {"variant": "push", "grain": 4096}))
         if nbytes >= (64 << 10):
             c.append(("ring_rs", 0, True, {"rs_ring_min": 1}, {"variant": "ring_rs"}))
-            c.append(("ring_rs t256 c256", 0, True, {"rs_ring_min": 1, "threads": 256, "max_ctas": 256, "ring_sub": 256 << 10},
-                      {"variant": "ring_rs", "threads": 256, "ctas": 256, "sub": 256 << 10}))
+            for threads, ctas, sub in ((512, 128, 128 << 10), (256, 256, 128 << 10), (256, 256, 32 << 10)):
+                c.append((f"ring_rs t{threads} c{ctas} s{sub >> 10}K", 0, True,
+                          {"rs_ring_min": 1, "threads": threads, "max_ctas": ctas, "ring_sub": sub},
+                          {"variant": "ring_rs", "threads": threads, "ctas": ctas, "sub": sub}))
     return c
 
 
@@ -133,7 +136,7 @@ def emit_tune(args, rank, world, buf, out, tdt, es, timed) -> None:
             best = results[0]
             if incumbent is not None:  # hysteresis: stay unless clearly beaten
                 same = [r for r in results if r[2] == incumbent]
-                if same and same[0][0] <= best[0] * (1.03 if size >= (1 << 20) else 1.06):
+                if same and same[0][0] <= best[0] * (1.01 if size >= (16 << 20) else 1.03 if size >= (1 << 20) else 1.06):
                     best = same[0]
             incumbent = best[2]
             if rank == 0:

@@ -311,6 +311,7 @@ cudaError_t Engine::p2p(const RankP2p* ops, cudaStream_t st) {
       std::memset(&a, 0, sizeof a);
       a.w = views[r];
       a.workers_per_cta = wpc;
+      a.bulk = tune.p2p_bulk && !world() ? 1 : 0;
       std::vector<P2pOp> rest;
       for (const P2pOp& o : left[r]) {
         int lane = -1;

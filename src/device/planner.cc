@@ -74,6 +74,7 @@ bool set_knob(Tuning* t, const char* name, long v) {
   else if (k == "ll_mc") t->ll_mc = v != 0;
   else if (k == "rs_ring_min") t->rs_ring_min = size_t(std::max(0L, v));
   else if (k == "table") t->use_table = v != 0;
+  else if (k == "p2p_bulk") t->p2p_bulk = v != 0;
   else if (k == "grain") t->grain = size_t(std::max(256L, v));
   else if (k == "mc_force") t->mc_force = v < 0 ? -1 : (v != 0);
   else if (k == "mc_copy") t->mc_copy = v != 0;

@@ -63,6 +63,7 @@ struct Tuning {
   int ring_max_ranks = kMaxRanks;     // ... on communicators of at most this many ranks
   size_t ring_sub = 512 * 1024;       // largest per-CTA share of one ring hop
   int p2p_threads = 512;              // CTA width of the Send/Recv lanes
+  bool p2p_bulk = true;               // Send pieces move by bulk asynchronous copies (one driving thread per CTA)
   size_t ll_max = 16 * 1024;          // AllReduce: up to here the flag-in-data kernel (0 = never)
   bool ll_mc = true;                  // ... its lines go out through the multicast alias when there is one
   size_t rs_ring_min = 256u << 20;    // ReduceScatter: neighbour ring from this many input bytes (0 = never)
@@ -86,7 +87,7 @@ bool parse_row(const std::string& line, TuneRow* row, std::string* why);
 
 // Sets one tuning knob by name ("max_ctas", "oneshot_max", "nvls_min", "single_sub_max",
 // "sub_max", "min_steps", "threads", "roles_min", "roles_sub", "ring_min", "ring_max_ranks", "ring_sub", "p2p_threads",
-// "exact", "nvls_gather", "table", "grain", "mc_force", "mc_copy", "mc_copy_min", "rs_ring_min", "ll_max", "ll_mc");
+// "exact", "nvls_gather", "table", "grain", "p2p_bulk", "mc_force", "mc_copy", "mc_copy_min", "rs_ring_min", "ll_max", "ll_mc");
 // false for an unknown name.
 bool set_knob(Tuning* t, const char* name, long value);
 // Applies a tuning file (HXCCL_TUNE_FILE): knob lines "name value" or "name=value", and table

@@ -205,6 +205,7 @@ struct P2pArgs {
   WinView w;
   int nlanes;
   int workers_per_cta;       // a power of two up to kP2pWorkers: workers one CTA serves in turn
+  int bulk;                  // senders move their pieces with bulk asynchronous copies (needs the dynamic shared memory)
   P2pLane lanes[kMaxLanes];  // CTA (lane, group) = blockIdx.x / G, % G with G = kP2pWorkers / workers_per_cta
 };
 

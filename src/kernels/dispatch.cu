@@ -18,12 +18,12 @@ __global__ void __launch_bounds__(512) k_xchg_copy_world(const XchgArgs* a) {
   xchg_body<uint8_t, false>(a[blockIdx.y], blockIdx.x, gridDim.x, sh);
 }
 // CTA (lane, group): the group's workers one after the other (see P2pArgs::workers_per_cta)
-__device__ inline void p2p_cta(const P2pArgs& a, int* fail, unsigned long long* word) {
+__device__ inline void p2p_cta(const P2pArgs& a, int* fail, unsigned long long* word, BulkPipe* pipe = nullptr) {
   const int wpc = a.workers_per_cta, groups = kP2pWorkers / wpc;
   const int lane = blockIdx.x / groups, first = (blockIdx.x % groups) * wpc;
   if (lane >= a.nlanes) return;
   for (int k = 0; k < wpc; ++k) {
-    if (!p2p_body(a, lane, first + k, fail, word)) return;
+    if (!p2p_body(a, lane, first + k, fail, word, pipe)) return;
     __syncthreads();
   }
 }
@@ -31,6 +31,17 @@ __global__ void __launch_bounds__(512) k_p2p(const __grid_constant__ P2pArgs a) 
   __shared__ int fail;
   __shared__ unsigned long long word;
   p2p_cta(a, &fail, &word);
+}
+// The same with the senders' pieces moved by bulk asynchronous copies through kBulkSmemBytes of
+// dynamic shared memory (production form only).
+__global__ void __launch_bounds__(512) k_p2p_bulk(const __grid_constant__ P2pArgs a) {
+  extern __shared__ __align__(128) unsigned char staging[];
+  __shared__ __align__(8) unsigned long long bars[kBulkStages];
+  __shared__ int fail;
+  __shared__ unsigned long long word;
+  BulkPipe pipe;
+  bulk_pipe_init(pipe, staging, bars);
+  p2p_cta(a, &fail, &word, &pipe);
 }
 __global__ void __launch_bounds__(512) k_p2p_world(const P2pArgs* a) {
   __shared__ int fail;
@@ -108,6 +119,12 @@ cudaError_t launch_xchg_copy(const XchgArgs* args, LaunchShape s, cudaStream_t s
 
 cudaError_t launch_p2p(const P2pArgs* args, LaunchShape s, cudaStream_t st) {
   if (s.world) return launch_world(reinterpret_cast<const void*>(&k_p2p_world), args, s, st);
+  if (args->bulk) {
+    static const cudaError_t opted = cudaFuncSetAttribute(k_p2p_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kBulkSmemBytes));
+    if (opted != cudaSuccess) return opted;
+    k_p2p_bulk<<<s.ctas, s.threads, kBulkSmemBytes, st>>>(*args);
+    return cudaGetLastError();
+  }
   k_p2p<<<s.ctas, s.threads, 0, st>>>(*args);
   return cudaGetLastError();
 }

@@ -65,12 +65,12 @@ __global__ void __launch_bounds__(512) k_ring_world(const TwoShotArgs* a) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) k_ll(const __grid_constant__ LLArgs a) {
+__global__ void __launch_bounds__(256, 1) k_ll(const __grid_constant__ LLArgs a) {
   __shared__ FoldShared sh;
   ll_body<T>(a, blockIdx.x, gridDim.x, sh);
 }
 template <typename T>
-__global__ void __launch_bounds__(256) k_ll_world(const LLArgs* a) {
+__global__ void __launch_bounds__(256, 1) k_ll_world(const LLArgs* a) {
   __shared__ FoldShared sh;
   ll_body<T>(a[blockIdx.y], blockIdx.x, gridDim.x, sh);
 }

@@ -74,11 +74,14 @@ __device__ __forceinline__ T ll_fold_pow2(const uint2* data, int lane, int rank,
   return fold_doubling_pow2<T, N>(x, rank, op);
 }
 
-template <typename T>
-__device__ void ll_body(const LLArgs& a, int cta, int ncta, FoldShared& sh) {
+// kN: the rank count when it is 2, 4 or 8 (loops unroll, every line lives in registers), else
+// kMaxRanks with run-time bounds.
+template <typename T, int kN>
+__device__ void ll_ranks(const LLArgs& a, int cta, int ncta, FoldShared& sh) {
   constexpr int E = 8 / sizeof(T);  // elements of one line
+  constexpr bool kFixed = kN != kMaxRanks;
   const WinView& w = a.w;
-  const int me = w.rank, n = w.n;
+  const int me = w.rank, n = kFixed ? kN : w.n;
   const FoldSpec& f = a.fold;
   const unsigned flag = unsigned(a.epoch);
   const size_t slot = kLLBytes / 2 / size_t(n) / 256 * 256;  // ll_slot_bytes(n)
@@ -116,26 +119,42 @@ __device__ void ll_body(const LLArgs& a, int cta, int ncta, FoldShared& sh) {
     if (a.use_mc) {
       mc_st16(w.mc + off, line);
     } else {
-      for (int pp = 1; pp < n; ++pp) st16_volatile(w.win[(me + pp) % n] + off, line);
+#pragma unroll
+      for (int pp = 1; pp < kN; ++pp)
+        if (pp < n) st16_volatile(w.win[(me + pp) % n] + off, line);
     }
   }
+  // The lines of all sources are loaded together (their latencies overlap) and only those that
+  // have not arrived yet are polled one by one.
   for (size_t i = first; i < nlines; i += stride) {
-    uint2 data[kMaxRanks];
-    data[me] = own_line(i);
-    for (int pp = 1; pp < n; ++pp) {
-      const int p = (me + pp) % n;
-      if (!ll_wait_line(w, w.win[me] + half + size_t(p) * slot + (i << 4), flag, p, &data[p])) return;
+    uint2 data[kN];
+    uint4 seen[kN];
+    const char* mine = w.win[me] + half + (i << 4);
+#pragma unroll
+    for (int p = 0; p < kN; ++p)
+      if (p < n && p != me) seen[p] = ld16_volatile(mine + size_t(p) * slot);
+    const uint2 own = own_line(i);
+#pragma unroll
+    for (int p = 0; p < kN; ++p) {
+      if (p >= n) continue;
+      if (p == me)
+        data[p] = own;
+      else if (seen[p].y == flag && seen[p].w == flag)
+        data[p] = make_uint2(seen[p].x, seen[p].z);
+      else if (!ll_wait_line(w, mine + size_t(p) * slot, flag, p, &data[p]))
+        return;
     }
 #pragma unroll
     for (int l = 0; l < E; ++l) {
       if (i * E + l >= total) break;
       T r;
-      if (f.kind == kFoldDoubling && n == 2) r = ll_fold_pow2<T, 2>(data, l, me, f.op);
-      else if (f.kind == kFoldDoubling && n == 4) r = ll_fold_pow2<T, 4>(data, l, me, f.op);
-      else if (f.kind == kFoldDoubling && n == 8) r = ll_fold_pow2<T, 8>(data, l, me, f.op);
-      else {
-        T x[kMaxRanks];
-        for (int p = 0; p < n; ++p) {
+      if (kFixed && f.kind == kFoldDoubling) {
+        r = ll_fold_pow2<T, kFixed ? kN : 2>(data, l, me, f.op);
+      } else {
+        T x[kN];
+#pragma unroll
+        for (int p = 0; p < kN; ++p) {
+          if (p >= n) continue;
           const unsigned long long bits = (static_cast<unsigned long long>(data[p].y) << 32) | data[p].x;
           T e[E];
           memcpy(e, &bits, 8);
@@ -147,6 +166,16 @@ __device__ void ll_body(const LLArgs& a, int cta, int ncta, FoldShared& sh) {
       if (f.postdiv) r = div_trunc(r, f.postdiv);
       out[i * E + l] = r;
     }
+  }
+}
+
+template <typename T>
+__device__ void ll_body(const LLArgs& a, int cta, int ncta, FoldShared& sh) {
+  switch (a.w.n) {
+    case 2: ll_ranks<T, 2>(a, cta, ncta, sh); break;
+    case 4: ll_ranks<T, 4>(a, cta, ncta, sh); break;
+    case 8: ll_ranks<T, 8>(a, cta, ncta, sh); break;
+    default: ll_ranks<T, kMaxRanks>(a, cta, ncta, sh); break;
   }
 }
 

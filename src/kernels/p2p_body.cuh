@@ -28,21 +28,30 @@ __device__ __forceinline__ unsigned long long* p2p_hdr(char* win, int sender, in
          (size_t(sender) * kP2pWorkers + worker) * kP2pDepth + idx;
 }
 
-// bytes of `total` that worker `wk` moves in round q (rounds advance by kP2pWorkers slots)
+// A message is cut into pieces of at most a slot; one that would not fill a slot per worker is
+// cut into kP2pWorkers equal pieces instead, so that every worker of the lane carries part of it
+// (both ends compute this from the message length, which travels in the slot header).
+__device__ __forceinline__ size_t p2p_piece(size_t total, size_t slot_bytes) {
+  const size_t even = ((total + kP2pWorkers - 1) / kP2pWorkers + 15) & ~size_t(15);
+  return even < 16 ? 16 : (even < slot_bytes ? even : slot_bytes);
+}
+// bytes of `total` that worker `wk` moves in round q (rounds advance by kP2pWorkers pieces)
 __device__ __forceinline__ void p2p_share(size_t total, size_t slot_bytes, unsigned long long q, int wk, size_t* off,
                                           size_t* len) {
-  const size_t o = (q * kP2pWorkers + wk) * slot_bytes;
+  const size_t piece = p2p_piece(total, slot_bytes);
+  const size_t o = (q * kP2pWorkers + wk) * piece;
   *off = o;
-  *len = o >= total ? 0 : (total - o < slot_bytes ? total - o : slot_bytes);
+  *len = o >= total ? 0 : (total - o < piece ? total - o : piece);
 }
 __device__ __forceinline__ unsigned long long p2p_rounds(size_t total, size_t slot_bytes) {
-  const size_t per = size_t(kP2pWorkers) * slot_bytes;
+  const size_t per = size_t(kP2pWorkers) * p2p_piece(total, slot_bytes);
   const unsigned long long r = (total + per - 1) / per;
   return r ? r : 1;  // an empty message still takes one hand-shake
 }
 
 // One worker's share of every operation of a lane. False when a wait gave up.
-__device__ inline bool p2p_body(const P2pArgs& a, int lane_idx, int wk, int* sh_fail, unsigned long long* sh_word) {
+__device__ inline bool p2p_body(const P2pArgs& a, int lane_idx, int wk, int* sh_fail, unsigned long long* sh_word,
+                                BulkPipe* pipe = nullptr) {
   const WinView& w = a.w;
   const P2pLane& lane = a.lanes[lane_idx];
   const int me = w.rank, peer = lane.peer;
@@ -64,8 +73,21 @@ __device__ inline bool p2p_body(const P2pArgs& a, int lane_idx, int wk, int* sh_
         if (*sh_fail) return false;
         size_t off, len;
         p2p_share(total, w.p2p_slot, q, wk, &off, &len);
-        if (len) cta_copy(p2p_slot(theirs, w.p2p_slot, me, wk, unsigned(tx % kP2pDepth)), lane.ops[k].buf + off, len);
+        if (len) {
+          char* to = p2p_slot(theirs, w.p2p_slot, me, wk, unsigned(tx % kP2pDepth));
+          const char* from = lane.ops[k].buf + off;
+          if (pipe && ((reinterpret_cast<uintptr_t>(to) | reinterpret_cast<uintptr_t>(from) | len) & 15u) == 0) {
+            // the copy unit moves the piece; one thread drives it, the others meet it at the barrier
+            if (threadIdx.x == 0 && !bulk_copy_by_one_thread(*pipe, to, from, len)) {
+              raise_failure(w, kStatTimeout, unsigned(peer));
+              *sh_fail = 1;
+            }
+          } else {
+            cta_copy(to, from, len);
+          }
+        }
         __syncthreads();
+        if (*sh_fail) return false;
         if (threadIdx.x == 0) {
           st_relaxed_sys(p2p_hdr(theirs, me, wk, unsigned(tx % kP2pDepth)), total);
           st_release_sys(ready, tx + 1);

@@ -192,6 +192,84 @@ __device__ inline size_t cta_copy_multicast(char* mc_dst, const char* src, size_
   return nv << 4;
 }
 
+// ---- bulk asynchronous copies (the TMA unit, untiled form) ------------------------------------------
+// A copy whose source is this GPU's memory and whose destination is a peer's window can be
+// driven by one thread: cp.async.bulk brings a chunk into shared memory (completion on an
+// mbarrier), a second cp.async.bulk writes it to the destination, and several chunks are in
+// flight at once. The copy unit issues large transactions on its own, so no warp spends
+// instructions on moving bytes. Loads never use cluster multicast. Both addresses and the size
+// must be multiples of 16 bytes (the caller checks). Every wait is bounded: when one runs out,
+// the function stops issuing, waits for its stores in flight and returns false.
+constexpr int kBulkStages = 4;
+constexpr unsigned kBulkChunk = 32 * 1024;
+constexpr size_t kBulkSmemBytes = size_t(kBulkStages) * kBulkChunk;
+struct BulkPipe {
+  unsigned char* buf;        // kBulkSmemBytes of shared memory, 128-byte aligned
+  unsigned long long* bars;  // kBulkStages mbarriers, initialised once per kernel by bulk_pipe_init
+  unsigned phase;            // bit s = parity the next wait on stage s expects (kept by the issuing thread)
+};
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
+// all threads call; leaves with a barrier
+__device__ inline void bulk_pipe_init(BulkPipe& pipe, unsigned char* buf, unsigned long long* bars) {
+  pipe.buf = buf;
+  pipe.bars = bars;
+  pipe.phase = 0;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kBulkStages; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&bars[s])));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+}
+// Called by ONE thread. dst[0, n) = src[0, n).
+__device__ inline bool bulk_copy_by_one_thread(BulkPipe& pipe, char* dst, const char* src, size_t n) {
+  const size_t chunks = (n + kBulkChunk - 1) / kBulkChunk;
+  auto chunk_len = [&](size_t c) { return unsigned(n - c * kBulkChunk < kBulkChunk ? n - c * kBulkChunk : kBulkChunk); };
+  auto load = [&](size_t c) {
+    const int s = int(c % kBulkStages);
+    const unsigned len = chunk_len(c), bar = smem_addr(&pipe.bars[s]);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(len) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_addr(pipe.buf + size_t(s) * kBulkChunk)),
+                 "l"(src + c * kBulkChunk), "r"(len), "r"(bar)
+                 : "memory");
+  };
+  // loads run kBulkStages - 1 chunks ahead of the stores; a stage is loaded again only after the
+  // store that read it has finished reading (wait_group.read keeps one store group outstanding)
+  size_t issued = 0;
+  for (; issued < chunks && issued < size_t(kBulkStages - 1); ++issued) load(issued);
+  bool ok = true;
+  for (size_t c = 0; c < chunks && ok; ++c) {
+    const int s = int(c % kBulkStages);
+    const unsigned bar = smem_addr(&pipe.bars[s]), parity = (pipe.phase >> s) & 1u;
+    unsigned done = 0;
+    for (unsigned spins = 0; !done; ++spins) {
+      asm volatile(
+          "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+          : "=r"(done)
+          : "r"(bar), "r"(parity)
+          : "memory");
+      if (!done && spins > (1u << 22)) {  // far beyond any copy: give up
+        ok = false;
+        break;
+      }
+    }
+    if (!ok) break;
+    pipe.phase ^= 1u << s;
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst + c * kBulkChunk),
+                 "r"(smem_addr(pipe.buf + size_t(s) * kBulkChunk)), "r"(chunk_len(c))
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    if (issued < chunks) {
+      // chunk `issued` reuses the stage of chunk issued - kBulkStages = c - 1, whose store is one group back
+      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      load(issued);
+      ++issued;
+    }
+  }
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // every store has been performed
+  return ok;
+}
+
 // 16 bytes of elements of type T
 template <typename T>
 union Vec16 {

@@ -139,48 +139,66 @@ __device__ void ring_body(const TwoShotArgs& a, int cta, int ncta, FoldShared& s
   const int shift = rs ? 1 : 0;
   const int hops = rs ? n - 1 : 2 * n - 2;  // flags raised per round (and slots of one set)
   const size_t base = w.half_off[0];
-  int set = 0;  // ReduceScatter: slot set of the current round
-  auto slot = [&](char* win, int s) {
-    return win + base + (size_t(set * hops + s) * ncta + cta) * a.sub_bytes;
+  // ReduceScatter alternates between two slot sets by the round's parity (see the file comment)
+  auto slot = [&](char* win, int k, int s) {
+    return win + base + (size_t((rs ? (k & 1) : 0) * hops + s) * ncta + cta) * a.sub_bytes;
   };
   unsigned long long* to_right = flag_at(w.win[right], kOffFlagsA, cta, me);
   const unsigned long long* from_left = flag_at(w.win[me], kOffFlagsA, cta, left);
   char* mine = w.win[me];
   char* peer = w.win[right];
 
-  for (int k = 0; k < a.steps; ++k) {
-    const unsigned long long e0 = a.epoch0 + 1 + static_cast<unsigned long long>(k) * hops;
+  // the element work of hop s of round k: no waiting, no flag
+  auto hop = [&](int k, int s) {
     const size_t rel = (size_t(k) * ncta + cta) * a.sub_bytes;
-    set = rs ? (k & 1) : 0;
-    for (int s = 0; s <= hops; ++s) {
-      int b = (me - s - shift) % n;
-      if (b < 0) b += n;
-      const size_t blk0 = sh.bound[b] * sizeof(T), blk_bytes = (sh.bound[b + 1] - sh.bound[b]) * sizeof(T);
-      const size_t len = rel < blk_bytes ? min_sz(a.sub_bytes, blk_bytes - rel) : 0;
-      if (s > 0) {
-        if (threadIdx.x == 0 && !wait_flag(w, from_left, e0 + s - 1, left)) sh.fail = 1;
-        __syncthreads();
-        if (sh.fail) return;
-        tm.lap(kTrWaitA);
-      }
-      const char* own = a.send + blk0 + rel;
-      char* out = rs ? a.recv + rel : a.recv + blk0 + rel;
-      if (len) {
-        if (s == 0)
-          ring_pass<T, true, false>(slot(peer, 0), nullptr, own, nullptr, len, rule, false);
-        else if (s < n - 1)
-          ring_pass<T, true, true>(slot(peer, s), nullptr, own, slot(mine, s - 1), len, rule, false);
-        else if (s == n - 1)
-          ring_pass<T, true, true>(rs ? nullptr : slot(peer, s), out, own, slot(mine, s - 1), len, rule, true);
-        else
-          ring_pass<T, false, true>(s < hops ? slot(peer, s) : nullptr, out, nullptr, slot(mine, s - 1), len, rule, false);
-      }
+    int b = (me - s - shift) % n;
+    if (b < 0) b += n;
+    const size_t blk0 = sh.bound[b] * sizeof(T), blk_bytes = (sh.bound[b + 1] - sh.bound[b]) * sizeof(T);
+    const size_t len = rel < blk_bytes ? min_sz(a.sub_bytes, blk_bytes - rel) : 0;
+    if (!len) return;
+    const char* own = a.send + blk0 + rel;
+    char* out = rs ? a.recv + rel : a.recv + blk0 + rel;
+    if (s == 0)
+      ring_pass<T, true, false>(slot(peer, k, 0), nullptr, own, nullptr, len, rule, false);
+    else if (s < n - 1)
+      ring_pass<T, true, true>(slot(peer, k, s), nullptr, own, slot(mine, k, s - 1), len, rule, false);
+    else if (s == n - 1)
+      ring_pass<T, true, true>(rs ? nullptr : slot(peer, k, s), out, own, slot(mine, k, s - 1), len, rule, true);
+    else
+      ring_pass<T, false, true>(s < hops ? slot(peer, k, s) : nullptr, out, nullptr, slot(mine, k, s - 1), len, rule, false);
+  };
+  auto epoch_of = [&](int k, int s) {
+    return a.epoch0 + 1 + static_cast<unsigned long long>(k) * hops + static_cast<unsigned long long>(s);
+  };
+  auto raise = [&](int k, int s) {
+    __syncthreads();  // the CTA's stores come before the flag (release is cumulative)
+    if (threadIdx.x == 0) st_release_sys(to_right, epoch_of(k, s));
+    tm.lap(kTrSigA);
+  };
+
+  // The first hop of a round only sends and the last one only receives. Run on their own they
+  // leave one direction of the link idle for two hops out of 2n-1 (n+1 for ReduceScatter); so
+  // the last hop of round k and the first hop of round k+1, which do not depend on each other,
+  // share one step. The slot that first hop writes was consumed long before: the wait of this
+  // step (for the left neighbour's last flag of round k) is the one the file comment's argument
+  // for slot 0 rests on.
+  hop(0, 0);
+  tm.lap(kTrMid);
+  raise(0, 0);
+  for (int k = 0; k < a.steps; ++k) {
+    for (int s = 1; s <= hops; ++s) {
+      if (threadIdx.x == 0 && !wait_flag(w, from_left, epoch_of(k, s - 1), left)) sh.fail = 1;
+      __syncthreads();
+      if (sh.fail) return;
+      tm.lap(kTrWaitA);
+      hop(k, s);
+      const bool next_first = s == hops && k + 1 < a.steps;
+      if (next_first) hop(k + 1, 0);
       tm.lap(s < n ? kTrMid : kTrOut);
-      if (s < hops) {
-        __syncthreads();  // the CTA's stores come before the flag (release is cumulative)
-        if (threadIdx.x == 0) st_release_sys(to_right, e0 + s);
-        tm.lap(kTrSigA);
-      }
+      if (s < hops)
+        raise(k, s);
+      else if (next_first)
+        raise(k + 1, 0);
     }
   }
   signal_and_wait(w, kOffFlagsA, cta, a.epoch0 + 1 + static_cast<unsigned long long>(a.steps) * hops, &sh.fail);  // closing
