@@ -47,7 +47,8 @@ NVCCFLAGS = [
 
 
 def _newest_header() -> float:
-    hdrs = list(SRC.rglob("*.h")) + list(SRC.rglob("*.cuh")) + list((ROOT / "include").glob("*.h"))
+    hdrs = (list(SRC.rglob("*.h")) + list(SRC.rglob("*.cuh")) + list(SRC.rglob("*.inc"))
+            + list((ROOT / "include").glob("*.h")))
     return max(p.stat().st_mtime for p in hdrs)
 
 
