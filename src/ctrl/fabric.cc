@@ -23,6 +23,7 @@ Fabric::Fabric(int self, std::vector<int> socks) : self_(self), links_(socks.siz
   for (size_t i = 0; i < socks.size(); ++i) links_[i].fd = socks[i];
   sink_.resize(64 * 1024);
   if (const char* e = std::getenv("HXCCL_NET_TIMEOUT_MS")) wait_limit_ms_ = std::atol(e);
+  if (const char* e = std::getenv("HXCCL_SPIN_US")) spin_us_ = std::max(0L, std::atol(e));
 }
 
 Fabric::~Fabric() {
@@ -137,16 +138,22 @@ void Fabric::flush_out(int peer) {
     Outgoing& o = l.out.front();
     const size_t hs = sizeof(Wire), total = hs + o.head.bytes;
     while (o.sent < total) {
-      const char* from;
-      size_t len;
+      // what is left of the header and of the body leave in one call
+      iovec part[2];
+      int parts = 0;
       if (o.sent < hs) {
-        from = reinterpret_cast<const char*>(&o.head) + o.sent;
-        len = hs - o.sent;
-      } else {
-        from = o.body + (o.sent - hs);
-        len = total - o.sent;
+        part[parts].iov_base = reinterpret_cast<char*>(&o.head) + o.sent;
+        part[parts++].iov_len = hs - o.sent;
       }
-      const ssize_t w = ::send(l.fd, from, len, MSG_NOSIGNAL);
+      const size_t body_done = o.sent > hs ? o.sent - hs : 0;
+      if (body_done < o.head.bytes) {
+        part[parts].iov_base = const_cast<char*>(o.body) + body_done;
+        part[parts++].iov_len = o.head.bytes - body_done;
+      }
+      msghdr m{};
+      m.msg_iov = part;
+      m.msg_iovlen = parts;
+      const ssize_t w = ::sendmsg(l.fd, &m, MSG_NOSIGNAL);
       if (w > 0) {
         o.sent += static_cast<size_t>(w);
         continue;
@@ -215,6 +222,25 @@ void Fabric::end_body(Link& l) {
   l.in_ticket = -1;
 }
 
+// Bytes from the connection: frame headers and small bodies come through a read-ahead buffer
+// (one system call then usually delivers a whole small message, header and body), large bodies
+// go straight from the socket into their destination.
+ssize_t Fabric::pull(Link& l, char* into, size_t want) {
+  constexpr size_t kDirect = 16 * 1024;
+  if (l.ahead_pos == l.ahead_end) {
+    if (want >= kDirect) return ::recv(l.fd, into, want, 0);
+    if (l.ahead.empty()) l.ahead.resize(64 * 1024);
+    const ssize_t r = ::recv(l.fd, l.ahead.data(), l.ahead.size(), 0);
+    if (r <= 0) return r;
+    l.ahead_pos = 0;
+    l.ahead_end = static_cast<size_t>(r);
+  }
+  const size_t n = std::min(want, l.ahead_end - l.ahead_pos);
+  std::memcpy(into, l.ahead.data() + l.ahead_pos, n);
+  l.ahead_pos += n;
+  return static_cast<ssize_t>(n);
+}
+
 void Fabric::drain_in(int peer) {
   Link& l = links_[peer];
   while (!l.down) {
@@ -236,7 +262,7 @@ void Fabric::drain_in(int peer) {
         want = std::min(left, sink_.size());
       }
     }
-    const ssize_t r = ::recv(l.fd, into, want, 0);
+    const ssize_t r = pull(l, into, want);
     if (r < 0) {
       if (errno == EINTR) continue;
       if (errno == EAGAIN || errno == EWOULDBLOCK) return;
@@ -284,9 +310,12 @@ void Fabric::link_down(int peer, const std::string& why) {
   l.in_ticket = -1;
 }
 
-void Fabric::pump(int timeout_ms) {
-  std::vector<pollfd> pf;
-  std::vector<int> who;
+// One round of socket progress; true when a connection had something to do.
+bool Fabric::pump(int timeout_ms) {
+  std::vector<pollfd>& pf = poll_set_;  // kept between calls: this runs once per wait
+  std::vector<int>& who = poll_who_;
+  pf.clear();
+  who.clear();
   for (int i = 0; i < nprocs(); ++i) {
     Link& l = links_[i];
     if (i == self_ || l.down || l.fd < 0) continue;
@@ -297,13 +326,14 @@ void Fabric::pump(int timeout_ms) {
     pf.push_back(p);
     who.push_back(i);
   }
-  if (pf.empty()) return;
+  if (pf.empty()) return false;
   const int rc = ::poll(pf.data(), pf.size(), timeout_ms);
-  if (rc <= 0) return;
+  if (rc <= 0) return false;
   for (size_t k = 0; k < pf.size(); ++k) {
     if (pf[k].revents & POLLOUT) flush_out(who[k]);
     if (pf[k].revents & (POLLIN | POLLHUP | POLLERR)) drain_in(who[k]);
   }
+  return true;
 }
 
 // ---- completion --------------------------------------------------------------------------------
@@ -323,17 +353,29 @@ hxcclResult_t Fabric::poll_ticket(int ticket, bool* done, std::string* why) {
 
 hxcclResult_t Fabric::wait_ticket(int ticket, std::string* why) {
   const auto t0 = std::chrono::steady_clock::now();
+  // An answer that is already on its way arrives within microseconds: look for it without
+  // sleeping first, since waking a sleeping thread costs more than the message took. While
+  // bytes keep moving the wait keeps polling; it sleeps once nothing came for spin_us_.
+  auto quiet_since = t0;
+  bool spinning = spin_us_ > 0;
   for (;;) {
+    bool moved = false;
     {
       Lock g(mu_);
-      if (!tickets_[ticket].finished) pump(20);
+      if (!tickets_[ticket].finished) moved = pump(spinning ? 0 : 20);
       if (tickets_[ticket].finished) {
         bool done;
         return poll_ticket(ticket, &done, why);
       }
     }
-    if (wait_limit_ms_ > 0 &&
-        std::chrono::steady_clock::now() - t0 > std::chrono::milliseconds(wait_limit_ms_)) {
+    const auto now = std::chrono::steady_clock::now();
+    if (moved) {
+      quiet_since = now;
+      spinning = spin_us_ > 0;
+    } else if (spinning && now - quiet_since > std::chrono::microseconds(spin_us_)) {
+      spinning = false;
+    }
+    if (wait_limit_ms_ > 0 && now - t0 > std::chrono::milliseconds(wait_limit_ms_)) {
       cancel(ticket);
       if (why) *why = "no answer from a peer within HXCCL_NET_TIMEOUT_MS";
       return hxcclTimeout;

@@ -13,6 +13,9 @@
 // may drive communicators that share a fabric, and waits can be bounded
 // (HXCCL_NET_TIMEOUT_MS).
 #pragma once
+#include <poll.h>
+#include <sys/types.h>
+
 #include <cstdint>
 #include <deque>
 #include <list>
@@ -122,13 +125,17 @@ class Fabric : public Carrier {
     size_t in_room = 0;
     bool in_orphan = false;  // matched receive was cancelled: swallow the body
     Parked* in_parked = nullptr;
+    // read-ahead for headers and small bodies: [ahead_pos, ahead_end) is received but not consumed
+    std::vector<char> ahead;
+    size_t ahead_pos = 0, ahead_end = 0;
   };
 
   int new_ticket();
   void finish(int ticket, hxcclResult_t rc, const std::string& why = {});
-  void pump(int timeout_ms);
+  bool pump(int timeout_ms);
   void flush_out(int peer);
   void drain_in(int peer);
+  ssize_t pull(Link& l, char* into, size_t want);
   void start_body(Link& l, int peer);
   void end_body(Link& l);
   void link_down(int peer, const std::string& why);
@@ -139,12 +146,15 @@ class Fabric : public Carrier {
   std::vector<Ticket> tickets_;
   std::vector<int> spare_;
   std::vector<char> sink_;  // where surplus bytes of truncated messages go
+  std::vector<struct pollfd> poll_set_;
+  std::vector<int> poll_who_;
   // self traffic
   std::list<Wanted> self_wanted_;
   struct SelfSend { int ticket; uint64_t chan; int tag; const char* buf; size_t bytes; };
   std::list<SelfSend> self_sends_;
   std::recursive_mutex mu_;
   long wait_limit_ms_ = 0;  // 0 = wait forever
+  long spin_us_ = 500;      // HXCCL_SPIN_US: how long a wait polls without news before it sleeps
 };
 
 // A communicator's view of the fabric: ranks are positions in `members` (fabric process

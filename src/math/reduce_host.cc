@@ -4,11 +4,59 @@
 
 namespace hx {
 
+namespace {
+// float / double Sum and Prod. The element rule (elem.h: arith) differs from the machine's plain
+// a + b / a * b only where the result is a NaN (a NaN operand, inf - inf, 0 * inf): there it
+// fixes which NaN comes out. So a tile is first computed with plain arithmetic, which the
+// compiler vectorises, and the rule is applied element by element only to tiles whose plain
+// results contain a NaN. Bit-identical to the rule everywhere, several times faster on finite
+// data (the reference's host loop is the plain form throughout, src/reduce.cc:16-18, and gets
+// its NaN behaviour from the x86 instruction; this one does not depend on the machine).
+template <typename F>
+void arith_tiles(F* out, const F* a, const F* b, size_t count, int op) {
+  constexpr size_t kTile = 256;
+  F tile[kTile];
+  for (size_t i0 = 0; i0 < count; i0 += kTile) {
+    const size_t n = count - i0 < kTile ? count - i0 : kTile;
+    bool special = false;
+    if (op == kSum) {
+      for (size_t i = 0; i < n; ++i) {
+        tile[i] = a[i0 + i] + b[i0 + i];
+        special |= tile[i] != tile[i];
+      }
+    } else {
+      for (size_t i = 0; i < n; ++i) {
+        tile[i] = a[i0 + i] * b[i0 + i];
+        special |= tile[i] != tile[i];
+      }
+    }
+    if (special) {
+      for (size_t i = 0; i < n; ++i) out[i0 + i] = arith(a[i0 + i], b[i0 + i], op);
+    } else {
+      std::memcpy(out + i0, tile, n * sizeof(F));
+    }
+  }
+}
+template <typename T>
+bool fast_arith(T*, const T*, const T*, size_t, int) { return false; }
+template <>
+bool fast_arith<float>(float* o, const float* a, const float* b, size_t n, int op) {
+  arith_tiles(o, a, b, n, op);
+  return true;
+}
+template <>
+bool fast_arith<double>(double* o, const double* a, const double* b, size_t n, int op) {
+  arith_tiles(o, a, b, n, op);
+  return true;
+}
+}  // namespace
+
 void combine(void* out, const void* in_a, const void* in_b, size_t count, int dt, int op) {
   HX_DISPATCH_DTYPE(dt, {
     T* o = static_cast<T*>(out);
     const T* a = static_cast<const T*>(in_a);
     const T* b = static_cast<const T*>(in_b);
+    if ((op == kSum || op == kProd) && fast_arith<T>(o, a, b, count, op)) break;
     switch (op) {  // hoisted so each loop body is branch-free
       case kSum: for (size_t i = 0; i < count; ++i) o[i] = apply(a[i], b[i], kSum); break;
       case kProd: for (size_t i = 0; i < count; ++i) o[i] = apply(a[i], b[i], kProd); break;
