@@ -3,11 +3,16 @@
 over their socket bootstraps on this machine's CPUs: no GPU involved. The reference is the build
 of baseline/build_ref.py (baseline/_ref/libhxccl_ref.so).
 
-    python bench/host_vs_reference.py [--ranks 4] [--iters 20]
+    python bench/host_vs_reference.py [--ranks 4] [--iters 20] [--coll allreduce]
+
+`--coll` is allreduce, allgather, reducescatter, broadcast or alltoall; `bytes` is the size of the
+larger of the two buffers of a rank (the whole gathered vector for allgather, the whole input for
+reducescatter and alltoall).
 
 Every rank times `iters` calls per size after 5 warm-up calls between barriers (a one-element
-AllReduce of the same library); the figure is the median over calls of the maximum over ranks,
-as in the reference's bench/hxccl_perf.cc:36-49. Rank 0 prints one JSON line per size.
+AllReduce of the same library); a run's figure is the median over calls of the maximum over ranks,
+as in the reference's bench/hxccl_perf.cc:36-49. The libraries alternate for `--rounds` runs each
+and the best run of each is printed, one JSON line per size.
 """
 from __future__ import annotations
 
@@ -45,11 +50,15 @@ def load(which: str):
     lib.hxcclGetUniqueId.argtypes = [C.POINTER(Id)]
     lib.hxcclCommInitRank.argtypes = [C.POINTER(vp), C.c_int, Id, C.c_int]
     lib.hxcclAllReduce.argtypes = [vp, vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
+    lib.hxcclAllGather.argtypes = [vp, vp, C.c_size_t, C.c_int, vp, vp]
+    lib.hxcclReduceScatter.argtypes = [vp, vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
+    lib.hxcclBroadcast.argtypes = [vp, vp, C.c_size_t, C.c_int, C.c_int, vp, vp]
+    lib.hxcclAlltoAll.argtypes = [vp, vp, C.c_size_t, C.c_int, vp, vp]
     lib.hxcclCommDestroy.argtypes = [vp]
     return lib
 
 
-def child(which, rank, n, sizes, iters, id_q, out_q):
+def child(which, coll, rank, n, sizes, iters, id_q, out_q):
     import numpy as np
 
     os.environ["HXCCL_DEVICE"] = "0"
@@ -70,13 +79,22 @@ def child(which, rank, n, sizes, iters, id_q, out_q):
 
     rows = []
     for size in sizes:
-        x = np.random.default_rng(1234 + rank).random(size // 4, dtype=np.float32)
+        whole = max(n, size // 4 // n * n)  # fp32 elements, a multiple of the rank count
+        x = np.random.default_rng(1234 + rank).random(whole, dtype=np.float32)
         y = np.empty_like(x)
+        xp, yp, part = x.ctypes.data, y.ctypes.data, whole // n
+        call = {
+            "allreduce": lambda: lib.hxcclAllReduce(xp, yp, whole, 7, 0, comm, None),
+            "allgather": lambda: lib.hxcclAllGather(xp, yp, part, 7, comm, None),
+            "reducescatter": lambda: lib.hxcclReduceScatter(xp, yp, part, 7, 0, comm, None),
+            "broadcast": lambda: lib.hxcclBroadcast(xp, yp, whole, 7, 0, comm, None),
+            "alltoall": lambda: lib.hxcclAlltoAll(xp, yp, part, 7, comm, None),
+        }[coll]
         times = []
         for it in range(iters + 5):
             barrier()
             t0 = time.perf_counter()
-            assert lib.hxcclAllReduce(x.ctypes.data, y.ctypes.data, x.size, 7, 0, comm, None) == 0
+            assert call() == 0
             if it >= 5:
                 times.append(time.perf_counter() - t0)
         rows.append(times)
@@ -84,10 +102,10 @@ def child(which, rank, n, sizes, iters, id_q, out_q):
     out_q.put((rank, rows))
 
 
-def run(which, n, sizes, iters):
+def run(which, coll, n, sizes, iters):
     ctx = mp.get_context("spawn")
     id_q, out_q = ctx.Queue(), ctx.Queue()
-    procs = [ctx.Process(target=child, args=(which, r, n, sizes, iters, id_q, out_q)) for r in range(n)]
+    procs = [ctx.Process(target=child, args=(which, coll, r, n, sizes, iters, id_q, out_q)) for r in range(n)]
     for p in procs:
         p.start()
     got = dict(out_q.get(timeout=600) for _ in range(n))
@@ -104,14 +122,27 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--ranks", type=int, default=4)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--coll", default="allreduce",
+                    choices=["allreduce", "allgather", "reducescatter", "broadcast", "alltoall"])
+    ap.add_argument("--rounds", type=int, default=3, help="alternating runs of each library")
     ap.add_argument("--sizes", default="256,16384,65536,1048576,4194304,16777216,67108864")
     args = ap.parse_args()
     sizes = [int(s) for s in args.sizes.split(",")]
-    ours = run("hxccl", args.ranks, sizes, args.iters)
-    ref = run("reference", args.ranks, sizes, args.iters) if REF.exists() else [None] * len(sizes)
-    f = 2.0 * (args.ranks - 1) / args.ranks
+    # the two libraries take turns, and the best median of each counts: other tenants of the
+    # machine move single runs by tens of per cent
+    ours, ref = None, None
+    for _ in range(max(1, args.rounds)):
+        a = run("hxccl", args.coll, args.ranks, sizes, args.iters)
+        ours = a if ours is None else [min(x, y) for x, y in zip(ours, a)]
+        if REF.exists():
+            b = run("reference", args.coll, args.ranks, sizes, args.iters)
+            ref = b if ref is None else [min(x, y) for x, y in zip(ref, b)]
+    if ref is None:
+        ref = [None] * len(sizes)
+    n = args.ranks
+    f = {"allreduce": 2.0 * (n - 1) / n, "broadcast": 1.0}.get(args.coll, (n - 1) / n)
     for size, a, b in zip(sizes, ours, ref):
-        print(json.dumps({"ranks": args.ranks, "bytes": size, "hxccl_us": round(a * 1e6, 1),
+        print(json.dumps({"coll": args.coll, "ranks": args.ranks, "bytes": size, "hxccl_us": round(a * 1e6, 1),
                           "hxccl_busbw_GBps": round(size / a / 1e9 * f, 3),
                           "reference_us": None if b is None else round(b * 1e6, 1),
                           "reference_busbw_GBps": None if b is None else round(size / b / 1e9 * f, 3),

@@ -2,6 +2,7 @@
 
 #include <errno.h>
 #include <poll.h>
+#include <sched.h>
 #include <sys/socket.h>
 #include <unistd.h>
 
@@ -132,27 +133,35 @@ int Fabric::post_recv(int peer, uint64_t chan, int tag, void* buf, size_t bytes)
 
 // ---- socket progress -------------------------------------------------------------------------
 
+// What of a frame has not left yet, as at most two pieces (rest of the header, rest of the body).
+int Fabric::Outgoing::unsent(iovec v[2]) const {
+  const struct {
+    const char* at;
+    size_t len;
+  } piece[2] = {{reinterpret_cast<const char*>(&head), sizeof(Wire)}, {body, head.bytes}};
+  size_t skip = sent;
+  int k = 0;
+  for (const auto& p : piece) {
+    if (skip >= p.len) {
+      skip -= p.len;
+      continue;
+    }
+    v[k].iov_base = const_cast<char*>(p.at) + skip;
+    v[k++].iov_len = p.len - skip;
+    skip = 0;
+  }
+  return k;
+}
+
 void Fabric::flush_out(int peer) {
   Link& l = links_[peer];
   while (!l.down && !l.out.empty()) {
     Outgoing& o = l.out.front();
-    const size_t hs = sizeof(Wire), total = hs + o.head.bytes;
-    while (o.sent < total) {
-      // what is left of the header and of the body leave in one call
-      iovec part[2];
-      int parts = 0;
-      if (o.sent < hs) {
-        part[parts].iov_base = reinterpret_cast<char*>(&o.head) + o.sent;
-        part[parts++].iov_len = hs - o.sent;
-      }
-      const size_t body_done = o.sent > hs ? o.sent - hs : 0;
-      if (body_done < o.head.bytes) {
-        part[parts].iov_base = const_cast<char*>(o.body) + body_done;
-        part[parts++].iov_len = o.head.bytes - body_done;
-      }
-      msghdr m{};
-      m.msg_iov = part;
-      m.msg_iovlen = parts;
+    iovec v[2];
+    msghdr m{};
+    m.msg_iov = v;
+    // header and body leave in one system call
+    while ((m.msg_iovlen = o.unsent(v)) > 0) {
       const ssize_t w = ::sendmsg(l.fd, &m, MSG_NOSIGNAL);
       if (w > 0) {
         o.sent += static_cast<size_t>(w);
@@ -372,8 +381,12 @@ hxcclResult_t Fabric::wait_ticket(int ticket, std::string* why) {
     if (moved) {
       quiet_since = now;
       spinning = spin_us_ > 0;
-    } else if (spinning && now - quiet_since > std::chrono::microseconds(spin_us_)) {
-      spinning = false;
+    } else if (spinning) {
+      const auto quiet = now - quiet_since;
+      if (quiet > std::chrono::microseconds(spin_us_))
+        spinning = false;
+      else if (quiet > std::chrono::microseconds(50))
+        ::sched_yield();  // with more ranks than cores the peer may be waiting for this core
     }
     if (wait_limit_ms_ > 0 && now - t0 > std::chrono::milliseconds(wait_limit_ms_)) {
       cancel(ticket);

@@ -26,6 +26,8 @@
 
 #include "hxccl.h"
 
+struct iovec;
+
 namespace hx {
 
 constexpr const char* kTruncatedMsg =
@@ -90,6 +92,7 @@ class Fabric : public Carrier {
     const char* body;
     size_t sent = 0;              // header + body bytes written
     std::vector<char> keepalive;  // body copy made when a started frame is cancelled
+    int unsent(iovec v[2]) const;
   };
   struct Wanted {  // a posted receive
     int ticket;
@@ -154,7 +157,7 @@ class Fabric : public Carrier {
   std::list<SelfSend> self_sends_;
   std::recursive_mutex mu_;
   long wait_limit_ms_ = 0;  // 0 = wait forever
-  long spin_us_ = 500;      // HXCCL_SPIN_US: how long a wait polls without news before it sleeps
+  long spin_us_ = 2000;     // HXCCL_SPIN_US: how long a wait polls without news before it sleeps
 };
 
 // A communicator's view of the fabric: ranks are positions in `members` (fabric process

@@ -119,10 +119,20 @@ hxcclResult_t host_broadcast(HostCtx c, const void* send, void* recv, size_t byt
       if (pos + bit < c.n) HX_TRY(c.wire.send(rank_at(pos + bit), recv, bytes));
     return hxcclSuccess;
   }
+  // A rank in the middle takes in piece k+1 while piece k leaves for its successor.
+  auto piece = [&](size_t off) { return std::min(kChainPiece, bytes - off); };
+  if (pos > 0) HX_TRY(c.wire.recv(rank_at(pos - 1), recv, piece(0)));
   for (size_t off = 0; off < bytes; off += kChainPiece) {
-    const size_t len = std::min(kChainPiece, bytes - off);
-    if (pos > 0) HX_TRY(c.wire.recv(rank_at(pos - 1), at(recv, off), len));
-    if (pos < c.n - 1) HX_TRY(c.wire.send(rank_at(pos + 1), at(recv, off), len));
+    const size_t nxt = off + kChainPiece;
+    if (pos > 0 && nxt < bytes)
+      c.wire.post_recv(rank_at(pos - 1), at(recv, nxt), piece(nxt), kTagColl);
+    if (pos < c.n - 1) {
+      if (hxcclResult_t r = c.wire.post_send(rank_at(pos + 1), at(recv, off), piece(off), kTagColl)) {
+        c.wire.cancel_all();
+        return r;
+      }
+    }
+    HX_TRY(c.wire.finish_all());
   }
   return hxcclSuccess;
 }
@@ -155,14 +165,26 @@ hxcclResult_t host_reduce(HostCtx c, const void* send, void* recv, size_t count,
     }
     return hxcclSuccess;
   }
-  std::vector<char> inbox(kChainPiece);  // a multiple of every element size
-  for (size_t off = 0; off < bytes; off += kChainPiece) {
-    const size_t len = std::min(kChainPiece, bytes - off);
+  // Two inboxes of one piece each (a multiple of every element size): while the combined piece
+  // k leaves for the predecessor, piece k+1 of the successor arrives in the other inbox.
+  std::vector<char> inbox(pos < c.n - 1 ? 2 * kChainPiece : 0);
+  auto piece = [&](size_t off) { return std::min(kChainPiece, bytes - off); };
+  if (pos < c.n - 1) HX_TRY(c.wire.recv(rank_at(pos + 1), inbox.data(), piece(0)));
+  for (size_t off = 0, k = 0; off < bytes; off += kChainPiece, ++k) {
+    const size_t nxt = off + kChainPiece;
     if (pos < c.n - 1) {
-      HX_TRY(c.wire.recv(rank_at(pos + 1), inbox.data(), len));
-      reduce_into(acc + off, inbox.data(), len / es, dt, op);
+      reduce_into(acc + off, inbox.data() + (k & 1) * kChainPiece, piece(off) / es, dt, op);
+      if (nxt < bytes)
+        c.wire.post_recv(rank_at(pos + 1), inbox.data() + ((k + 1) & 1) * kChainPiece, piece(nxt),
+                         kTagColl);
     }
-    if (pos > 0) HX_TRY(c.wire.send(rank_at(pos - 1), acc + off, len));
+    if (pos > 0) {
+      if (hxcclResult_t r = c.wire.post_send(rank_at(pos - 1), acc + off, piece(off), kTagColl)) {
+        c.wire.cancel_all();
+        return r;
+      }
+    }
+    HX_TRY(c.wire.finish_all());
   }
   return hxcclSuccess;
 }

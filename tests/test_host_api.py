@@ -100,6 +100,45 @@ def test_send_recv_and_groups(n):
     assert res[1]["blocking"] == 7.5
 
 
+# sizes around the transport's thresholds: bodies under 16 KiB come through the 64 KiB read-ahead
+# buffer (several frames per system call), larger ones go straight into the receive buffer
+_BURST = [0, 1, 8, 4000, 16352, 16384, 16385, 65504, 65536, 65537, 300_001, 3, 1 << 20, 17, 5]
+
+
+def _burst(comm, rank, n):
+    peer = 1 - rank
+    ins = [np.random.default_rng(50 * k + rank).integers(0, 255, sz).astype(np.uint8)
+           for k, sz in enumerate(_BURST)]
+    expect = [np.random.default_rng(50 * k + peer).integers(0, 255, sz).astype(np.uint8)
+              for k, sz in enumerate(_BURST)]
+    outs = [np.zeros(sz, dtype=np.uint8) for sz in _BURST]
+    ok = []
+    # all sends first: the messages queue up at the receiver before it asks for any of them
+    hx.group_start()
+    for x in ins:
+        comm.send(x, peer)
+    for y in outs:
+        comm.recv(y, peer)
+    assert hx.group_end() == 0
+    ok.append(all(np.array_equal(a, b) for a, b in zip(outs, expect)))
+    # and as blocking pairs, one message at a time, in both directions
+    for k, sz in enumerate(_BURST):
+        y = np.zeros(sz, dtype=np.uint8)
+        if rank == 0:
+            comm.send(ins[k], 1)
+            comm.recv(y, 1)
+        else:
+            comm.recv(y, 0)
+            comm.send(ins[k], 0)
+        ok.append(np.array_equal(y, expect[k]))
+    return all(ok)
+
+
+@pytest.mark.parametrize("spin_us", ["0", "2000"])
+def test_mixed_message_sizes_arrive_intact(spin_us):
+    assert run_ranks(2, _burst, env={"HXCCL_SPIN_US": spin_us}) == [True, True]
+
+
 def _two_comm_group(comm, rank, n):
     """Crossed Send/Recv over two communicators in one group must not deadlock."""
     other = comm.split(0, rank)
