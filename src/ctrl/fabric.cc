@@ -1,6 +1,7 @@
 #include "fabric.h"
 
 #include <errno.h>
+#include <cstdio>
 #include <poll.h>
 #include <sched.h>
 #include <sys/socket.h>
@@ -15,6 +16,7 @@ namespace hx {
 namespace {
 constexpr uint32_t kWireMagic = 0x48784632u;        // "HxF2"
 constexpr uint64_t kMaxFrame = uint64_t(1) << 40;    // larger sizes mean a corrupt stream
+constexpr uint64_t kHoldMin = 64 * 1024;             // smaller early frames are parked at once
 using Lock = std::lock_guard<std::recursive_mutex>;
 
 std::string peer_gone(int peer) { return "rank " + std::to_string(peer) + " closed the connection"; }
@@ -25,6 +27,7 @@ Fabric::Fabric(int self, std::vector<int> socks) : self_(self), links_(socks.siz
   sink_.resize(64 * 1024);
   if (const char* e = std::getenv("HXCCL_NET_TIMEOUT_MS")) wait_limit_ms_ = std::atol(e);
   if (const char* e = std::getenv("HXCCL_SPIN_US")) spin_us_ = std::max(0L, std::atol(e));
+  if (const char* e = std::getenv("HXCCL_HOLD_US")) hold_us_ = std::max(0L, std::atol(e));
 }
 
 Fabric::~Fabric() {
@@ -127,6 +130,20 @@ int Fabric::post_recv(int peer, uint64_t chan, int tag, void* buf, size_t bytes)
     finish(t, hxcclSystemError, l.down_why);
     return t;
   }
+  if (l.held) {
+    if (l.in_head.chan == chan && l.in_head.tag == tag) {  // the held frame is the one
+      l.held = false;
+      l.in_ticket = t;
+      l.in_buf = dst;
+      l.in_room = bytes;
+      drain_in(peer);
+      return t;
+    }
+    park_frame(l);  // what this receive wants is behind the held frame
+    l.wanted.push_back({t, chan, tag, dst, bytes});
+    drain_in(peer);
+    return t;
+  }
   l.wanted.push_back({t, chan, tag, dst, bytes});
   return t;
 }
@@ -197,15 +214,25 @@ void Fabric::start_body(Link& l, int peer) {
     l.in_buf = w->buf;
     l.in_room = w->room;
     l.wanted.erase(w);
+  } else if (hold_us_ > 0 && l.in_head.bytes >= kHoldMin && l.wanted.empty()) {
+    l.held = true;
+    l.held_since = std::chrono::steady_clock::now();
+    return;
   } else {
-    l.parked.emplace_back();
-    Parked& p = l.parked.back();
-    p.chan = l.in_head.chan;
-    p.tag = l.in_head.tag;
-    p.bytes.resize(l.in_head.bytes);
-    l.in_parked = &p;
+    park_frame(l);
   }
   if (l.in_head.bytes == 0) end_body(l);
+}
+
+// The frame whose header is in l.in_head gets a private buffer until a receive asks for it.
+void Fabric::park_frame(Link& l) {
+  l.held = false;
+  l.parked.emplace_back();
+  Parked& p = l.parked.back();
+  p.chan = l.in_head.chan;
+  p.tag = l.in_head.tag;
+  p.bytes.resize(l.in_head.bytes);
+  l.in_parked = &p;
 }
 
 void Fabric::end_body(Link& l) {
@@ -252,7 +279,7 @@ ssize_t Fabric::pull(Link& l, char* into, size_t want) {
 
 void Fabric::drain_in(int peer) {
   Link& l = links_[peer];
-  while (!l.down) {
+  while (!l.down && !l.held) {
     char* into;
     size_t want;
     if (!l.in_body) {
@@ -315,6 +342,7 @@ void Fabric::link_down(int peer, const std::string& why) {
     }
   }
   l.in_body = false;
+  l.held = false;
   l.in_parked = nullptr;
   l.in_ticket = -1;
 }
@@ -328,9 +356,14 @@ bool Fabric::pump(int timeout_ms) {
   for (int i = 0; i < nprocs(); ++i) {
     Link& l = links_[i];
     if (i == self_ || l.down || l.fd < 0) continue;
+    if (l.held && std::chrono::steady_clock::now() - l.held_since > std::chrono::microseconds(hold_us_)) {
+      park_frame(l);  // nobody came for it: take it in as any early message
+      drain_in(i);
+      if (l.down) continue;
+    }
     pollfd p{};
     p.fd = l.fd;
-    p.events = POLLIN;
+    p.events = l.held ? 0 : POLLIN;  // a held frame's bytes wait in the socket
     if (!l.out.empty()) p.events |= POLLOUT;
     pf.push_back(p);
     who.push_back(i);
@@ -340,7 +373,11 @@ bool Fabric::pump(int timeout_ms) {
   if (rc <= 0) return false;
   for (size_t k = 0; k < pf.size(); ++k) {
     if (pf[k].revents & POLLOUT) flush_out(who[k]);
-    if (pf[k].revents & (POLLIN | POLLHUP | POLLERR)) drain_in(who[k]);
+    if (pf[k].revents & (POLLIN | POLLHUP | POLLERR)) {
+      Link& l = links_[who[k]];
+      if (l.held) park_frame(l);  // the peer hung up: read what it left
+      drain_in(who[k]);
+    }
   }
   return true;
 }

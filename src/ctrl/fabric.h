@@ -17,6 +17,7 @@
 #include <sys/types.h>
 
 #include <cstdint>
+#include <chrono>
 #include <deque>
 #include <list>
 #include <memory>
@@ -128,6 +129,11 @@ class Fabric : public Carrier {
     size_t in_room = 0;
     bool in_orphan = false;  // matched receive was cancelled: swallow the body
     Parked* in_parked = nullptr;
+    // The header of a large frame is in, nothing asks for it yet and nothing else is wanted from
+    // this peer: its body stays in the socket for a moment, so that a receive posted right after
+    // gets it straight into its buffer instead of through a parked copy.
+    bool held = false;
+    std::chrono::steady_clock::time_point held_since{};
     // read-ahead for headers and small bodies: [ahead_pos, ahead_end) is received but not consumed
     std::vector<char> ahead;
     size_t ahead_pos = 0, ahead_end = 0;
@@ -140,6 +146,7 @@ class Fabric : public Carrier {
   void drain_in(int peer);
   ssize_t pull(Link& l, char* into, size_t want);
   void start_body(Link& l, int peer);
+  void park_frame(Link& l);
   void end_body(Link& l);
   void link_down(int peer, const std::string& why);
   void pair_self();
@@ -157,7 +164,8 @@ class Fabric : public Carrier {
   std::list<SelfSend> self_sends_;
   std::recursive_mutex mu_;
   long wait_limit_ms_ = 0;  // 0 = wait forever
-  long spin_us_ = 2000;     // HXCCL_SPIN_US: how long a wait polls without news before it sleeps
+  long spin_us_ = 10000;    // HXCCL_SPIN_US: how long a wait polls without news before it sleeps
+  long hold_us_ = 200;      // HXCCL_HOLD_US: how long an unclaimed large frame stays held (0: never)
 };
 
 // A communicator's view of the fabric: ranks are positions in `members` (fabric process

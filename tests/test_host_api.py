@@ -139,6 +139,50 @@ def test_mixed_message_sizes_arrive_intact(spin_us):
     assert run_ranks(2, _burst, env={"HXCCL_SPIN_US": spin_us}) == [True, True]
 
 
+def _early_large(comm, rank, n):
+    """Large messages that arrive before anyone asks for them: taken straight into the receive
+    posted next, parked when something behind them is wanted first, parked when nobody comes."""
+    import time
+
+    twin = comm.split(0, rank)  # same members, its own channel on the same connections
+    big = lambda seed: np.random.default_rng(seed).integers(0, 255, 1 << 20).astype(np.uint8)  # noqa: E731
+    out = {}
+    if rank == 1:
+        comm.send(big(1), 0)                    # (a) early, asked for next
+        comm.send(big(2), 0)                    # (b) early, but the twin's message is wanted first
+        twin.send(np.array([42], np.int32), 0)
+        comm.send(big(3), 0)                    # (c) early, nobody asks while rank 0 waits for rank 2
+    elif rank == 0:
+        time.sleep(0.05)
+        a = np.zeros(1 << 20, np.uint8)
+        comm.recv(a, 1)
+        small = np.zeros(1, np.int32)
+        twin.recv(small, 1)
+        b = np.zeros(1 << 20, np.uint8)
+        comm.recv(b, 1)
+        late = np.zeros(1, np.int32)
+        comm.recv(late, 2)
+        c = np.zeros(1 << 20, np.uint8)
+        comm.recv(c, 1)
+        out = {"a": np.array_equal(a, big(1)), "b": np.array_equal(b, big(2)),
+               "c": np.array_equal(c, big(3)), "small": int(small[0]), "late": int(late[0])}
+    else:
+        time.sleep(0.15)
+        comm.send(np.array([7], np.int32), 0)
+    z = np.array([1], dtype=np.int32)
+    comm.all_reduce(z)
+    out["after"] = int(z[0])
+    twin.destroy()
+    return out
+
+
+@pytest.mark.parametrize("hold_us", ["200", "0", "1000000"])
+def test_large_messages_ahead_of_their_receives(hold_us):
+    res = run_ranks(3, _early_large, env={"HXCCL_HOLD_US": hold_us})
+    assert res[0] == {"a": True, "b": True, "c": True, "small": 42, "late": 7, "after": 3}
+    assert res[1]["after"] == 3 and res[2]["after"] == 3
+
+
 def _two_comm_group(comm, rank, n):
     """Crossed Send/Recv over two communicators in one group must not deadlock."""
     other = comm.split(0, rank)
