@@ -2,12 +2,24 @@
 
 #include <algorithm>
 #include <cstring>
+#include <memory>
 #include <vector>
 
 #include "math/reduce_host.h"
 
 namespace hx {
 namespace {
+// Working memory whose first use is a write: not cleared (clearing 64 MiB costs as much as
+// sending it once).
+class Scratch {
+ public:
+  explicit Scratch(size_t bytes) : mem_(bytes ? new char[bytes] : nullptr) {}
+  char* data() { return mem_.get(); }
+
+ private:
+  std::unique_ptr<char[]> mem_;
+};
+
 char* at(void* p, size_t off) { return static_cast<char*>(p) + off; }
 const char* at(const void* p, size_t off) { return static_cast<const char*>(p) + off; }
 #define HX_TRY(expr)                                  \
@@ -26,7 +38,7 @@ hxcclResult_t host_allreduce_ring(HostCtx c, const void* send, void* recv, size_
   if (send != recv) std::memmove(recv, send, count * es);
   if (c.n == 1 || count == 0) return hxcclSuccess;
   const int next = wrap(c.rank + 1, c.n), prev = wrap(c.rank - 1, c.n);
-  std::vector<char> inbox(ring_block(count, c.n, 0).len * es);
+  Scratch inbox(ring_block(count, c.n, 0).len * es);
   auto blk = [&](int i) { return ring_block(count, c.n, wrap(i, c.n)); };
   for (int hop = 0; hop < c.n - 1; ++hop) {
     const Span out = blk(c.rank - hop), in = blk(c.rank - hop - 1);
@@ -52,7 +64,7 @@ hxcclResult_t host_allreduce_doubling(HostCtx c, const void* send, void* recv, s
   int p = 1;
   while (2 * p <= c.n) p *= 2;
   const int spare = c.n - p;
-  std::vector<char> inbox(bytes);
+  Scratch inbox(bytes);
   const bool paired = c.rank < 2 * spare;
   if (paired && c.rank % 2 == 0) {
     HX_TRY(c.wire.send(c.rank + 1, recv, bytes));
@@ -84,21 +96,38 @@ hxcclResult_t host_allgather(HostCtx c, const void* send, void* recv, size_t blo
   return hxcclSuccess;
 }
 
-// Ring reduce-scatter on a private copy of the input (recv may point into send). The hops
-// are one block ahead of the AllReduce schedule so that rank r finishes with block r.
+// Ring reduce-scatter. The input is never written (recv may point into send): a hop sends
+// either an untouched input block or the block combined after the previous hop, and combines
+// the arriving block with the input's next block into the buffer it arrived in. The hops are
+// one block ahead of the AllReduce schedule so that rank r finishes with block r.
 hxcclResult_t host_reducescatter(HostCtx c, const void* send, void* recv, size_t per, int dt,
                                  int op) {
   const size_t block = per * dtype_size(dt);
   if (per == 0) return hxcclSuccess;
-  std::vector<char> work(block * c.n), inbox(block);
-  std::memcpy(work.data(), send, work.size());
-  const int next = wrap(c.rank + 1, c.n), prev = wrap(c.rank - 1, c.n);
-  for (int hop = 0; hop < c.n - 1; ++hop) {
-    const int out = wrap(c.rank - hop - 1, c.n), in = wrap(c.rank - hop - 2, c.n);
-    HX_TRY(c.wire.exchange(next, work.data() + out * block, block, prev, inbox.data(), block));
-    reduce_into(work.data() + in * block, inbox.data(), per, dt, op);
+  const char* mine = at(send, size_t(c.rank) * block);
+  if (c.n == 1) {
+    if (recv != mine) std::memmove(recv, mine, block);
+    return hxcclSuccess;
   }
-  std::memcpy(recv, work.data() + c.rank * block, block);
+  Scratch two(2 * block);
+  const int next = wrap(c.rank + 1, c.n), prev = wrap(c.rank - 1, c.n);
+  const char* leaving = at(send, size_t(wrap(c.rank - 1, c.n)) * block);
+  for (int hop = 0; hop < c.n - 1; ++hop) {
+    const int in = wrap(c.rank - hop - 2, c.n);
+    char* inbox = two.data() + (hop & 1) * block;
+    HX_TRY(c.wire.exchange(next, leaving, block, prev, inbox, block));
+    const char* local = at(send, size_t(in) * block);
+    if (hop < c.n - 2) {
+      combine(inbox, local, inbox, per, dt, op);
+      leaving = inbox;
+      continue;
+    }
+    // the last block is this rank's: straight into recv unless recv overlaps it out of step
+    char* out = static_cast<char*>(recv);
+    const bool skewed = out != local && out < local + block && local < out + block;
+    combine(skewed ? inbox : out, local, inbox, per, dt, op);
+    if (skewed) std::memmove(out, inbox, block);
+  }
   return hxcclSuccess;
 }
 
@@ -155,7 +184,7 @@ hxcclResult_t host_reduce(HostCtx c, const void* send, void* recv, size_t count,
   const int pos = wrap(c.rank - root, c.n);
   auto rank_at = [&](int v) { return (v + root) % c.n; };
   if (bytes < kTreeMaxBytes) {
-    std::vector<char> inbox(bytes);
+    Scratch inbox(bytes);
     for (int bit = 1; bit < c.n; bit <<= 1) {
       if (pos & bit) return c.wire.send(rank_at(pos - bit), acc, bytes);
       if (pos + bit < c.n) {
@@ -167,7 +196,7 @@ hxcclResult_t host_reduce(HostCtx c, const void* send, void* recv, size_t count,
   }
   // Two inboxes of one piece each (a multiple of every element size): while the combined piece
   // k leaves for the predecessor, piece k+1 of the successor arrives in the other inbox.
-  std::vector<char> inbox(pos < c.n - 1 ? 2 * kChainPiece : 0);
+  Scratch inbox(pos < c.n - 1 ? 2 * kChainPiece : 0);
   auto piece = [&](size_t off) { return std::min(kChainPiece, bytes - off); };
   if (pos < c.n - 1) HX_TRY(c.wire.recv(rank_at(pos + 1), inbox.data(), piece(0)));
   for (size_t off = 0, k = 0; off < bytes; off += kChainPiece, ++k) {
