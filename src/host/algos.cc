@@ -35,21 +35,31 @@ const char* at(const void* p, size_t off) { return static_cast<const char*>(p) +
 hxcclResult_t host_allreduce_ring(HostCtx c, const void* send, void* recv, size_t count, int dt,
                                   int op) {
   const size_t es = dtype_size(dt);
-  if (send != recv) std::memmove(recv, send, count * es);
-  if (c.n == 1 || count == 0) return hxcclSuccess;
+  if (c.n == 1 || count == 0) {
+    if (send != recv && count) std::memmove(recv, send, count * es);
+    return hxcclSuccess;
+  }
+  // Out of place the input is read where it lies: every block of recv is written by a combine
+  // or by the all-gather. Buffers that overlap without being equal are first made one.
+  const char* lo = static_cast<const char*>(send);
+  char* res = static_cast<char*>(recv);
+  if (lo != res && lo < res + count * es && res < lo + count * es) {
+    std::memmove(res, lo, count * es);
+    lo = res;
+  }
   const int next = wrap(c.rank + 1, c.n), prev = wrap(c.rank - 1, c.n);
   Scratch inbox(ring_block(count, c.n, 0).len * es);
   auto blk = [&](int i) { return ring_block(count, c.n, wrap(i, c.n)); };
   for (int hop = 0; hop < c.n - 1; ++hop) {
     const Span out = blk(c.rank - hop), in = blk(c.rank - hop - 1);
-    HX_TRY(c.wire.exchange(next, at(recv, out.off * es), out.len * es, prev, inbox.data(),
-                           in.len * es));
-    reduce_into(at(recv, in.off * es), inbox.data(), in.len, dt, op);
+    const char* leaving = (hop == 0 ? lo : res) + out.off * es;
+    HX_TRY(c.wire.exchange(next, leaving, out.len * es, prev, inbox.data(), in.len * es));
+    combine(res + in.off * es, lo + in.off * es, inbox.data(), in.len, dt, op);
   }
   for (int hop = 0; hop < c.n - 1; ++hop) {
     const Span out = blk(c.rank + 1 - hop), in = blk(c.rank - hop);
-    HX_TRY(c.wire.exchange(next, at(recv, out.off * es), out.len * es, prev,
-                           at(recv, in.off * es), in.len * es));
+    HX_TRY(c.wire.exchange(next, res + out.off * es, out.len * es, prev, res + in.off * es,
+                           in.len * es));
   }
   return hxcclSuccess;
 }
