@@ -254,12 +254,21 @@ hxcclResult_t host_scatter(HostCtx c, const void* send, void* recv, size_t block
 hxcclResult_t host_alltoallv(HostCtx c, const char* send, const size_t* sbytes,
                              const size_t* soff, char* recv, const size_t* rbytes,
                              const size_t* roff) {
-  if (rbytes[c.rank]) std::memmove(recv + roff[c.rank], send + soff[c.rank], rbytes[c.rank]);
+  // every receive is posted before the first send, then all pairs move at once: one message
+  // per pair and direction, so nothing can be mismatched
   for (int k = 1; k < c.n; ++k) {
-    const int to = (c.rank + k) % c.n, from = wrap(c.rank - k, c.n);
-    HX_TRY(c.wire.exchange(to, send + soff[to], sbytes[to], from, recv + roff[from], rbytes[from]));
+    const int from = wrap(c.rank - k, c.n);
+    c.wire.post_recv(from, recv + roff[from], rbytes[from], kTagColl);
   }
-  return hxcclSuccess;
+  for (int k = 1; k < c.n; ++k) {
+    const int to = (c.rank + k) % c.n;
+    if (hxcclResult_t r = c.wire.post_send(to, send + soff[to], sbytes[to], kTagColl)) {
+      c.wire.cancel_all();
+      return r;
+    }
+  }
+  if (rbytes[c.rank]) std::memmove(recv + roff[c.rank], send + soff[c.rank], rbytes[c.rank]);
+  return c.wire.finish_all();
 }
 
 }  // namespace hx
