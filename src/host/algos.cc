@@ -20,6 +20,18 @@ class Scratch {
   std::unique_ptr<char[]> mem_;
 };
 
+// A ring over large blocks moves them in rounds of at most kRingSlice bytes per block, so that
+// what a hop receives is still in the cache when it is combined or sent on. Every round cuts all
+// blocks at the same offsets: which rank's value meets which, and in what order, does not
+// change. The pieces of one block count as one message.
+constexpr size_t kRingSlice = size_t(1) << 20;
+
+// Elements [first, first + len) of a block, clipped to the block.
+Span slice_of(Span whole, size_t first, size_t len) {
+  if (first >= whole.len) return Span{whole.off + whole.len, 0};
+  return Span{whole.off + first, std::min(len, whole.len - first)};
+}
+
 char* at(void* p, size_t off) { return static_cast<char*>(p) + off; }
 const char* at(const void* p, size_t off) { return static_cast<const char*>(p) + off; }
 #define HX_TRY(expr)                                  \
@@ -48,18 +60,23 @@ hxcclResult_t host_allreduce_ring(HostCtx c, const void* send, void* recv, size_
     lo = res;
   }
   const int next = wrap(c.rank + 1, c.n), prev = wrap(c.rank - 1, c.n);
-  Scratch inbox(ring_block(count, c.n, 0).len * es);
-  auto blk = [&](int i) { return ring_block(count, c.n, wrap(i, c.n)); };
-  for (int hop = 0; hop < c.n - 1; ++hop) {
-    const Span out = blk(c.rank - hop), in = blk(c.rank - hop - 1);
-    const char* leaving = (hop == 0 ? lo : res) + out.off * es;
-    HX_TRY(c.wire.exchange(next, leaving, out.len * es, prev, inbox.data(), in.len * es));
-    combine(res + in.off * es, lo + in.off * es, inbox.data(), in.len, dt, op);
-  }
-  for (int hop = 0; hop < c.n - 1; ++hop) {
-    const Span out = blk(c.rank + 1 - hop), in = blk(c.rank - hop);
-    HX_TRY(c.wire.exchange(next, res + out.off * es, out.len * es, prev, res + in.off * es,
-                           in.len * es));
+  const size_t widest = ring_block(count, c.n, 0).len;  // block 0 is never the shorter one
+  const size_t per = std::max<size_t>(1, kRingSlice / es);
+  Scratch inbox(std::min(widest, per) * es);
+  for (size_t first = 0; first < widest; first += per) {
+    const bool more = first > 0;
+    auto blk = [&](int i) { return slice_of(ring_block(count, c.n, wrap(i, c.n)), first, per); };
+    for (int hop = 0; hop < c.n - 1; ++hop) {
+      const Span out = blk(c.rank - hop), in = blk(c.rank - hop - 1);
+      const char* leaving = (hop == 0 ? lo : res) + out.off * es;
+      HX_TRY(c.wire.exchange(next, leaving, out.len * es, prev, inbox.data(), in.len * es, more));
+      combine(res + in.off * es, lo + in.off * es, inbox.data(), in.len, dt, op);
+    }
+    for (int hop = 0; hop < c.n - 1; ++hop) {
+      const Span out = blk(c.rank + 1 - hop), in = blk(c.rank - hop);
+      HX_TRY(c.wire.exchange(next, res + out.off * es, out.len * es, prev, res + in.off * es,
+                             in.len * es, more));
+    }
   }
   return hxcclSuccess;
 }
@@ -99,9 +116,13 @@ hxcclResult_t host_allgather(HostCtx c, const void* send, void* recv, size_t blo
   if (send != at(recv, c.rank * block)) std::memmove(at(recv, c.rank * block), send, block);
   if (c.n == 1 || block == 0) return hxcclSuccess;
   const int next = wrap(c.rank + 1, c.n), prev = wrap(c.rank - 1, c.n);
-  for (int hop = 0; hop < c.n - 1; ++hop) {
-    const int out = wrap(c.rank - hop, c.n), in = wrap(c.rank - hop - 1, c.n);
-    HX_TRY(c.wire.exchange(next, at(recv, out * block), block, prev, at(recv, in * block), block));
+  for (size_t first = 0; first < block; first += kRingSlice) {
+    const size_t len = std::min(kRingSlice, block - first);
+    for (int hop = 0; hop < c.n - 1; ++hop) {
+      const int out = wrap(c.rank - hop, c.n), in = wrap(c.rank - hop - 1, c.n);
+      HX_TRY(c.wire.exchange(next, at(recv, out * block + first), len, prev,
+                             at(recv, in * block + first), len, first > 0));
+    }
   }
   return hxcclSuccess;
 }
@@ -112,32 +133,37 @@ hxcclResult_t host_allgather(HostCtx c, const void* send, void* recv, size_t blo
 // one block ahead of the AllReduce schedule so that rank r finishes with block r.
 hxcclResult_t host_reducescatter(HostCtx c, const void* send, void* recv, size_t per, int dt,
                                  int op) {
-  const size_t block = per * dtype_size(dt);
+  const size_t es = dtype_size(dt), block = per * es;
   if (per == 0) return hxcclSuccess;
   const char* mine = at(send, size_t(c.rank) * block);
   if (c.n == 1) {
     if (recv != mine) std::memmove(recv, mine, block);
     return hxcclSuccess;
   }
-  Scratch two(2 * block);
+  // the result goes straight into recv when recv is apart from the input or exactly this
+  // rank's block of it (the in-place form); any other overlap gets a private result
+  char* out = static_cast<char*>(recv);
+  const char* in_lo = at(send, 0);
+  const bool apart = out + block <= in_lo || in_lo + block * c.n <= out;
+  Scratch detour(apart || out == mine ? 0 : block);
+  char* result = detour.data() ? detour.data() : out;
+  const size_t slice = std::max<size_t>(1, kRingSlice / es);  // elements per round
+  Scratch two(2 * std::min(per, slice) * es);
   const int next = wrap(c.rank + 1, c.n), prev = wrap(c.rank - 1, c.n);
-  const char* leaving = at(send, size_t(wrap(c.rank - 1, c.n)) * block);
-  for (int hop = 0; hop < c.n - 1; ++hop) {
-    const int in = wrap(c.rank - hop - 2, c.n);
-    char* inbox = two.data() + (hop & 1) * block;
-    HX_TRY(c.wire.exchange(next, leaving, block, prev, inbox, block));
-    const char* local = at(send, size_t(in) * block);
-    if (hop < c.n - 2) {
-      combine(inbox, local, inbox, per, dt, op);
+  for (size_t first = 0; first < per; first += slice) {
+    const size_t len = std::min(slice, per - first), bytes = len * es;
+    auto part = [&](int b) { return at(send, size_t(wrap(b, c.n)) * block + first * es); };
+    const char* leaving = part(c.rank - 1);
+    for (int hop = 0; hop < c.n - 1; ++hop) {
+      char* inbox = two.data() + (hop & 1) * bytes;
+      HX_TRY(c.wire.exchange(next, leaving, bytes, prev, inbox, bytes, first > 0));
+      const char* local = part(c.rank - hop - 2);
+      char* into = hop < c.n - 2 ? inbox : result + first * es;
+      combine(into, local, inbox, len, dt, op);
       leaving = inbox;
-      continue;
     }
-    // the last block is this rank's: straight into recv unless recv overlaps it out of step
-    char* out = static_cast<char*>(recv);
-    const bool skewed = out != local && out < local + block && local < out + block;
-    combine(skewed ? inbox : out, local, inbox, per, dt, op);
-    if (skewed) std::memmove(out, inbox, block);
   }
+  if (result != out) std::memmove(out, result, block);
   return hxcclSuccess;
 }
 

@@ -9,11 +9,11 @@ bool HostWire::injected() {
   return true;
 }
 
-hxcclResult_t HostWire::post_send(int to, const void* buf, size_t bytes, int tag) {
+hxcclResult_t HostWire::post_send(int to, const void* buf, size_t bytes, int tag, bool fragment) {
   if (injected()) return hxcclSystemError;
   open_.push_back(ch_->post_send(to, tag, buf, bytes));
   bytes_sent += bytes;
-  ++msgs_sent;
+  if (!fragment) ++msgs_sent;
   return hxcclSuccess;
 }
 
@@ -70,9 +70,9 @@ void HostWire::cancel_all() {
 }
 
 hxcclResult_t HostWire::exchange(int to, const void* sbuf, size_t sbytes, int from, void* rbuf,
-                                 size_t rbytes) {
+                                 size_t rbytes, bool fragment) {
   post_recv(from, rbuf, rbytes, kTagColl);
-  if (hxcclResult_t r = post_send(to, sbuf, sbytes, kTagColl)) {
+  if (hxcclResult_t r = post_send(to, sbuf, sbytes, kTagColl, fragment)) {
     cancel_all();
     return r;
   }

@@ -16,12 +16,14 @@ class HostWire {
   explicit HostWire(std::shared_ptr<Channel> ch) : ch_(std::move(ch)) {}
 
   // blocking forms used by the collective algorithms (tag kTagColl)
+  // `fragment`: the send continues a message that was counted already (bytes count, the
+  // message does not)
   hxcclResult_t exchange(int to, const void* sbuf, size_t sbytes, int from, void* rbuf,
-                         size_t rbytes);
+                         size_t rbytes, bool fragment = false);
   hxcclResult_t send(int to, const void* buf, size_t bytes);
   hxcclResult_t recv(int from, void* buf, size_t bytes);
   // non-blocking forms: post, then finish_all (blocking) or step (one pass)
-  hxcclResult_t post_send(int to, const void* buf, size_t bytes, int tag);
+  hxcclResult_t post_send(int to, const void* buf, size_t bytes, int tag, bool fragment = false);
   hxcclResult_t post_recv(int from, void* buf, size_t bytes, int tag);
   hxcclResult_t finish_all();
   // One non-blocking pass over everything posted. *done turns true when nothing is left; the

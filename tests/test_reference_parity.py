@@ -280,6 +280,11 @@ def make_cases():
     for dt, bits in ((L.FLOAT16, 0x3000), (L.BFLOAT16, 0x3F00), (L.INT32, 3), (L.FLOAT8E5M2, 0x3E), (L.FLOAT32, 0xBE800000)):
         cases.append(("premul", dt, bits, 1001, len(cases)))
         cases.append(("premul", dt, bits, (64 << 10) // L.DTYPE_SIZE[dt] + 7, len(cases)))
+    # ring blocks above 1 MiB travel in several rounds here; results and message counts stay the reference's
+    cases.append(("allreduce", L.FLOAT32, L.SUM, (9 << 20) // 4 + 5, len(cases)))
+    cases.append(("allreduce", L.BFLOAT16, L.AVG, (9 << 20) // 2 + 3, len(cases)))
+    cases.append(("reducescatter", L.FLOAT32, L.SUM, 300_001, len(cases)))
+    cases.append(("allgather", L.UINT8, 0, (3 << 19) + 3, len(cases)))
     return cases
 
 
