@@ -120,3 +120,16 @@ def test_gpu_numa_cpus_reads_sysfs(tmp_path):
     assert gpu_numa_cpus("0000:1b:00.0", sysfs=str(tmp_path)) == set()
     assert gpu_numa_cpus("0000:ff:00.0", sysfs=str(tmp_path)) == set()
     assert _parse_cpulist("0,2-3") == {0, 2, 3}
+
+
+def test_host_benchmark_against_the_reference_runs():
+    """bench/host_vs_reference.py: one JSON line per size, with the reference's columns filled
+    when the reference library has been built (baseline/build_ref.py)."""
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench", "host_vs_reference.py"), "--ranks", "2",
+                          "--iters", "3", "--rounds", "1", "--coll", "allgather", "--sizes", "256,70000"],
+                         capture_output=True, text=True, timeout=300, check=True)
+    rows = [json.loads(ln) for ln in out.stdout.splitlines() if ln.startswith("{")]
+    assert [r["bytes"] for r in rows] == [256, 70000] and all(r["coll"] == "allgather" for r in rows)
+    assert all(r["hxccl_us"] > 0 and r["hxccl_busbw_GBps"] >= 0 for r in rows)
+    built = os.path.exists(os.path.join(ROOT, "baseline", "_ref", "libhxccl_ref.so"))
+    assert all((r["reference_us"] is not None) == built for r in rows)
