@@ -1,7 +1,6 @@
 #include "fabric.h"
 
 #include <errno.h>
-#include <cstdio>
 #include <poll.h>
 #include <sched.h>
 #include <sys/socket.h>
@@ -353,13 +352,21 @@ bool Fabric::pump(int timeout_ms) {
   std::vector<int>& who = poll_who_;
   pf.clear();
   who.clear();
+  bool took_in = false;
   for (int i = 0; i < nprocs(); ++i) {
     Link& l = links_[i];
     if (i == self_ || l.down || l.fd < 0) continue;
-    if (l.held && std::chrono::steady_clock::now() - l.held_since > std::chrono::microseconds(hold_us_)) {
-      park_frame(l);  // nobody came for it: take it in as any early message
-      drain_in(i);
-      if (l.down) continue;
+    if (l.held) {
+      const auto age = std::chrono::duration_cast<std::chrono::microseconds>(
+                           std::chrono::steady_clock::now() - l.held_since).count();
+      if (age > hold_us_) {
+        park_frame(l);  // nobody came for it: take it in as any early message
+        drain_in(i);
+        took_in = true;
+        if (l.down) continue;
+      } else if (timeout_ms > 0) {  // a sleep must not outlast the hold
+        timeout_ms = std::min<long>(timeout_ms, 1 + (hold_us_ - age) / 1000);
+      }
     }
     pollfd p{};
     p.fd = l.fd;
@@ -368,9 +375,9 @@ bool Fabric::pump(int timeout_ms) {
     pf.push_back(p);
     who.push_back(i);
   }
-  if (pf.empty()) return false;
-  const int rc = ::poll(pf.data(), pf.size(), timeout_ms);
-  if (rc <= 0) return false;
+  if (pf.empty()) return took_in;
+  const int rc = ::poll(pf.data(), pf.size(), took_in ? 0 : timeout_ms);
+  if (rc <= 0) return took_in;
   for (size_t k = 0; k < pf.size(); ++k) {
     if (pf[k].revents & POLLOUT) flush_out(who[k]);
     if (pf[k].revents & (POLLIN | POLLHUP | POLLERR)) {
