@@ -5,6 +5,7 @@
 #include <climits>
 #include <cstdlib>
 #include <cstring>
+#include <memory>
 #include <vector>
 
 #include "core/comm.h"
@@ -40,13 +41,14 @@ hxcclResult_t dev_done(hxcclComm* c, hxcclResult_t r, Traffic t) {
 }
 HostCtx ctx(hxcclComm* c) { return HostCtx{*c->wire, c->rank, c->nranks}; }
 
-// input * scalar into `tmp` when the plan asks for it; returns the buffer to reduce from
-const void* host_premul(const OpPlan& p, const void* send, size_t count, int dt,
-                        std::vector<char>& tmp) {
+// input * scalar into `tmp` when the plan asks for it; returns the buffer to reduce from.
+// `tmp` is written before it is read, so it is not cleared.
+using HostTmp = std::unique_ptr<char[]>;
+const void* host_premul(const OpPlan& p, const void* send, size_t count, int dt, HostTmp& tmp) {
   if (!p.premul || count == 0) return send;
-  tmp.resize(count * dtype_size(dt));
-  scale_into(tmp.data(), send, count, dt, p.scalar);
-  return tmp.data();
+  tmp.reset(new char[count * dtype_size(dt)]);
+  scale_into(tmp.get(), send, count, dt, p.scalar);
+  return tmp.get();
 }
 void host_finish(const OpPlan& p, void* buf, size_t count, int dt) {
   if (p.postdiv && count) divide_trunc(buf, count, dt, p.divisor);
@@ -126,8 +128,19 @@ hxcclResult_t hxcclAllReduce(const void* send, void* recv, size_t count, hxcclDa
     if (path == Path::Device)
       return dev_done(c, c->device.path->allreduce(send, recv, count, dt, plan, order, stream),
                       traffic_allreduce(order, c->rank, c->nranks, count, es));
-    std::vector<char> tmp;
-    const void* in = host_premul(plan, send, count, dt, tmp);
+    // the scaled input of an AllReduce can live in the result buffer: the algorithms work in
+    // place (unless the two buffers overlap without being equal)
+    HostTmp tmp;
+    const void* in = send;
+    const char* s0 = static_cast<const char*>(send);
+    char* r0 = static_cast<char*>(recv);
+    const bool apart = s0 == r0 || s0 + count * es <= r0 || r0 + count * es <= s0;
+    if (plan.premul && count && apart) {
+      scale_into(recv, send, count, dt, plan.scalar);
+      in = recv;
+    } else {
+      in = host_premul(plan, send, count, dt, tmp);
+    }
     hxcclResult_t r = order == kOrderRing
                           ? host_allreduce_ring(ctx(c), in, recv, count, dt, plan.base)
                           : host_allreduce_doubling(ctx(c), in, recv, count, dt, plan.base);
@@ -191,7 +204,7 @@ hxcclResult_t hxcclReduceScatter(const void* send, void* recv, size_t recvcount,
     if (path == Path::Device)
       return dev_done(c, c->device.path->reducescatter(send, recv, recvcount, dt, plan, stream),
                       traffic_ring_blocks(c->nranks, block));
-    std::vector<char> tmp;
+    HostTmp tmp;
     const void* in = host_premul(plan, send, recvcount * c->nranks, dt, tmp);
     hxcclResult_t r = host_reducescatter(ctx(c), in, recv, recvcount, dt, plan.base);
     if (r == hxcclSuccess) host_finish(plan, recv, recvcount, dt);
@@ -240,7 +253,7 @@ hxcclResult_t hxcclReduce(const void* send, void* recv, size_t count, hxcclDataT
     if (path == Path::Device)
       return dev_done(c, c->device.path->reduce(send, recv, count, dt, plan, root, stream),
                       traffic_reduce(c->rank, c->nranks, bytes, root));
-    std::vector<char> tmp;
+    HostTmp tmp;
     const void* in = host_premul(plan, send, count, dt, tmp);
     hxcclResult_t r = host_reduce(ctx(c), in, recv, count, dt, plan.base, root);
     if (r == hxcclSuccess && is_root) host_finish(plan, recv, count, dt);  // divide once
