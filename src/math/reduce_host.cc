@@ -2,6 +2,13 @@
 
 #include <cstring>
 
+// The loops of this file are the host data path: let the compiler unroll and vectorise them
+// whatever level the rest of the library is built at (no value-changing option is implied;
+// contraction stays off through the command line).
+#if defined(__GNUC__) && !defined(__clang__)
+#pragma GCC optimize("O3")
+#endif
+
 namespace hx {
 
 namespace {
@@ -18,24 +25,48 @@ void arith_tiles(F* out, const F* a, const F* b, size_t count, int op) {
   F tile[kTile];
   for (size_t i0 = 0; i0 < count; i0 += kTile) {
     const size_t n = count - i0 < kTile ? count - i0 : kTile;
-    bool special = false;
     if (op == kSum) {
-      for (size_t i = 0; i < n; ++i) {
-        tile[i] = a[i0 + i] + b[i0 + i];
-        special |= tile[i] != tile[i];
-      }
+      for (size_t i = 0; i < n; ++i) tile[i] = a[i0 + i] + b[i0 + i];
     } else {
-      for (size_t i = 0; i < n; ++i) {
-        tile[i] = a[i0 + i] * b[i0 + i];
-        special |= tile[i] != tile[i];
-      }
+      for (size_t i = 0; i < n; ++i) tile[i] = a[i0 + i] * b[i0 + i];
     }
+    int special = 0;  // a loop of its own: both then vectorise
+    for (size_t i = 0; i < n; ++i) special += tile[i] != tile[i];
     if (special) {
       for (size_t i = 0; i < n; ++i) out[i0 + i] = arith(a[i0 + i], b[i0 + i], op);
     } else {
       std::memcpy(out + i0, tile, n * sizeof(F));
     }
   }
+}
+// The same for value * scalar.
+template <typename F>
+void scale_tiles(F* out, const F* src, F k, size_t count) {
+  constexpr size_t kTile = 256;
+  F tile[kTile];
+  for (size_t i0 = 0; i0 < count; i0 += kTile) {
+    const size_t n = count - i0 < kTile ? count - i0 : kTile;
+    for (size_t i = 0; i < n; ++i) tile[i] = src[i0 + i] * k;
+    int special = 0;
+    for (size_t i = 0; i < n; ++i) special += tile[i] != tile[i];
+    if (special) {
+      for (size_t i = 0; i < n; ++i) out[i0 + i] = arith(src[i0 + i], k, kProd);
+    } else {
+      std::memcpy(out + i0, tile, n * sizeof(F));
+    }
+  }
+}
+template <typename T>
+bool fast_scale(T*, const T*, T, size_t) { return false; }
+template <>
+bool fast_scale<float>(float* o, const float* s, float k, size_t n) {
+  scale_tiles(o, s, k, n);
+  return true;
+}
+template <>
+bool fast_scale<double>(double* o, const double* s, double k, size_t n) {
+  scale_tiles(o, s, k, n);
+  return true;
 }
 template <typename T>
 bool fast_arith(T*, const T*, const T*, size_t, int) { return false; }
@@ -77,6 +108,7 @@ void scale_into(void* dst, const void* src, size_t count, int dt, const void* sc
     std::memcpy(&k, scalar, sizeof(T));
     T* o = static_cast<T*>(dst);
     const T* s = static_cast<const T*>(src);
+    if (fast_scale<T>(o, s, k, count)) break;
     for (size_t i = 0; i < count; ++i) o[i] = scale(s[i], k);
   })
 }
