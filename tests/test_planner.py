@@ -135,3 +135,19 @@ def test_compiled_in_table_parses():
     lib = L.lib()
     lib.hxcclTestTableRows.restype = C.c_int
     assert lib.hxcclTestTableRows() == len(rows)
+
+
+def test_explain_tool_prints_the_choice_per_size(capsys, monkeypatch):
+    """python -m hxccl_b200.explain: one line per size with the variant and who decided."""
+    from hxccl_b200 import explain
+
+    monkeypatch.delenv("HXCCL_TUNE_FILE", raising=False)
+    assert explain.main(["--ranks", "8", "--from", "8", "--to", "256M"]) == 0
+    lines = capsys.readouterr().out.splitlines()
+    assert lines[0].split()[:2] == ["bytes", "variant"] and len(lines) == 1 + 26
+    first, last = lines[1].split(), lines[-1].split()
+    assert first[:2] == ["8", "lines"] and last[:2] == [str(256 << 20), "ring"]
+    name, tabled, shape = explain.choose(100, L.FLOAT32, 3)  # nothing tabled below four ranks but n=2: its rows serve
+    assert name in explain.VARIANTS.values() and len(shape) == 3
+    with pytest.raises(ValueError):
+        explain.choose(100, L.FLOAT32, 1)
