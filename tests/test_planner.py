@@ -147,7 +147,7 @@ def test_explain_tool_prints_the_choice_per_size(capsys, monkeypatch):
     assert lines[0].split()[:2] == ["bytes", "variant"] and len(lines) == 1 + 26
     first, last = lines[1].split(), lines[-1].split()
     assert first[:2] == ["8", "lines"] and last[:2] == [str(256 << 20), "ring"]
-    name, tabled, shape = explain.choose(100, L.FLOAT32, 3)  # nothing tabled below four ranks but n=2: its rows serve
+    name, tabled, shape = explain.choose(100, L.FLOAT32, 3)  # three ranks use the rows measured for two
     assert name in explain.VARIANTS.values() and len(shape) == 3
     with pytest.raises(ValueError):
         explain.choose(100, L.FLOAT32, 1)
