@@ -5,7 +5,7 @@ of baseline/build_ref.py (baseline/_ref/libhxccl_ref.so).
 
     python bench/host_vs_reference.py [--ranks 4] [--iters 20] [--coll allreduce]
 
-Inputs are fp32, uniform in (-1, 1) from seed 1234 + rank. `--coll` is allreduce, allgather, reducescatter, broadcast or alltoall; `bytes` is the size of the
+Inputs are uniform in (-1, 1) from seed 1234 + rank in `--dtype` (float32 unless given). `--coll` is allreduce, allgather, reducescatter, broadcast or alltoall; `bytes` is the size of the
 larger of the two buffers of a rank (the whole gathered vector for allgather, the whole input for
 reducescatter and alltoall).
 
@@ -29,6 +29,11 @@ ROOT = Path(__file__).resolve().parent.parent
 sys.path.insert(0, str(ROOT))
 REF = ROOT / "baseline" / "_ref" / "libhxccl_ref.so"
 STUB = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "lib64" / "stubs" / "libcuda.so"
+
+
+# name -> (hxcclDataType_t, element bytes)
+DTYPES = {"int32": (2, 4), "float16": (6, 2), "float32": (7, 4), "float64": (8, 8), "bfloat16": (9, 2),
+          "float8e4m3": (10, 1)}
 
 
 class Id(C.Structure):
@@ -58,7 +63,7 @@ def load(which: str):
     return lib
 
 
-def child(which, coll, op, rank, n, sizes, iters, id_q, out_q):
+def child(which, coll, op, dtype, rank, n, sizes, iters, id_q, out_q):
     import numpy as np
 
     os.environ["HXCCL_DEVICE"] = "0"
@@ -79,16 +84,25 @@ def child(which, coll, op, rank, n, sizes, iters, id_q, out_q):
 
     rows = []
     for size in sizes:
-        whole = max(n, size // 4 // n * n)  # fp32 elements, a multiple of the rank count
-        x = np.random.default_rng(1234 + rank).uniform(-1.0, 1.0, whole).astype(np.float32)
+        code, es = DTYPES[dtype]
+        whole = max(n, size // es // n * n)  # elements, a multiple of the rank count
+        u = np.random.default_rng(1234 + rank).uniform(-1.0, 1.0, whole)
+        if dtype == "bfloat16":      # the upper half of the fp32 pattern
+            x = (u.astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+        elif dtype == "float8e4m3":  # small finite codes of either sign
+            x = (np.random.default_rng(1234 + rank).integers(0, 256, whole) & 0xBF).astype(np.uint8)
+        elif dtype == "int32":
+            x = (u * 1000).astype(np.int32)
+        else:
+            x = u.astype({"float32": np.float32, "float16": np.float16, "float64": np.float64}[dtype])
         y = np.empty_like(x)
         xp, yp, part = x.ctypes.data, y.ctypes.data, whole // n
         call = {
-            "allreduce": lambda: lib.hxcclAllReduce(xp, yp, whole, 7, op, comm, None),
-            "allgather": lambda: lib.hxcclAllGather(xp, yp, part, 7, comm, None),
-            "reducescatter": lambda: lib.hxcclReduceScatter(xp, yp, part, 7, op, comm, None),
-            "broadcast": lambda: lib.hxcclBroadcast(xp, yp, whole, 7, 0, comm, None),
-            "alltoall": lambda: lib.hxcclAlltoAll(xp, yp, part, 7, comm, None),
+            "allreduce": lambda: lib.hxcclAllReduce(xp, yp, whole, code, op, comm, None),
+            "allgather": lambda: lib.hxcclAllGather(xp, yp, part, code, comm, None),
+            "reducescatter": lambda: lib.hxcclReduceScatter(xp, yp, part, code, op, comm, None),
+            "broadcast": lambda: lib.hxcclBroadcast(xp, yp, whole, code, 0, comm, None),
+            "alltoall": lambda: lib.hxcclAlltoAll(xp, yp, part, code, comm, None),
         }[coll]
         times = []
         for it in range(iters + 5):
@@ -102,10 +116,10 @@ def child(which, coll, op, rank, n, sizes, iters, id_q, out_q):
     out_q.put((rank, rows))
 
 
-def run(which, coll, op, n, sizes, iters):
+def run(which, coll, op, dtype, n, sizes, iters):
     ctx = mp.get_context("spawn")
     id_q, out_q = ctx.Queue(), ctx.Queue()
-    procs = [ctx.Process(target=child, args=(which, coll, op, r, n, sizes, iters, id_q, out_q)) for r in range(n)]
+    procs = [ctx.Process(target=child, args=(which, coll, op, dtype, r, n, sizes, iters, id_q, out_q)) for r in range(n)]
     for p in procs:
         p.start()
     got = dict(out_q.get(timeout=600) for _ in range(n))
@@ -124,6 +138,7 @@ def main() -> int:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--coll", default="allreduce",
                     choices=["allreduce", "allgather", "reducescatter", "broadcast", "alltoall"])
+    ap.add_argument("--dtype", default="float32", choices=sorted(DTYPES))
     ap.add_argument("--op", default="sum", choices=["sum", "avg"], help="for allreduce and reducescatter")
     ap.add_argument("--rounds", type=int, default=3, help="alternating runs of each library")
     ap.add_argument("--sizes", default="256,16384,65536,1048576,4194304,16777216,67108864")
@@ -134,17 +149,17 @@ def main() -> int:
     ours, ref = None, None
     for _ in range(max(1, args.rounds)):
         op = {"sum": 0, "avg": 4}[args.op]
-        a = run("hxccl", args.coll, op, args.ranks, sizes, args.iters)
+        a = run("hxccl", args.coll, op, args.dtype, args.ranks, sizes, args.iters)
         ours = a if ours is None else [min(x, y) for x, y in zip(ours, a)]
         if REF.exists():
-            b = run("reference", args.coll, op, args.ranks, sizes, args.iters)
+            b = run("reference", args.coll, op, args.dtype, args.ranks, sizes, args.iters)
             ref = b if ref is None else [min(x, y) for x, y in zip(ref, b)]
     if ref is None:
         ref = [None] * len(sizes)
     n = args.ranks
     f = {"allreduce": 2.0 * (n - 1) / n, "broadcast": 1.0}.get(args.coll, (n - 1) / n)
     for size, a, b in zip(sizes, ours, ref):
-        print(json.dumps({"coll": args.coll, "op": args.op, "ranks": args.ranks, "bytes": size, "hxccl_us": round(a * 1e6, 1),
+        print(json.dumps({"coll": args.coll, "op": args.op, "dtype": args.dtype, "ranks": args.ranks, "bytes": size, "hxccl_us": round(a * 1e6, 1),
                           "hxccl_busbw_GBps": round(size / a / 1e9 * f, 3),
                           "reference_us": None if b is None else round(b * 1e6, 1),
                           "reference_busbw_GBps": None if b is None else round(size / b / 1e9 * f, 3),

@@ -1,6 +1,10 @@
 #include "reduce_host.h"
 
 #include <cstring>
+#include <mutex>
+#if defined(__x86_64__) && defined(__GNUC__)
+#include <immintrin.h>
+#endif
 
 // The loops of this file are the host data path: let the compiler unroll and vectorise them
 // whatever level the rest of the library is built at (no value-changing option is implied;
@@ -68,8 +72,74 @@ bool fast_scale<double>(double* o, const double* s, double k, size_t n) {
   scale_tiles(o, s, k, n);
   return true;
 }
+// The 8-bit float types have 256 x 256 operand pairs: the element rule is evaluated once per
+// pair into a 64 KiB table per type and operator, on first use, and a reduce is one lookup per
+// element after that (the rule itself decodes to float, combines, and rounds back per element).
+template <typename T>
+const uint8_t* pair_table(int op) {
+  static uint8_t table[4][256 * 256];
+  static std::once_flag built[4];
+  std::call_once(built[op], [op] {
+    for (int a = 0; a < 256; ++a)
+      for (int b = 0; b < 256; ++b)
+        table[op][a * 256 + b] = apply(T{uint8_t(a)}, T{uint8_t(b)}, op).b;
+  });
+  return table[op];
+}
+template <typename T>
+bool fast_pairs(T*, const T*, const T*, size_t, int) { return false; }
+template <typename T>
+bool lookup_pairs(T* o, const T* a, const T* b, size_t n, int op) {
+  if (op < 0 || op >= 4) return false;
+  const uint8_t* t = pair_table<T>(op);
+  for (size_t i = 0; i < n; ++i) o[i].b = t[a[i].b * 256 + b[i].b];
+  return true;
+}
+template <>
+bool fast_pairs<e4m3>(e4m3* o, const e4m3* a, const e4m3* b, size_t n, int op) { return lookup_pairs(o, a, b, n, op); }
+template <>
+bool fast_pairs<e5m2>(e5m2* o, const e5m2* a, const e5m2* b, size_t n, int op) { return lookup_pairs(o, a, b, n, op); }
+#if defined(__x86_64__) && defined(__GNUC__)
+#define HX_HAVE_F16C_PATH 1
+// fp16 Sum / Prod with the machine's half <-> float conversions, eight elements at a time. The
+// conversions are exact (widening) and round to nearest even with gradual underflow and
+// overflow to infinity (narrowing), as the element rule does; the rule differs only in what
+// NaN comes out (always the canonical one), which is patched in afterwards.
+__attribute__((target("avx2,f16c"))) void f16_arith_x86(uint16_t* o, const uint16_t* a, const uint16_t* b,
+                                                       size_t n, bool sum) {
+  const __m128i exp = _mm_set1_epi16(0x7c00), man = _mm_set1_epi16(0x03ff);
+  const __m128i canon = _mm_set1_epi16(0x7e00), zero = _mm_setzero_si128();
+  size_t i = 0;
+  for (; i + 8 <= n; i += 8) {
+    const __m256 fa = _mm256_cvtph_ps(_mm_loadu_si128(reinterpret_cast<const __m128i*>(a + i)));
+    const __m256 fb = _mm256_cvtph_ps(_mm_loadu_si128(reinterpret_cast<const __m128i*>(b + i)));
+    const __m256 r = sum ? _mm256_add_ps(fa, fb) : _mm256_mul_ps(fa, fb);
+    __m128i h = _mm256_cvtps_ph(r, _MM_FROUND_TO_NEAREST_INT | _MM_FROUND_NO_EXC);
+    const __m128i all_ones_exp = _mm_cmpeq_epi16(_mm_and_si128(h, exp), exp);
+    const __m128i no_mantissa = _mm_cmpeq_epi16(_mm_and_si128(h, man), zero);
+    const __m128i nan = _mm_andnot_si128(no_mantissa, all_ones_exp);
+    h = _mm_blendv_epi8(h, canon, nan);
+    _mm_storeu_si128(reinterpret_cast<__m128i*>(o + i), h);
+  }
+  for (; i < n; ++i) o[i] = apply(f16{a[i]}, f16{b[i]}, sum ? kSum : kProd).b;
+}
+bool f16_hw() {
+  static const bool yes = __builtin_cpu_supports("avx2") && __builtin_cpu_supports("f16c");
+  return yes;
+}
+#endif
 template <typename T>
 bool fast_arith(T*, const T*, const T*, size_t, int) { return false; }
+#ifdef HX_HAVE_F16C_PATH
+template <>
+bool fast_arith<f16>(f16* o, const f16* a, const f16* b, size_t n, int op) {
+  if (!f16_hw()) return false;
+  static_assert(sizeof(f16) == 2, "f16 is its 16 bits");
+  f16_arith_x86(reinterpret_cast<uint16_t*>(o), reinterpret_cast<const uint16_t*>(a),
+                reinterpret_cast<const uint16_t*>(b), n, op == kSum);
+  return true;
+}
+#endif
 template <>
 bool fast_arith<float>(float* o, const float* a, const float* b, size_t n, int op) {
   arith_tiles(o, a, b, n, op);
@@ -88,6 +158,7 @@ void combine(void* out, const void* in_a, const void* in_b, size_t count, int dt
     const T* a = static_cast<const T*>(in_a);
     const T* b = static_cast<const T*>(in_b);
     if ((op == kSum || op == kProd) && fast_arith<T>(o, a, b, count, op)) break;
+    if (count >= 4096 && fast_pairs<T>(o, a, b, count, op)) break;  // small calls do not pay for the table
     switch (op) {  // hoisted so each loop body is branch-free
       case kSum: for (size_t i = 0; i < count; ++i) o[i] = apply(a[i], b[i], kSum); break;
       case kProd: for (size_t i = 0; i < count; ++i) o[i] = apply(a[i], b[i], kProd); break;

@@ -149,3 +149,41 @@ def test_fp8_sum_and_product_same_through_half():
             ef = np.array([enc(dt, float(x)) for x in via_float.flatten()[::37]])
             eh = np.array([enc(dt, float(x)) for x in via_half.flatten()[::37]])
             assert np.array_equal(ef, eh)
+
+
+def _host_reduce(dst, src, dt, op, chunk=None):
+    """dst = dst (op) src through hxcclHostReduce, whole or in calls of `chunk` elements."""
+    lib = L.lib()
+    lib.hxcclHostReduce.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int]
+    n, es = dst.size, dst.itemsize
+    step = n if chunk is None else chunk
+    for i in range(0, n, step):
+        k = min(step, n - i)
+        assert lib.hxcclHostReduce(dst.ctypes.data + i * es, src.ctypes.data + i * es, k, dt, op) == 0
+
+
+def test_bulk_paths_equal_the_element_rule():
+    """Long vectors take shortcuts on the host (pair tables for the 8-bit floats, the machine's
+    half conversions for fp16 sums and products); short ones go element by element through the
+    rule. Both must give the same bits: all 65536 pairs of each 8-bit type, and every fp16 code
+    against random and special partners."""
+    for dt in (L.FLOAT8E4M3, L.FLOAT8E5M2):
+        a = np.repeat(np.arange(256, dtype=np.uint8), 256)
+        b = np.tile(np.arange(256, dtype=np.uint8), 256)
+        for op in (L.SUM, L.PROD, L.MAX, L.MIN):
+            bulk, slow = a.copy(), a.copy()
+            _host_reduce(bulk, b, dt, op)               # 65536 elements: table
+            _host_reduce(slow, b, dt, op, chunk=1024)   # below 4096 per call: rule
+            assert np.array_equal(bulk, slow), (dt, op)
+    rng = np.random.default_rng(5)
+    special = np.array([0x0000, 0x8000, 0x0001, 0x8001, 0x03FF, 0x0400, 0x7BFF, 0xFBFF, 0x7C00, 0xFC00,
+                        0x7C01, 0xFE00, 0x7E00, 0x3C00, 0xBC00, 0x3555], dtype=np.uint16)
+    a = np.arange(65536, dtype=np.uint16)
+    partners = [rng.integers(0, 65536, 65536).astype(np.uint16) for _ in range(3)]
+    partners += [np.full(65536, s, dtype=np.uint16) for s in special]
+    for op in (L.SUM, L.PROD):
+        for b in partners[:6] if op == L.PROD else partners:
+            bulk, slow = a.copy(), a.copy()
+            _host_reduce(bulk, b, L.FLOAT16, op)
+            _host_reduce(slow, b, L.FLOAT16, op, chunk=7)  # fewer than eight per call: rule
+            assert np.array_equal(bulk, slow), (op, hex(int(b[0])))
