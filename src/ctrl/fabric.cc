@@ -258,13 +258,15 @@ void Fabric::end_body(Link& l) {
 }
 
 // Bytes from the connection: frame headers and small bodies come through a read-ahead buffer
-// (one system call then usually delivers a whole small message, header and body), large bodies
-// go straight from the socket into their destination.
+// (one system call then usually delivers a whole small message, header and body, or several
+// of them), larger bodies go straight from the socket into their destination. The buffer is
+// small so that the head of a large body, which arrives in it with the header, costs little to
+// copy on.
 ssize_t Fabric::pull(Link& l, char* into, size_t want) {
-  constexpr size_t kDirect = 16 * 1024;
+  constexpr size_t kAhead = 8 * 1024, kDirect = 4 * 1024;
   if (l.ahead_pos == l.ahead_end) {
     if (want >= kDirect) return ::recv(l.fd, into, want, 0);
-    if (l.ahead.empty()) l.ahead.resize(64 * 1024);
+    if (l.ahead.empty()) l.ahead.resize(kAhead);
     const ssize_t r = ::recv(l.fd, l.ahead.data(), l.ahead.size(), 0);
     if (r <= 0) return r;
     l.ahead_pos = 0;

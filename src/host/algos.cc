@@ -180,9 +180,15 @@ hxcclResult_t host_broadcast(HostCtx c, const void* send, void* recv, size_t byt
         HX_TRY(c.wire.recv(rank_at(pos - bit), recv, bytes));
         break;
       }
+    // the sends to all children leave together (farthest child first, as in the tree's order)
     for (bit >>= 1; bit > 0; bit >>= 1)
-      if (pos + bit < c.n) HX_TRY(c.wire.send(rank_at(pos + bit), recv, bytes));
-    return hxcclSuccess;
+      if (pos + bit < c.n) {
+        if (hxcclResult_t r = c.wire.post_send(rank_at(pos + bit), recv, bytes, kTagColl)) {
+          c.wire.cancel_all();
+          return r;
+        }
+      }
+    return c.wire.finish_all();
   }
   // A rank in the middle takes in piece k+1 while piece k leaves for its successor.
   auto piece = [&](size_t off) { return std::min(kChainPiece, bytes - off); };

@@ -100,9 +100,10 @@ def test_send_recv_and_groups(n):
     assert res[1]["blocking"] == 7.5
 
 
-# sizes around the transport's thresholds: bodies under 16 KiB come through the 64 KiB read-ahead
-# buffer (several frames per system call), larger ones go straight into the receive buffer
-_BURST = [0, 1, 8, 4000, 16352, 16384, 16385, 65504, 65536, 65537, 300_001, 3, 1 << 20, 17, 5]
+# sizes around the transport's thresholds: bodies under 4 KiB come through the 8 KiB read-ahead
+# buffer (several frames per system call), larger ones go straight into the receive buffer, and
+# from 64 KiB on an early frame waits in the socket for its receive
+_BURST = [0, 1, 8, 4000, 4064, 4096, 4097, 8160, 8192, 8193, 16384, 65504, 65536, 65537, 300_001, 3, 1 << 20, 17, 5]
 
 
 def _burst(comm, rank, n):
