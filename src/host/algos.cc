@@ -1,6 +1,7 @@
 #include "algos.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <vector>
@@ -20,11 +21,18 @@ class Scratch {
   std::unique_ptr<char[]> mem_;
 };
 
-// A ring over large blocks moves them in rounds of at most kRingSlice bytes per block, so that
+// A ring over large blocks moves them in rounds of at most ring_slice() bytes per block, so that
 // what a hop receives is still in the cache when it is combined or sent on. Every round cuts all
 // blocks at the same offsets: which rank's value meets which, and in what order, does not
 // change. The pieces of one block count as one message.
-constexpr size_t kRingSlice = size_t(1) << 20;
+size_t ring_slice() {  // HXCCL_RING_SLICE_KB, 16 KiB .. 1 GiB, default 1 MiB
+  static const size_t bytes = [] {
+    const char* e = std::getenv("HXCCL_RING_SLICE_KB");
+    const long kb = e ? std::atol(e) : 0;
+    return kb >= 16 && kb <= (1 << 20) ? size_t(kb) << 10 : size_t(1) << 20;
+  }();
+  return bytes;
+}
 
 // Elements [first, first + len) of a block, clipped to the block.
 Span slice_of(Span whole, size_t first, size_t len) {
@@ -61,7 +69,7 @@ hxcclResult_t host_allreduce_ring(HostCtx c, const void* send, void* recv, size_
   }
   const int next = wrap(c.rank + 1, c.n), prev = wrap(c.rank - 1, c.n);
   const size_t widest = ring_block(count, c.n, 0).len;  // block 0 is never the shorter one
-  const size_t per = std::max<size_t>(1, kRingSlice / es);
+  const size_t per = std::max<size_t>(1, ring_slice() / es);
   Scratch inbox(std::min(widest, per) * es);
   for (size_t first = 0; first < widest; first += per) {
     const bool more = first > 0;
@@ -116,8 +124,8 @@ hxcclResult_t host_allgather(HostCtx c, const void* send, void* recv, size_t blo
   if (send != at(recv, c.rank * block)) std::memmove(at(recv, c.rank * block), send, block);
   if (c.n == 1 || block == 0) return hxcclSuccess;
   const int next = wrap(c.rank + 1, c.n), prev = wrap(c.rank - 1, c.n);
-  for (size_t first = 0; first < block; first += kRingSlice) {
-    const size_t len = std::min(kRingSlice, block - first);
+  for (size_t first = 0; first < block; first += ring_slice()) {
+    const size_t len = std::min(ring_slice(), block - first);
     for (int hop = 0; hop < c.n - 1; ++hop) {
       const int out = wrap(c.rank - hop, c.n), in = wrap(c.rank - hop - 1, c.n);
       HX_TRY(c.wire.exchange(next, at(recv, out * block + first), len, prev,
@@ -147,7 +155,7 @@ hxcclResult_t host_reducescatter(HostCtx c, const void* send, void* recv, size_t
   const bool apart = out + block <= in_lo || in_lo + block * c.n <= out;
   Scratch detour(apart || out == mine ? 0 : block);
   char* result = detour.data() ? detour.data() : out;
-  const size_t slice = std::max<size_t>(1, kRingSlice / es);  // elements per round
+  const size_t slice = std::max<size_t>(1, ring_slice() / es);  // elements per round
   Scratch two(2 * std::min(per, slice) * es);
   const int next = wrap(c.rank + 1, c.n), prev = wrap(c.rank - 1, c.n);
   for (size_t first = 0; first < per; first += slice) {

@@ -115,3 +115,43 @@ def test_cpu_plumbing_config_against_fp64_sum():
             assert np.array_equal(got_sum, res[0][algo, "sum"][0])  # every rank holds the same bits
             # with two ranks both schedules move the whole vector once: two halves (ring) or one piece (rd)
             assert stats == ((count * 4, 2) if algo == "ring" else (count * 4, 1)), (algo, stats)
+
+
+def _sliced_body(comm, rank, n):
+    out = []
+    for dt, op, count in ((L.FLOAT32, L.SUM, 100_003), (L.BFLOAT16, L.AVG, 70_001), (L.INT64, L.MAX, 30_000)):
+        x = inputs_for(n, count, dt, 77)[rank]
+        y = np.zeros_like(x)
+        comm.reset_stats()
+        comm.all_reduce(x, y, op=op, count=count, dtype=dt)
+        stats = comm.stats()
+        z = x.copy()
+        comm.all_reduce(z, op=op, count=count, dtype=dt)          # in place
+        per = count // n
+        rs_in = inputs_for(n, per * n, dt, 78)[rank]
+        rs = np.zeros(per * L.DTYPE_SIZE[dt], dtype=np.uint8).view(oracle.raw_dtype(dt))
+        comm.reduce_scatter(rs_in, rs, op=op, count=per, dtype=dt)
+        ag = np.zeros(per * n * L.DTYPE_SIZE[dt], dtype=np.uint8).view(oracle.raw_dtype(dt))
+        comm.all_gather(rs_in[:per], ag, count=per, dtype=dt)
+        out.append((y, stats, z, rs, ag))
+    return out
+
+
+@pytest.mark.parametrize("n", [2, 3, 5])
+def test_ring_rounds_keep_results_and_message_counts(n):
+    """Ring blocks above HXCCL_RING_SLICE_KB (here 16 KiB, so dozens of rounds with a ragged
+    last one) travel in rounds; the bits, and the messages counted, are those of whole blocks."""
+    res = run_ranks(n, _sliced_body, env={"HXCCL_RING_SLICE_KB": "16"})
+    for k, (dt, op, count) in enumerate(((L.FLOAT32, L.SUM, 100_003), (L.BFLOAT16, L.AVG, 70_001), (L.INT64, L.MAX, 30_000))):
+        ins = inputs_for(n, count, dt, 77)
+        want = oracle.allreduce(ins, dt, op, order=0)
+        per = count // n
+        rs_ins = inputs_for(n, per * n, dt, 78)
+        rs_want = oracle.reducescatter(rs_ins, dt, op) if hasattr(oracle, "reducescatter") else None
+        for r in range(n):
+            y, stats, z, rs, ag = res[r][k]
+            assert np.array_equal(y, want[r]) and np.array_equal(z, want[r]), (n, dt, r)
+            assert stats[1] == 2 * (n - 1), stats
+            if rs_want is not None:
+                assert np.array_equal(rs, rs_want[r]), (n, dt, r)
+            assert np.array_equal(ag, np.concatenate([rs_ins[q][:per] for q in range(n)])), (n, dt, r)
