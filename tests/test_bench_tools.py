@@ -6,6 +6,8 @@ import subprocess
 import sys
 import xml.dom.minidom
 
+import pytest
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -133,3 +135,19 @@ def test_host_benchmark_against_the_reference_runs():
     assert all(r["hxccl_us"] > 0 and r["hxccl_busbw_GBps"] >= 0 for r in rows)
     built = os.path.exists(os.path.join(ROOT, "baseline", "_ref", "libhxccl_ref.so"))
     assert all((r["reference_us"] is not None) == built for r in rows)
+
+
+@pytest.mark.parametrize("extra", [[], ["--compress"]])
+def test_ddp_example_trains_on_two_cpu_ranks(extra):
+    """examples/ddp_train.py through torchrun: the loss falls and all ranks end with the same weights."""
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", str(port),
+                          os.path.join(ROOT, "examples", "ddp_train.py"), "--cpu", "--steps", "12", *extra],
+                         capture_output=True, text=True, timeout=240)
+    assert res.returncode == 0, (res.stdout[-1000:], res.stderr[-2000:])
+    assert "weights identical on all 2 ranks: True" in res.stdout
