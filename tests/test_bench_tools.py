@@ -151,3 +151,20 @@ def test_ddp_example_trains_on_two_cpu_ranks(extra):
                          capture_output=True, text=True, timeout=240)
     assert res.returncode == 0, (res.stdout[-1000:], res.stderr[-2000:])
     assert "weights identical on all 2 ranks: True" in res.stdout
+
+
+@pytest.mark.parametrize("ranks", [2, 3])
+def test_parallel_patterns_example_on_cpu_ranks(ranks):
+    """examples/parallel_patterns.py: tensor, pipeline, sequence and expert parallel data movement
+    on the backend's primitives, each checked against the single-rank computation."""
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks),
+                          "--master-addr", "127.0.0.1", "--master-port", str(port),
+                          os.path.join(ROOT, "examples", "parallel_patterns.py"), "--cpu"],
+                         capture_output=True, text=True, timeout=240)
+    assert res.returncode == 0, (res.stdout[-1000:], res.stderr[-2000:])
+    assert "all ranks agree: True" in res.stdout
