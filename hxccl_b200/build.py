@@ -11,6 +11,10 @@ it with the ordinary kernel objects. Run the CPU tests against it with
     HXCCL_LIBRARY=build/libhxccl_san.so LD_PRELOAD=$(g++ -print-file-name=libasan.so) \
         ASAN_OPTIONS=detect_leaks=0 python -m pytest tests -q -m "not gpu" --deselect tests/test_torch_backend.py
 
+`python -m hxccl_b200.build --tsan` builds the host sources under ThreadSanitizer together with
+build/ranks_as_threads (tests/tsan/ranks_as_threads.cc: the ranks of a communicator as threads of one
+process); run `build/ranks_as_threads 4`.
+
 (the interpreter itself is not instrumented, hence the preload and no leak report; the torch
 backend test is left out because libtorch throws C++ exceptions before the preloaded ASan has
 found the real __cxa_throw, which ends the process with an ASan CHECK that is not about this code).
@@ -53,18 +57,45 @@ def _newest_header() -> float:
 
 
 SANFLAGS = ["-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-g", "-O1"]
+TSANFLAGS = ["-fsanitize=thread", "-fno-omit-frame-pointer", "-g", "-O1"]
 
 
-def _compile(src: Path, hdr_time: float, verbose: bool, sanitize: bool = False) -> Path:
-    sanitize = sanitize and src.suffix != ".cu"
-    obj = OBJ / (str(src.relative_to(SRC)).replace("/", "_") + (".san.o" if sanitize else ".o"))
+_TSAN_CXX: list = []
+
+
+def _tsan_cxx() -> str:
+    """A host compiler that can link its ThreadSanitizer runtime (not every installed one ships it)."""
+    if not _TSAN_CXX:
+        probe = ROOT / "build" / "tsan_probe.cc"
+        probe.parent.mkdir(parents=True, exist_ok=True)
+        probe.write_text("int main() { return 0; }\n")
+        for cxx in dict.fromkeys([os.environ.get("CXX", "g++"), "g++", "/usr/bin/g++", "c++"]):
+            try:
+                ok = subprocess.run([cxx, "-fsanitize=thread", str(probe), "-o", str(probe.with_suffix(""))],
+                                    capture_output=True).returncode == 0
+            except OSError:
+                ok = False
+            if ok:
+                _TSAN_CXX.append(cxx)
+                break
+        else:
+            raise RuntimeError("no host compiler here can link -fsanitize=thread")
+    return _TSAN_CXX[0]
+
+
+def _compile(src: Path, hdr_time: float, verbose: bool, sanitize=False) -> Path:
+    """`sanitize`: False, True (ASan + UBSan) or "thread" (TSan); host sources only."""
+    sanitize = sanitize if src.suffix != ".cu" else False
+    suffix = {False: ".o", True: ".san.o", "thread": ".tsan.o"}[sanitize]
+    obj = OBJ / (str(src.relative_to(SRC)).replace("/", "_") + suffix)
     if obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, hdr_time):
         return obj
     if src.suffix == ".cu":
         cmd = [NVCC, *NVCCFLAGS, *INCLUDES, "-c", str(src), "-o", str(obj)]
     else:
-        cmd = [os.environ.get("CXX", "g++"), *CXXFLAGS, *(SANFLAGS if sanitize else []), *INCLUDES, "-c", str(src),
-               "-o", str(obj)]
+        extra = {False: [], True: SANFLAGS, "thread": TSANFLAGS}[sanitize]
+        cxx = _tsan_cxx() if sanitize == "thread" else os.environ.get("CXX", "g++")
+        cmd = [cxx, *CXXFLAGS, *extra, *INCLUDES, "-c", str(src), "-o", str(obj)]
     if verbose:
         print(" ".join(cmd), flush=True)
     res = subprocess.run(cmd, capture_output=True, text=True)
@@ -110,6 +141,31 @@ def build_sanitized(verbose: bool = False, jobs: int | None = None) -> Path:
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"linking libhxccl_san.so failed:\n{res.stdout}\n{res.stderr}")
+    return out
+
+
+def build_tsan(verbose: bool = False, jobs: int | None = None) -> Path:
+    """Links build/libhxccl_tsan.so (host sources under ThreadSanitizer) and build/ranks_as_threads,
+    the program of tests/tsan/ranks_as_threads.cc that runs the ranks of a communicator as threads of
+    one process, so that the sanitizer sees both ends of every hand-over."""
+    build_lib(verbose, jobs)
+    sources = sorted(SRC.rglob("*.cc")) + sorted(SRC.rglob("*.cu"))
+    hdr_time = _newest_header()
+    with ThreadPoolExecutor(max_workers=jobs or max(1, (os.cpu_count() or 2))) as pool:
+        objs = list(pool.map(lambda s: _compile(s, hdr_time, verbose, sanitize="thread"), sources))
+    out = ROOT / "build" / "libhxccl_tsan.so"
+    cxx = _tsan_cxx()  # the host compiler links: it knows where its TSan runtime is
+    steps = [[cxx, "-shared", "-fsanitize=thread", "-o", str(out), *map(str, objs), f"-L{CUDA_HOME / 'lib64'}",
+              "-lcudart_static", "-pthread", "-ldl", "-lrt"],
+             [cxx, "-std=c++17", *TSANFLAGS, *INCLUDES,
+              str(ROOT / "tests" / "tsan" / "ranks_as_threads.cc"), "-o", str(ROOT / "build" / "ranks_as_threads"),
+              f"-L{ROOT / 'build'}", "-lhxccl_tsan", f"-Wl,-rpath,{ROOT / 'build'}", "-pthread"]]
+    for cmd in steps:
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"{cmd[0]} failed:\n{res.stdout}\n{res.stderr}")
     return out
 
 
@@ -163,6 +219,7 @@ def main() -> None:
     ap.add_argument("--torch", action="store_true", help="also build the torch.distributed backend")
     ap.add_argument("--perf", action="store_true", help="also build bench/hx_perf")
     ap.add_argument("--sanitize", action="store_true", help="also build build/libhxccl_san.so (ASan + UBSan)")
+    ap.add_argument("--tsan", action="store_true", help="also build build/libhxccl_tsan.so and build/ranks_as_threads")
     ap.add_argument("-v", "--verbose", action="store_true")
     ap.add_argument("-j", "--jobs", type=int, default=None)
     args = ap.parse_args()
@@ -173,6 +230,8 @@ def main() -> None:
         print(build_perf(args.verbose))
     if args.sanitize:
         print(build_sanitized(args.verbose, args.jobs))
+    if args.tsan:
+        print(build_tsan(args.verbose, args.jobs))
 
 
 if __name__ == "__main__":

@@ -475,3 +475,33 @@ def test_mpi_carrier_against_a_loopback_mpi(tmp_path):
     assert built.returncode == 0, built.stderr[-3000:]
     ran = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
     assert ran.returncode == 0 and ran.stdout.strip().endswith("ok"), ran.stdout + ran.stderr
+
+
+def test_ranks_as_threads_of_one_process(tmp_path):
+    """tests/tsan/ranks_as_threads.cc against the ordinary library: four ranks as threads of one
+    process, a parent and its Split child used from two threads at once. The same program runs
+    under ThreadSanitizer with `python -m hxccl_b200.build --tsan` (next test)."""
+    import subprocess
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    L.lib()
+    exe = tmp_path / "ranks_as_threads"
+    lib_dir = root / "hxccl_b200" / "lib"
+    subprocess.run(["g++", "-std=c++17", "-O1", f"-I{root / 'include'}", str(root / "tests" / "tsan" / "ranks_as_threads.cc"),
+                    "-o", str(exe), f"-L{lib_dir}", "-lhxccl", f"-Wl,-rpath,{lib_dir}", "-pthread"], check=True)
+    res = subprocess.run([str(exe), "4"], capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0 and "4 ranks as threads: 0 failures" in res.stdout, (res.stdout, res.stderr[-2000:])
+
+
+def test_ranks_as_threads_under_thread_sanitizer():
+    import subprocess
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    exe = root / "build" / "ranks_as_threads"
+    if not exe.exists() or not (root / "build" / "libhxccl_tsan.so").exists():
+        pytest.skip("python -m hxccl_b200.build --tsan has not been run")
+    env = dict(os.environ, TSAN_OPTIONS=f"suppressions={root / 'tests' / 'tsan' / 'suppressions.txt'} exitcode=66")
+    res = subprocess.run([str(exe), "4"], capture_output=True, text=True, timeout=300, env=env)
+    assert res.returncode == 0 and "ThreadSanitizer" not in res.stderr, res.stderr[-3000:]
