@@ -1,6 +1,7 @@
 #include "reduce_host.h"
 
 #include <cstring>
+#include <memory>
 #include <mutex>
 #if defined(__x86_64__) && defined(__GNUC__)
 #include <immintrin.h>
@@ -60,6 +61,27 @@ void scale_tiles(F* out, const F* src, F k, size_t count) {
     }
   }
 }
+// The narrow floats have few codes: for a long vector the scaled value of every code is worked
+// out once with the rule and the vector is mapped through that table.
+template <typename T>
+bool table_scale(T*, const T*, T, size_t) { return false; }
+template <typename T, typename Bits>
+bool map_codes(T* o, const T* s, T k, size_t n) {
+  constexpr size_t kCodes = size_t(1) << (8 * sizeof(Bits));
+  if (n < 4 * kCodes) return false;
+  std::unique_ptr<Bits[]> table(new Bits[kCodes]);
+  for (size_t c = 0; c < kCodes; ++c) table[c] = scale(T{Bits(c)}, k).b;
+  for (size_t i = 0; i < n; ++i) o[i].b = table[s[i].b];
+  return true;
+}
+template <>
+bool table_scale<e4m3>(e4m3* o, const e4m3* s, e4m3 k, size_t n) { return map_codes<e4m3, uint8_t>(o, s, k, n); }
+template <>
+bool table_scale<e5m2>(e5m2* o, const e5m2* s, e5m2 k, size_t n) { return map_codes<e5m2, uint8_t>(o, s, k, n); }
+template <>
+bool table_scale<f16>(f16* o, const f16* s, f16 k, size_t n) { return map_codes<f16, uint16_t>(o, s, k, n); }
+template <>
+bool table_scale<bf16>(bf16* o, const bf16* s, bf16 k, size_t n) { return map_codes<bf16, uint16_t>(o, s, k, n); }
 template <typename T>
 bool fast_scale(T*, const T*, T, size_t) { return false; }
 template <>
@@ -180,6 +202,7 @@ void scale_into(void* dst, const void* src, size_t count, int dt, const void* sc
     T* o = static_cast<T*>(dst);
     const T* s = static_cast<const T*>(src);
     if (fast_scale<T>(o, s, k, count)) break;
+    if (table_scale<T>(o, s, k, count)) break;
     for (size_t i = 0; i < count; ++i) o[i] = scale(s[i], k);
   })
 }

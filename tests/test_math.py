@@ -187,3 +187,21 @@ def test_bulk_paths_equal_the_element_rule():
             _host_reduce(bulk, b, L.FLOAT16, op)
             _host_reduce(slow, b, L.FLOAT16, op, chunk=7)  # fewer than eight per call: rule
             assert np.array_equal(bulk, slow), (op, hex(int(b[0])))
+
+
+def test_bulk_scaling_equals_the_element_rule():
+    """Long vectors of the narrow floats are scaled through a table of all codes; short ones
+    element by element. Every code times a few scalars, both ways."""
+    lib = L.lib()
+    lib.hxcclHostScale.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
+    for dt, (bits, _, npdt) in NARROW.items():
+        codes = np.arange(1 << bits, dtype=npdt)
+        src = np.tile(codes, 4)                      # four times the number of codes: table
+        for scalar in (0.125, -3.0, 1.0 / 3.0, 0.0, float("inf"), float("nan"), 60000.0):
+            k = np.array([enc(dt, scalar)], dtype=npdt)
+            bulk, slow = np.zeros_like(src), np.zeros_like(src)
+            assert lib.hxcclHostScale(bulk.ctypes.data, src.ctypes.data, src.size, dt, k.ctypes.data) == 0
+            for i in range(0, src.size, codes.size):  # below the threshold per call: rule
+                assert lib.hxcclHostScale(slow.ctypes.data + i * src.itemsize, src.ctypes.data + i * src.itemsize,
+                                          codes.size, dt, k.ctypes.data) == 0
+            assert np.array_equal(bulk, slow), (dt, scalar)
