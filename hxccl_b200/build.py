@@ -9,7 +9,8 @@ The sanitizer build compiles every host source (.cc) with -fsanitize=address,und
 it with the ordinary kernel objects. Run the CPU tests against it with
 
     HXCCL_LIBRARY=build/libhxccl_san.so LD_PRELOAD=$(g++ -print-file-name=libasan.so) \
-        ASAN_OPTIONS=detect_leaks=0 python -m pytest tests -q -m "not gpu" --deselect tests/test_torch_backend.py
+        ASAN_OPTIONS=detect_leaks=0 python -m pytest tests -q -m "not gpu" --deselect tests/test_torch_backend.py \
+        --deselect tests/test_bench_tools.py
 
 `python -m hxccl_b200.build --tsan` builds the host sources under ThreadSanitizer together with
 build/ranks_as_threads (tests/tsan/ranks_as_threads.cc: the ranks of a communicator as threads of one

@@ -503,5 +503,6 @@ def test_ranks_as_threads_under_thread_sanitizer():
     if not exe.exists() or not (root / "build" / "libhxccl_tsan.so").exists():
         pytest.skip("python -m hxccl_b200.build --tsan has not been run")
     env = dict(os.environ, TSAN_OPTIONS=f"suppressions={root / 'tests' / 'tsan' / 'suppressions.txt'} exitcode=66")
+    env.pop("LD_PRELOAD", None)  # another sanitizer's runtime (the ASan run of this suite) cannot share the process
     res = subprocess.run([str(exe), "4"], capture_output=True, text=True, timeout=300, env=env)
     assert res.returncode == 0 and "ThreadSanitizer" not in res.stderr, res.stderr[-3000:]
