@@ -19,6 +19,7 @@
 #include <torch/csrc/distributed/c10d/Work.hpp>
 #include <torch/python.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <optional>
 
@@ -158,6 +159,7 @@ class HxcclBackend : public Backend {
     for (const at::Tensor& t : keep)  // the allocator must not hand the memory out while the kernel runs
       c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), cs);
     enqueue(cs.stream());
+    if (coalescing_) coalesced_device_ = probe.device().index();  // the batch's Work comes from endCoalescing
     return c10::make_intrusive<StreamWork>(type, std::move(out), cs);
   }
 
@@ -370,12 +372,30 @@ class HxcclBackend : public Backend {
     }
     return w;
   }
-  void startCoalescing() override { ok(hxcclGroupStart(), "GroupStart"); }
+  // Coalescing = one hxccl group: the calls between start and end are queued and run at the
+  // end, collectives first, then all Send/Recv together (on GPUs in one kernel, so that
+  // dist.batch_isend_irecv cannot stall on its own order). The Work of the whole batch is
+  // recorded on the communication stream after the group has been launched.
+  void startCoalescing() override {
+    ok(hxcclGroupStart(), "GroupStart");
+    coalescing_ = true;
+    coalesced_device_ = -1;
+  }
   c10::intrusive_ptr<Work> endCoalescing() override {
+    coalescing_ = false;
     ok(hxcclGroupEnd(), "GroupEnd");
+    if (coalesced_device_ >= 0)
+      return c10::make_intrusive<StreamWork>(OpType::COALESCED, std::vector<at::Tensor>{},
+                                             comm_stream(coalesced_device_));
     return c10::make_intrusive<DoneWork>(OpType::COALESCED, std::vector<at::Tensor>{});
   }
-  bool supportsCoalescing() const override { return false; }
+  // Advertised where it has been exercised: process groups without a GPU always, with a GPU
+  // when HXCCL_TORCH_COALESCE=1 asks for it.
+  bool supportsCoalescing() const override {
+    if (device_ < 0) return true;
+    const char* e = std::getenv("HXCCL_TORCH_COALESCE");
+    return e && *e == '1';
+  }
 
  private:
   void ok(hxcclResult_t r, const char* what) const {
@@ -389,6 +409,8 @@ class HxcclBackend : public Backend {
   }
   hxcclComm_t comm_ = nullptr;
   c10::DeviceIndex device_ = -1;
+  bool coalescing_ = false;
+  c10::DeviceIndex coalesced_device_ = -1;
   std::optional<c10::cuda::CUDAStream> stream_;
 };
 

@@ -60,6 +60,27 @@ def _worker(rank, world, port, q):
         sc = torch.empty(2)
         dist.scatter(sc, [torch.full((2,), float(r)) for r in range(world)] if rank == 0 else None, src=0)
         assert sc.tolist() == [float(rank)] * 2
+        # a batch of sends and receives is one hxccl group: a crossed exchange of 8 MiB with both
+        # ranks naming the send first runs without either side waiting for the other's order
+        nxt, prv = (rank + 1) % world, (rank - 1) % world
+        big_out = torch.full((2 << 20,), float(rank))
+        big_in, small_in = torch.empty(2 << 20), torch.empty(3)
+        works = dist.batch_isend_irecv([dist.P2POp(dist.isend, big_out, nxt),
+                                        dist.P2POp(dist.isend, torch.full((3,), rank + 0.5), nxt),
+                                        dist.P2POp(dist.irecv, big_in, prv),
+                                        dist.P2POp(dist.irecv, small_in, prv)])
+        for w in works:
+            w.wait()
+        assert big_in[0].item() == float(prv) and big_in[-1].item() == float(prv)
+        assert small_in.tolist() == [prv + 0.5] * 3
+        offered = dist.distributed_c10d._get_default_group()._get_backend(torch.device("cpu")).supports_coalescing
+        assert offered == (not torch.cuda.is_available() or os.environ.get("HXCCL_TORCH_COALESCE") == "1")
+        if offered:  # several collectives under torch's coalescing manager
+            c1, c2 = torch.full((5,), float(rank)), torch.full((70000,), 1.0)
+            with dist.distributed_c10d._coalescing_manager(device=torch.device("cpu")):
+                dist.all_reduce(c1)
+                dist.all_reduce(c2)
+            assert c1.tolist() == [float(sum(range(world)))] * 5 and c2[-1].item() == float(world)
         dist.barrier()
         with pytest.raises((ValueError, RuntimeError)):
             dist.all_reduce(torch.zeros(4, 4).t())  # not contiguous
