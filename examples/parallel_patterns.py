@@ -82,9 +82,14 @@ def main() -> int:
     # ---- sequence parallel: blocks round the ring -------------------------------------------------
     block = torch.full((16,), float(rank), device=dev)
     seen = [float(block[0])]
+    batched = dist.distributed_c10d._get_default_group()._get_backend(dev).supports_coalescing
     for _ in range(n - 1):
         incoming = torch.empty_like(block)
-        if rank % 2 == 0:   # even ranks send first, odd ranks receive first: no pair waits on itself
+        if batched:         # one library group: send and receive move together
+            for w in dist.batch_isend_irecv([dist.P2POp(dist.isend, block, (rank + 1) % n),
+                                             dist.P2POp(dist.irecv, incoming, (rank - 1) % n)]):
+                w.wait()
+        elif rank % 2 == 0:  # even ranks send first, odd ranks receive first: no pair waits on itself
             dist.send(block, dst=(rank + 1) % n)
             dist.recv(incoming, src=(rank - 1) % n)
         else:
